@@ -1,0 +1,128 @@
+/*
+ * selective_attention_b200.h — C ABI of the B200 (sm_100a) Selective Attention operator.
+ *
+ * The reference project (Royer-Research-Labs/Selective-Attention-Study) has no FFI: its operator is a
+ * Python module of Triton kernels.  This library replaces what that module launches on the device;
+ * the Python host wrapper (selective_attention_b200/kernels.py) keeps the reference's Python
+ * signatures and calls these entry points through ctypes.  Each declaration names the reference code
+ * it replaces (paths are relative to the reference project).
+ *
+ * Conventions
+ *   - every pointer is a DEVICE pointer unless its name ends in _host; the library never allocates
+ *     device memory and never frees any: all outputs and scratch come from the caller;
+ *   - q, k, v are (batch, heads, seq, head_dim) with arbitrary batch/head/token strides (in elements)
+ *     and a contiguous innermost axis; head 0 of every sequence supplies the selection (the per-head
+ *     variant reshapes every head into its own one-head sequence, as the reference does);
+ *   - `stream` is a cudaStream_t passed as void*; launches are asynchronous on it;
+ *   - the return value is 0 (SA_OK) or one of the SA_ERR_* codes; sa_status_string() names it.
+ */
+#ifndef SELECTIVE_ATTENTION_B200_H
+#define SELECTIVE_ATTENTION_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum sa_status {
+  SA_OK = 0,
+  SA_ERR_BAD_ARGUMENT = 1,   /* null pointer, non-positive size, bad enum, struct size mismatch       */
+  SA_ERR_UNSUPPORTED = 2,    /* shape / dtype / engine combination the selected engine cannot run     */
+  SA_ERR_ALIGNMENT = 3,      /* a pointer or stride violates the engine's alignment rule              */
+  SA_ERR_WORKSPACE = 4,      /* workspace smaller than sa_*_workspace_bytes() reports                 */
+  SA_ERR_CUDA = 5,           /* a CUDA runtime / driver call failed; sa_last_cuda_error() has the code */
+  SA_ERR_DEVICE_TIMEOUT = 6, /* a bounded device-side wait ran out (status word set by a kernel)      */
+  SA_ERR_TOO_LARGE = 7       /* problem exceeds a fixed capacity (static-scratch entry point)         */
+};
+
+enum sa_dtype { SA_F32 = 0, SA_BF16 = 1, SA_F16 = 2 };
+
+/* SA_ENGINE_SIMT   : fp32 FFMA arithmetic on CUDA cores, exact ("ieee") products; any supported dtype,
+ *                    head_dim 16/32/64/128, any seq >= 1; carry checkpoints every 32 queries.
+ * SA_ENGINE_TCGEN05: bf16/fp16 operands on the tcgen05 tensor cores with fp32 TMEM accumulators, fed by
+ *                    TMA; head_dim 64 or 128; carry checkpoints every 128 queries.                    */
+enum sa_engine { SA_ENGINE_SIMT = 0, SA_ENGINE_TCGEN05 = 1 };
+
+enum sa_damp { SA_DAMP_NONE = 0, SA_DAMP_LINEAR = 1, SA_DAMP_SQRT = 2 };
+
+typedef struct sa_problem {
+  int32_t struct_bytes; /* sizeof(sa_problem), checked                                                */
+  int32_t dtype;        /* sa_dtype of q, k, v                                                        */
+  int32_t engine;       /* sa_engine                                                                  */
+  int32_t batch;        /* sequences (one selector, head 0, per sequence)                             */
+  int32_t heads;
+  int32_t seq;          /* T >= 1                                                                     */
+  int32_t head_dim;     /* 16, 32, 64 or 128                                                          */
+  int32_t exempt;       /* >= 1: keys [0, exempt) are never selected (1 = <BOS> only)                 */
+  int32_t damp;         /* sa_damp; forward only                                                      */
+  int32_t train_len;    /* used when damp != SA_DAMP_NONE                                             */
+  int64_t q_stride[3];  /* batch, head, token strides of q in elements                                */
+  int64_t k_stride[3];
+  int64_t v_stride[3];
+} sa_problem;
+
+/* Library / build identification. */
+int sa_abi_version(void);
+const char* sa_status_string(int status);
+int sa_last_cuda_error(void);              /* cudaError_t of the most recent SA_ERR_CUDA on this thread */
+
+/* 1 when the engine is compiled into this build of the library, else 0. */
+int sa_engine_available(int engine);
+
+/* Query rows between two checkpoints of the running selection sum for an engine (32 or 128).
+ * Replaces the module constant CARRY_M (src/selective_attention/kernels.py:86-87). */
+int sa_carry_rows(int engine);
+
+/* Forward.  Replaces the two launches of selective_attention_forward
+ * (src/selective_attention/kernels.py:526-605: _selective_carry :111-138 and
+ * _selective_forward / _selective_forward_grouped :140-194, :366-424).
+ *   out    (batch, heads, seq, head_dim) fp32, contiguous
+ *   lse2   (batch, heads, seq) fp32: log2 of the softmax denominator in the log2 domain of
+ *          z = (L - F) * log2(e); equals the reference's rmax + log2(rden)
+ *   carry  (batch, ceil(seq / carry_rows), seq) fp32 scratch AND saved state for the backward: row r
+ *          holds, for every key, the selection received from queries < r * carry_rows
+ *   total  (batch, seq) fp32: selection received from all queries ("selected_total")
+ * carry needs no initialisation. */
+int sa_forward(const sa_problem* p, const void* q, const void* k, const void* v,
+               float* out, float* lse2, float* carry, float* total, void* stream);
+
+/* Bytes of scratch sa_backward needs for this problem (0 on a bad problem). */
+size_t sa_backward_workspace_bytes(const sa_problem* p);
+
+/* Backward.  Replaces _SelectiveAttentionFn.backward (src/selective_attention/kernels.py:621-666):
+ * the dbar reduction (:636), the zero fills (:638-642), _selective_backward / _selective_backward_pair
+ * (:196-364) and the fold of dq0 / dk0 into head 0 with the casts (:662-666).
+ *   out, lse2, carry      as produced by sa_forward for the same problem
+ *   d_out                 (batch, heads, seq, head_dim) contiguous, element type d_out_dtype
+ *   dq, dk, dv            (batch, heads, seq, head_dim) contiguous, element type p->dtype
+ *   workspace             sa_backward_workspace_bytes(p) bytes, 256-byte aligned; contents undefined
+ *                         on entry and exit */
+int sa_backward(const sa_problem* p, const void* q, const void* k, const void* v,
+                const float* out, const float* lse2, const float* carry,
+                const void* d_out, int d_out_dtype,
+                void* dq, void* dk, void* dv,
+                void* workspace, size_t workspace_bytes, void* stream);
+
+/* Bytes of scratch sa_decode_step needs. */
+size_t sa_decode_workspace_bytes(int batch, int heads, int groups, int length, int head_dim);
+
+/* One cached decode step.  Replaces the PyTorch ops of SelectiveAttention.step_cache
+ * (src/selective_attention/mixers.py:115-130) and _append_kv (src/selective_attention/model.py:86-93).
+ *   k_cache, v_cache (batch, heads, capacity, head_dim) contiguous, element type dtype
+ *   selected         (batch, groups, capacity) fp32: selection each cached key has received so far;
+ *                    updated in place AFTER y is formed
+ *   q1, k1, v1       (batch, heads, head_dim) contiguous, element type dtype: the new token
+ *   length           number of cached tokens BEFORE this step; k1/v1 are written at index `length`
+ *   y                (batch, heads, head_dim) fp32
+ * Heads are split in `groups` contiguous runs; the first head of a run is its selector. */
+int sa_decode_step(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim,
+                   int exempt, const void* q1, const void* k1, const void* v1,
+                   void* k_cache, void* v_cache, float* selected, float* y,
+                   void* workspace, size_t workspace_bytes, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SELECTIVE_ATTENTION_B200_H */

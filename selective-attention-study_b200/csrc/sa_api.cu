@@ -1,0 +1,193 @@
+// extern "C" boundary of the Selective Attention library: argument checks, workspace carving and the
+// launch sequences of the two engines.  Declarations and the reference code each entry point replaces
+// are in include/selective_attention_b200.h.
+#include <math.h>
+
+#include "sa_common.cuh"
+
+namespace sa {
+
+static thread_local int g_last_cuda_error = 0;
+void set_last_cuda_error(int code) { g_last_cuda_error = code; }
+
+namespace {
+
+size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
+
+bool dim_ok(int d) { return d == 16 || d == 32 || d == 64 || d == 128; }
+bool dtype_ok(int t) { return t == SA_F32 || t == SA_BF16 || t == SA_F16; }
+size_t dtype_bytes(int t) { return t == SA_F32 ? 4 : 2; }
+
+int to_problem(const sa_problem* in, const void* q, const void* k, const void* v, Problem* p) {
+  if (in == nullptr || in->struct_bytes != (int32_t)sizeof(sa_problem)) return SA_ERR_BAD_ARGUMENT;
+  if (!dtype_ok(in->dtype)) return SA_ERR_BAD_ARGUMENT;
+  if (in->engine != SA_ENGINE_SIMT && in->engine != SA_ENGINE_TCGEN05) return SA_ERR_BAD_ARGUMENT;
+  if (in->batch < 1 || in->heads < 1 || in->seq < 1 || in->exempt < 1) return SA_ERR_BAD_ARGUMENT;
+  if (!dim_ok(in->head_dim)) return SA_ERR_UNSUPPORTED;
+  if (in->damp < SA_DAMP_NONE || in->damp > SA_DAMP_SQRT) return SA_ERR_BAD_ARGUMENT;
+  if (in->damp != SA_DAMP_NONE && in->train_len < 1) return SA_ERR_BAD_ARGUMENT;
+  if ((int64_t)in->batch * in->heads > 65535) return SA_ERR_UNSUPPORTED;   // grid.y
+  p->batch = in->batch;
+  p->heads = in->heads;
+  p->seq = in->seq;
+  p->head_dim = in->head_dim;
+  p->exempt = in->exempt;
+  p->damp = in->damp;
+  p->train_len = in->train_len;
+  p->dtype = in->dtype;
+  p->scale = (float)(1.0 / sqrt((double)in->head_dim));
+  p->q = Strided{q, in->q_stride[0], in->q_stride[1], in->q_stride[2]};
+  p->k = Strided{k, in->k_stride[0], in->k_stride[1], in->k_stride[2]};
+  p->v = Strided{v, in->v_stride[0], in->v_stride[1], in->v_stride[2]};
+  return SA_OK;
+}
+
+struct BackwardWorkspace {
+  size_t dq_acc, dk_acc, dq0, dk0, dbar, d_out_lowp, total;
+};
+
+BackwardWorkspace carve(const sa_problem* in) {
+  const size_t rows = (size_t)in->batch * in->heads * in->seq;
+  const size_t elems = rows * in->head_dim;
+  const size_t elems0 = (size_t)in->batch * in->seq * in->head_dim;
+  BackwardWorkspace w{};
+  size_t off = 0;
+  w.dq_acc = off; off = align_up(off + elems * 4, 256);
+  w.dk_acc = off;
+  if (in->engine == SA_ENGINE_SIMT) off = align_up(off + elems * 4, 256);   // tensor-core engine stores dk directly
+  w.dq0 = off; off = align_up(off + elems0 * 4, 256);
+  w.dk0 = off; off = align_up(off + elems0 * 4, 256);
+  w.dbar = off; off = align_up(off + rows * 4, 256);
+  w.d_out_lowp = off;   // d_out converted for the engine: bf16/fp16 (tensor-core) or fp32 (CUDA-core)
+  off = align_up(off + elems * (in->engine == SA_ENGINE_TCGEN05 ? 2 : 4), 256);
+  w.total = off;
+  return w;
+}
+
+}  // namespace
+}  // namespace sa
+
+using namespace sa;
+
+extern "C" {
+
+int sa_abi_version(void) { return 1; }
+
+const char* sa_status_string(int status) {
+  switch (status) {
+    case SA_OK: return "ok";
+    case SA_ERR_BAD_ARGUMENT: return "bad argument";
+    case SA_ERR_UNSUPPORTED: return "unsupported shape, dtype or engine";
+    case SA_ERR_ALIGNMENT: return "pointer or stride alignment";
+    case SA_ERR_WORKSPACE: return "workspace too small";
+    case SA_ERR_CUDA: return "CUDA call failed";
+    case SA_ERR_DEVICE_TIMEOUT: return "device-side wait timed out";
+    case SA_ERR_TOO_LARGE: return "problem exceeds the fixed capacity";
+  }
+  return "unknown status";
+}
+
+int sa_last_cuda_error(void) { return g_last_cuda_error; }
+
+int sa_engine_available(int engine) {
+  if (engine == SA_ENGINE_SIMT) return 1;
+  if (engine == SA_ENGINE_TCGEN05) return tc_available();
+  return 0;
+}
+
+int sa_carry_rows(int engine) {
+  if (engine == SA_ENGINE_SIMT) return kSimtCarryRows;
+  if (engine == SA_ENGINE_TCGEN05) return kTcCarryRows;
+  return 0;
+}
+
+int sa_forward(const sa_problem* in, const void* q, const void* k, const void* v, float* out, float* lse2,
+               float* carry, float* total, void* stream) {
+  Problem p;
+  int st = to_problem(in, q, k, v, &p);
+  if (st != SA_OK) return st;
+  if (!q || !k || !v || !out || !lse2 || !carry || !total) return SA_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (in->engine == SA_ENGINE_SIMT) return simt_forward(p, out, lse2, carry, total, s);
+  st = tc_supported(p);
+  if (st != SA_OK) return st;
+  return tc_forward(p, out, lse2, carry, total, s);
+}
+
+size_t sa_backward_workspace_bytes(const sa_problem* in) {
+  Problem p;
+  if (to_problem(in, nullptr, nullptr, nullptr, &p) != SA_OK) return 0;
+  return carve(in).total;
+}
+
+int sa_backward(const sa_problem* in, const void* q, const void* k, const void* v, const float* out,
+                const float* lse2, const float* carry, const void* d_out, int d_out_dtype, void* dq, void* dk,
+                void* dv, void* workspace, size_t workspace_bytes, void* stream) {
+  Problem p;
+  int st = to_problem(in, q, k, v, &p);
+  if (st != SA_OK) return st;
+  if (!q || !k || !v || !out || !lse2 || !carry || !d_out || !dq || !dk || !dv || !workspace) return SA_ERR_BAD_ARGUMENT;
+  if (!dtype_ok(d_out_dtype) || in->damp != SA_DAMP_NONE) return SA_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return SA_ERR_ALIGNMENT;
+  const BackwardWorkspace w = carve(in);
+  if (workspace_bytes < w.total) return SA_ERR_WORKSPACE;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  char* base = static_cast<char*>(workspace);
+  float* dq_acc = reinterpret_cast<float*>(base + w.dq_acc);
+  float* dk_acc = reinterpret_cast<float*>(base + w.dk_acc);
+  float* dq0 = reinterpret_cast<float*>(base + w.dq0);
+  float* dk0 = reinterpret_cast<float*>(base + w.dk0);
+  float* dbar = reinterpret_cast<float*>(base + w.dbar);
+  const int64_t rows = (int64_t)p.batch * p.heads * p.seq;
+  const int64_t per_head = (int64_t)p.seq * p.head_dim;
+  const size_t elems = (size_t)rows * p.head_dim;
+  const size_t elems0 = (size_t)p.batch * per_head;
+
+  // dq_acc, dq0 and dk0 are accumulated with atomics and start at zero (the dq0/dk0 pair is contiguous).
+  SA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, elems * 4, s));
+  SA_CUDA_CHECK(cudaMemsetAsync(dq0, 0, (w.dk0 - w.dq0) + elems0 * 4, s));
+
+  if (in->engine == SA_ENGINE_SIMT) {
+    const float* d_out_f32 = static_cast<const float*>(d_out);
+    void* copy = nullptr;
+    if (d_out_dtype != SA_F32) {
+      copy = base + w.d_out_lowp;
+      d_out_f32 = static_cast<const float*>(copy);
+    }
+    st = launch_dbar(out, d_out, d_out_dtype, rows, p.head_dim, dbar, copy, SA_F32, s);
+    if (st != SA_OK) return st;
+    st = simt_backward(p, lse2, carry, dbar, d_out_f32, dq_acc, dk_acc, dq0, dk0, dv, s);
+    if (st != SA_OK) return st;
+    st = launch_fold_cast(dk_acc, dk0, dk, p.dtype, p.batch, p.heads, per_head, s);
+    if (st != SA_OK) return st;
+    return launch_fold_cast(dq_acc, dq0, dq, p.dtype, p.batch, p.heads, per_head, s);
+  }
+  st = tc_supported(p);
+  if (st != SA_OK) return st;
+  void* d_out_lowp = base + w.d_out_lowp;
+  st = launch_dbar(out, d_out, d_out_dtype, rows, p.head_dim, dbar, d_out_lowp, p.dtype, s);
+  if (st != SA_OK) return st;
+  // The tensor-core backward accumulates dk (with head 0's selection share) in fp32 in dk_acc as well.
+  return SA_ERR_UNSUPPORTED;
+}
+
+size_t sa_decode_workspace_bytes(int batch, int heads, int groups, int length, int head_dim) {
+  if (batch < 1 || heads < 1 || groups < 1 || length < 0 || !dim_ok(head_dim)) return 0;
+  return decode_workspace_floats(batch, heads, groups, length, head_dim) * sizeof(float);
+}
+
+int sa_decode_step(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim, int exempt,
+                   const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache, float* selected,
+                   float* y, void* workspace, size_t workspace_bytes, void* stream) {
+  if (!dtype_ok(dtype) || batch < 1 || heads < 1 || groups < 1 || heads % groups != 0 || length < 0 || exempt < 1)
+    return SA_ERR_BAD_ARGUMENT;
+  if (!dim_ok(head_dim)) return SA_ERR_UNSUPPORTED;
+  if (length >= capacity) return SA_ERR_BAD_ARGUMENT;
+  if (!q1 || !k1 || !v1 || !k_cache || !v_cache || !selected || !y || !workspace) return SA_ERR_BAD_ARGUMENT;
+  if ((int64_t)batch * heads > 65535) return SA_ERR_UNSUPPORTED;
+  if (workspace_bytes < sa_decode_workspace_bytes(batch, heads, groups, length, head_dim)) return SA_ERR_WORKSPACE;
+  return decode_step(dtype, batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, k_cache, v_cache,
+                     selected, y, static_cast<float*>(workspace), static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,78 @@
+// Shared declarations of the Selective Attention kernels (sm_100a).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/selective_attention_b200.h"
+
+namespace sa {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kSimtCarryRows = 32;   // query rows per carry checkpoint, CUDA-core engine
+constexpr int kTcCarryRows = 128;    // tensor-core engine: one checkpoint per 128-query tile
+
+template <typename T> __device__ __forceinline__ float to_float(T x);
+template <> __device__ __forceinline__ float to_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_float<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_float<__half>(__half x) { return __half2float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_float<__half>(float x) { return __float2half_rn(x); }
+
+// Everything a kernel needs to find a (batch, head) row of q, k or v.
+struct Strided {
+  const void* ptr;
+  int64_t sb, sh, st;   // batch, head, token strides in elements
+};
+
+struct Problem {
+  int batch, heads, seq, head_dim;
+  int exempt, damp, train_len;
+  int dtype;
+  float scale;          // 1 / sqrt(head_dim)
+  Strided q, k, v;
+};
+
+// ---- engine entry points (host) -------------------------------------------------------------------
+int simt_forward(const Problem& p, float* out, float* lse2, float* carry, float* total, cudaStream_t s);
+int simt_backward(const Problem& p, const float* lse2, const float* carry, const float* dbar,
+                  const float* d_out, float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv,
+                  cudaStream_t s);
+
+int tc_available();
+int tc_supported(const Problem& p);
+int tc_forward(const Problem& p, float* out, float* lse2, float* carry, float* total, cudaStream_t s);
+int tc_backward(const Problem& p, const float* lse2, const float* carry, const float* dbar,
+                const void* d_out_lowp, float* dq_acc, float* dq0, float* dk0,
+                void* dk, void* dv, cudaStream_t s);
+
+// ---- helper launches shared by both engines --------------------------------------------------------
+// dbar[row] = sum_d d_out[row, d] * out[row, d]; optionally also writes d_out rounded to `lowp_dtype`.
+int launch_dbar(const float* out, const void* d_out, int d_out_dtype, int64_t rows, int head_dim,
+                float* dbar, void* d_out_lowp, int lowp_dtype, cudaStream_t s);
+// dst[b, h] = cast(acc[b, h] + (h == 0 ? acc0[b] : 0)), rows of head_dim elements.
+int launch_fold_cast(const float* acc, const float* acc0, void* dst, int dtype, int batch, int heads,
+                     int64_t seq_times_dim, cudaStream_t s);
+
+size_t decode_workspace_floats(int batch, int heads, int groups, int length, int head_dim);
+int decode_step(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim, int exempt,
+                const void* q1, const void* k1, const void* v1, void* kc, void* vc, float* selected, float* y,
+                float* ws, cudaStream_t s);
+
+void set_last_cuda_error(int code);
+
+#define SA_CUDA_CHECK(expr)                                   \
+  do {                                                        \
+    cudaError_t _e = (expr);                                  \
+    if (_e != cudaSuccess) {                                  \
+      ::sa::set_last_cuda_error(static_cast<int>(_e));        \
+      return SA_ERR_CUDA;                                     \
+    }                                                         \
+  } while (0)
+
+}  // namespace sa

@@ -1,0 +1,310 @@
+// Bandwidth-bound helpers of the Selective Attention operator (sm_100a):
+//   dbar      dbar[row] = sum_d dO[row, d] * out[row, d], optionally also dO rounded to bf16 / fp16
+//             (reference: src/selective_attention/kernels.py:635-636)
+//   fold/cast dq = cast(dq_acc + [head 0] dq0)            (reference: kernels.py:662-666)
+//   decode    one cached decode step                       (reference: src/selective_attention/mixers.py:115-130)
+#include "sa_common.cuh"
+
+namespace sa {
+namespace {
+
+// ---- dbar -----------------------------------------------------------------------------------------
+// A group of D / 4 consecutive lanes owns one row; every lane handles 4 consecutive elements.
+template <typename TDO, typename TLOW, int D, bool kWriteLow>
+__global__ void __launch_bounds__(256) dbar_kernel(const float* __restrict__ out, const TDO* __restrict__ d_out,
+                                                   int64_t rows, float* __restrict__ dbar,
+                                                   TLOW* __restrict__ d_out_low) {
+  constexpr int kLanes = D / 4;
+  const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t row = gid / kLanes;
+  const int lane = (int)(gid % kLanes);
+  float sum = 0.f;
+  if (row < rows) {
+    const int64_t off = row * D + lane * 4;
+    float4 o = *reinterpret_cast<const float4*>(out + off);
+    float g[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) g[e] = to_float<TDO>(d_out[off + e]);
+    sum = g[0] * o.x + g[1] * o.y + g[2] * o.z + g[3] * o.w;
+    if (kWriteLow) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) d_out_low[off + e] = from_float<TLOW>(g[e]);
+    }
+  }
+#pragma unroll
+  for (int s = kLanes / 2; s > 0; s >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, s);
+  if (row < rows && lane == 0) dbar[row] = sum;
+}
+
+template <typename TDO, typename TLOW, bool kWriteLow>
+int dbar_by_dim(const float* out, const void* d_out, int64_t rows, int head_dim, float* dbar, void* low,
+                cudaStream_t s) {
+  const int64_t threads = rows * (head_dim / 4);
+  const unsigned blocks = (unsigned)((threads + 255) / 256);
+  const TDO* g = static_cast<const TDO*>(d_out);
+  TLOW* l = static_cast<TLOW*>(low);
+  switch (head_dim) {
+    case 16: dbar_kernel<TDO, TLOW, 16, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
+    case 32: dbar_kernel<TDO, TLOW, 32, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
+    case 64: dbar_kernel<TDO, TLOW, 64, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
+    case 128: dbar_kernel<TDO, TLOW, 128, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
+    default: return SA_ERR_UNSUPPORTED;
+  }
+  SA_CUDA_CHECK(cudaGetLastError());
+  return SA_OK;
+}
+
+template <typename TDO>
+int dbar_by_low(const float* out, const void* d_out, int64_t rows, int head_dim, float* dbar, void* low,
+                int low_dtype, cudaStream_t s) {
+  if (low == nullptr) return dbar_by_dim<TDO, float, false>(out, d_out, rows, head_dim, dbar, nullptr, s);
+  if (low_dtype == SA_BF16) return dbar_by_dim<TDO, __nv_bfloat16, true>(out, d_out, rows, head_dim, dbar, low, s);
+  if (low_dtype == SA_F16) return dbar_by_dim<TDO, __half, true>(out, d_out, rows, head_dim, dbar, low, s);
+  if (low_dtype == SA_F32) return dbar_by_dim<TDO, float, true>(out, d_out, rows, head_dim, dbar, low, s);
+  return SA_ERR_BAD_ARGUMENT;
+}
+
+// ---- fold + cast ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void __launch_bounds__(256) fold_cast_kernel(const float* __restrict__ acc, const float* __restrict__ acc0,
+                                                        T* __restrict__ dst, int heads, int64_t per_head,
+                                                        int64_t total4) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= total4) return;
+  int64_t e = idx * 4;
+  int64_t row = e / per_head;                 // (batch, head) row
+  int64_t within = e - row * per_head;
+  int b = (int)(row / heads), h = (int)(row - (int64_t)b * heads);
+  float4 a = *reinterpret_cast<const float4*>(acc + e);
+  if (h == 0 && acc0 != nullptr) {
+    float4 z = *reinterpret_cast<const float4*>(acc0 + (int64_t)b * per_head + within);
+    a.x += z.x; a.y += z.y; a.z += z.z; a.w += z.w;
+  }
+  dst[e + 0] = from_float<T>(a.x);
+  dst[e + 1] = from_float<T>(a.y);
+  dst[e + 2] = from_float<T>(a.z);
+  dst[e + 3] = from_float<T>(a.w);
+}
+
+// ---- decode -----------------------------------------------------------------------------------------
+constexpr int kDecThreads = 128;
+constexpr int kDecSplit = 512;                // keys per CTA
+
+template <typename T>
+__global__ void append_kernel(const T* __restrict__ k1, const T* __restrict__ v1, T* __restrict__ kc,
+                              T* __restrict__ vc, int rows, int capacity, int length, int D) {
+  int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= rows * D) return;
+  int n = idx / D, d = idx - n * D;
+  int64_t dst = ((int64_t)n * capacity + length) * D + d;
+  kc[dst] = k1[idx];
+  vc[dst] = v1[idx];
+}
+
+// grid (splits, batch * heads).  A group of D / 8 lanes owns one key per step.
+template <typename T, int D>
+__global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
+    const T* __restrict__ q1, const T* __restrict__ kc, const T* __restrict__ vc, const float* __restrict__ selected,
+    float* __restrict__ partial, float* __restrict__ sel_new, int heads, int groups, int t, int capacity,
+    int exempt, float scale) {
+  constexpr int kLanes = D / 8;                       // lanes per key
+  constexpr int kKeysPerStep = kDecThreads / kLanes;  // keys the CTA covers per step
+  __shared__ float zs[kDecSplit];
+  __shared__ float red[kDecThreads];
+  __shared__ float accs[kKeysPerStep][D];
+
+  const int n = blockIdx.y, split = blockIdx.x;
+  const int b = n / heads, h = n - b * heads;
+  const int per = heads / groups, g = h / per;
+  const bool selector = (h - g * per) == 0;
+  const int c0 = split * kDecSplit, c1 = min(t, c0 + kDecSplit);
+  const int grp = threadIdx.x / kLanes, lane = threadIdx.x % kLanes;
+
+  float qv[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) qv[e] = to_float<T>(q1[(int64_t)n * D + lane * 8 + e]);
+  const T* kb = kc + (int64_t)n * capacity * D;
+  const T* vb = vc + (int64_t)n * capacity * D;
+  const float* selb = selected + ((int64_t)b * groups + g) * capacity;
+  float* selnb = sel_new + ((int64_t)b * groups + g) * t;
+
+  float local_max = -INFINITY;
+  for (int base = c0; base < c1; base += kKeysPerStep) {   // uniform trip count: the shuffles need whole warps
+    const int j = base + grp;
+    const bool valid = j < c1;
+    float dot = 0.f;
+    if (valid) {
+      const T* kr = kb + (int64_t)j * D + lane * 8;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot = fmaf(qv[e], to_float<T>(kr[e]), dot);
+    }
+#pragma unroll
+    for (int s = kLanes / 2; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
+    if (valid) {
+      float raw = dot * scale;
+      float z = (raw - selb[j]) * kLog2e;
+      if (lane == 0) {
+        zs[j - c0] = z;
+        if (selector) selnb[j] = (j >= exempt && j != t - 1 && raw > 0.f) ? raw : 0.f;
+      }
+      local_max = fmaxf(local_max, z);
+    }
+  }
+  red[threadIdx.x] = local_max;
+  __syncthreads();
+  for (int s = kDecThreads / 2; s > 0; s >>= 1) {
+    if (threadIdx.x < s) red[threadIdx.x] = fmaxf(red[threadIdx.x], red[threadIdx.x + s]);
+    __syncthreads();
+  }
+  const float m = red[0];
+  __syncthreads();
+
+  float acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  float den = 0.f;
+  for (int j = c0 + grp; j < c1; j += kKeysPerStep) {
+    float e2 = exp2f(zs[j - c0] - m);
+    den += e2;
+    const T* vr = vb + (int64_t)j * D + lane * 8;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = fmaf(e2, to_float<T>(vr[e]), acc[e]);
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) accs[grp][lane * 8 + e] = acc[e];
+  red[threadIdx.x] = (lane == 0) ? den : 0.f;
+  __syncthreads();
+  for (int s = kDecThreads / 2; s > 0; s >>= 1) {
+    if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
+    __syncthreads();
+  }
+  float* prow = partial + ((int64_t)n * gridDim.x + split) * (D + 2);
+  for (int d = threadIdx.x; d < D; d += kDecThreads) {
+    float sum = 0.f;
+    for (int gg = 0; gg < kKeysPerStep; ++gg) sum += accs[gg][d];
+    prow[d] = sum;
+  }
+  if (threadIdx.x == 0) {
+    prow[D] = m;
+    prow[D + 1] = red[0];
+  }
+}
+
+// grid (batch * heads), D threads: merges the per-split partial softmaxes.
+__global__ void decode_combine_kernel(const float* __restrict__ partial, float* __restrict__ y, int splits, int D) {
+  const int n = blockIdx.x, d = threadIdx.x;
+  const float* prow = partial + (int64_t)n * splits * (D + 2);
+  float m = -INFINITY;
+  for (int s = 0; s < splits; ++s) m = fmaxf(m, prow[s * (D + 2) + D]);
+  float num = 0.f, den = 0.f;
+  for (int s = 0; s < splits; ++s) {
+    float w = exp2f(prow[s * (D + 2) + D] - m);
+    num = fmaf(w, prow[s * (D + 2) + d], num);
+    den = fmaf(w, prow[s * (D + 2) + D + 1], den);
+  }
+  y[(int64_t)n * D + d] = num / den;
+}
+
+__global__ void decode_update_kernel(float* __restrict__ selected, const float* __restrict__ sel_new, int rows, int t,
+                                     int capacity) {
+  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)rows * t) return;
+  int r = (int)(idx / t), j = (int)(idx - (int64_t)r * t);
+  selected[(int64_t)r * capacity + j] += sel_new[idx];
+}
+
+template <typename T>
+int decode_impl(int batch, int heads, int groups, int length, int capacity, int D, int exempt, const void* q1,
+                const void* k1, const void* v1, void* kc, void* vc, float* selected, float* y, float* ws,
+                cudaStream_t s) {
+  const int rows = batch * heads, t = length + 1;
+  const int splits = (t + kDecSplit - 1) / kDecSplit;
+  float* partial = ws;
+  float* sel_new = ws + (size_t)rows * splits * (D + 2);
+  append_kernel<T><<<(rows * D + 255) / 256, 256, 0, s>>>(static_cast<const T*>(k1), static_cast<const T*>(v1),
+                                                         static_cast<T*>(kc), static_cast<T*>(vc), rows, capacity,
+                                                         length, D);
+  SA_CUDA_CHECK(cudaGetLastError());
+  dim3 grid(splits, rows);
+  const float scale = 1.0f / sqrtf((float)D);
+  const T* q = static_cast<const T*>(q1);
+  const T* kk = static_cast<const T*>(kc);
+  const T* vv = static_cast<const T*>(vc);
+#define SA_DECODE_LAUNCH(DIM)                                                                                   \
+  decode_attend_kernel<T, DIM><<<grid, kDecThreads, 0, s>>>(q, kk, vv, selected, partial, sel_new, heads, groups, \
+                                                            t, capacity, exempt, scale)
+  switch (D) {
+    case 16: SA_DECODE_LAUNCH(16); break;
+    case 32: SA_DECODE_LAUNCH(32); break;
+    case 64: SA_DECODE_LAUNCH(64); break;
+    case 128: SA_DECODE_LAUNCH(128); break;
+    default: return SA_ERR_UNSUPPORTED;
+  }
+#undef SA_DECODE_LAUNCH
+  SA_CUDA_CHECK(cudaGetLastError());
+  decode_combine_kernel<<<rows, D, 0, s>>>(partial, y, splits, D);
+  SA_CUDA_CHECK(cudaGetLastError());
+  const int64_t upd = (int64_t)batch * groups * t;
+  decode_update_kernel<<<(unsigned)((upd + 255) / 256), 256, 0, s>>>(selected, sel_new, batch * groups, t, capacity);
+  SA_CUDA_CHECK(cudaGetLastError());
+  return SA_OK;
+}
+
+}  // namespace
+
+int launch_dbar(const float* out, const void* d_out, int d_out_dtype, int64_t rows, int head_dim, float* dbar,
+                void* d_out_lowp, int lowp_dtype, cudaStream_t s) {
+  switch (d_out_dtype) {
+    case SA_F32: return dbar_by_low<float>(out, d_out, rows, head_dim, dbar, d_out_lowp, lowp_dtype, s);
+    case SA_BF16: return dbar_by_low<__nv_bfloat16>(out, d_out, rows, head_dim, dbar, d_out_lowp, lowp_dtype, s);
+    case SA_F16: return dbar_by_low<__half>(out, d_out, rows, head_dim, dbar, d_out_lowp, lowp_dtype, s);
+  }
+  return SA_ERR_BAD_ARGUMENT;
+}
+
+int launch_fold_cast(const float* acc, const float* acc0, void* dst, int dtype, int batch, int heads,
+                     int64_t seq_times_dim, cudaStream_t s) {
+  const int64_t total4 = (int64_t)batch * heads * seq_times_dim / 4;
+  const unsigned blocks = (unsigned)((total4 + 255) / 256);
+  switch (dtype) {
+    case SA_F32:
+      fold_cast_kernel<float><<<blocks, 256, 0, s>>>(acc, acc0, static_cast<float*>(dst), heads, seq_times_dim, total4);
+      break;
+    case SA_BF16:
+      fold_cast_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(acc, acc0, static_cast<__nv_bfloat16*>(dst), heads,
+                                                             seq_times_dim, total4);
+      break;
+    case SA_F16:
+      fold_cast_kernel<__half><<<blocks, 256, 0, s>>>(acc, acc0, static_cast<__half*>(dst), heads, seq_times_dim,
+                                                      total4);
+      break;
+    default: return SA_ERR_BAD_ARGUMENT;
+  }
+  SA_CUDA_CHECK(cudaGetLastError());
+  return SA_OK;
+}
+
+size_t decode_workspace_floats(int batch, int heads, int groups, int length, int head_dim) {
+  const int t = length + 1;
+  const size_t splits = (size_t)(t + kDecSplit - 1) / kDecSplit;
+  return (size_t)batch * heads * splits * (head_dim + 2) + (size_t)batch * groups * t;
+}
+
+int decode_step(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim, int exempt,
+                const void* q1, const void* k1, const void* v1, void* kc, void* vc, float* selected, float* y,
+                float* ws, cudaStream_t s) {
+  switch (dtype) {
+    case SA_F32:
+      return decode_impl<float>(batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, kc, vc, selected,
+                                y, ws, s);
+    case SA_BF16:
+      return decode_impl<__nv_bfloat16>(batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, kc, vc,
+                                        selected, y, ws, s);
+    case SA_F16:
+      return decode_impl<__half>(batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, kc, vc, selected,
+                                 y, ws, s);
+  }
+  return SA_ERR_BAD_ARGUMENT;
+}
+
+}  // namespace sa

@@ -1,0 +1,86 @@
+"""ctypes binding of libselective_attention_b200.so (declarations: include/selective_attention_b200.h).
+
+There is no fallback: if the library is missing or a call returns a non-zero status, an exception is
+raised.  Build the library with ``python -m selective_attention_b200.build``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libselective_attention_b200.so")
+
+SA_OK = 0
+STATUS_NAMES = {1: "BAD_ARGUMENT", 2: "UNSUPPORTED", 3: "ALIGNMENT", 4: "WORKSPACE", 5: "CUDA", 6: "DEVICE_TIMEOUT",
+                7: "TOO_LARGE"}
+DTYPE_F32, DTYPE_BF16, DTYPE_F16 = 0, 1, 2
+ENGINE_SIMT, ENGINE_TCGEN05 = 0, 1
+DAMP_CODES = {"none": 0, "linear": 1, "sqrt": 2}
+
+# every symbol include/selective_attention_b200.h declares
+EXPORTS = ("sa_abi_version", "sa_status_string", "sa_last_cuda_error", "sa_engine_available", "sa_carry_rows", "sa_forward",
+           "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step")
+
+
+class Problem(ctypes.Structure):
+    _fields_ = [("struct_bytes", ctypes.c_int32), ("dtype", ctypes.c_int32), ("engine", ctypes.c_int32),
+                ("batch", ctypes.c_int32), ("heads", ctypes.c_int32), ("seq", ctypes.c_int32),
+                ("head_dim", ctypes.c_int32), ("exempt", ctypes.c_int32), ("damp", ctypes.c_int32),
+                ("train_len", ctypes.c_int32), ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3),
+                ("v_stride", ctypes.c_int64 * 3)]
+
+
+class LibraryError(RuntimeError):
+    def __init__(self, fn: str, status: int, detail: str):
+        super().__init__(f"{fn} failed: SA_ERR_{STATUS_NAMES.get(status, status)} ({detail})")
+        self.status = status
+
+
+_lib = None
+
+
+def available() -> bool:
+    return os.path.exists(LIB_PATH)
+
+
+def load() -> ctypes.CDLL:
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not available():
+        raise RuntimeError(f"{LIB_PATH} is missing: build it with `python -m selective_attention_b200.build` "
+                           "(there is no fallback path)")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i32, sz, f32p = ctypes.c_void_p, ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p
+    pp = ctypes.POINTER(Problem)
+    lib.sa_abi_version.restype = i32
+    lib.sa_status_string.restype = ctypes.c_char_p
+    lib.sa_status_string.argtypes = [i32]
+    lib.sa_last_cuda_error.restype = i32
+    lib.sa_engine_available.restype = i32
+    lib.sa_engine_available.argtypes = [i32]
+    lib.sa_carry_rows.restype = i32
+    lib.sa_carry_rows.argtypes = [i32]
+    lib.sa_forward.restype = i32
+    lib.sa_forward.argtypes = [pp, vp, vp, vp, f32p, f32p, f32p, f32p, vp]
+    lib.sa_backward_workspace_bytes.restype = sz
+    lib.sa_backward_workspace_bytes.argtypes = [pp]
+    lib.sa_backward.restype = i32
+    lib.sa_backward.argtypes = [pp, vp, vp, vp, f32p, f32p, f32p, vp, i32, vp, vp, vp, vp, sz, vp]
+    lib.sa_decode_workspace_bytes.restype = sz
+    lib.sa_decode_workspace_bytes.argtypes = [i32] * 5
+    lib.sa_decode_step.restype = i32
+    lib.sa_decode_step.argtypes = [i32] * 8 + [vp] * 8 + [sz, vp]
+    _lib = lib
+    return lib
+
+
+def check(fn: str, status: int) -> None:
+    if status != SA_OK:
+        lib = load()
+        detail = lib.sa_status_string(status).decode()
+        if status == 5:
+            detail += f", cudaError {lib.sa_last_cuda_error()}"
+        raise LibraryError(fn, status, detail)

@@ -1,0 +1,327 @@
+"""Selective Attention for B200: the reference's operator API over a C-ABI library of sm_100a kernels.
+
+The names, signatures, return types and error behaviour follow the reference module
+``src/selective_attention/kernels.py`` so that its callers (``mixers.py:86-98``, its kernel tests, its
+bench script) can import this module instead:
+
+    selective_attention(q, k, v, ...)            differentiable, fp32 output      (reference :669-703)
+    selective_attention_forward(q, k, v, ...)    forward only, optional aux dict  (reference :526-605)
+    selective_logits / selective_attention_reference   the dense paper listing    (reference :61-83)
+    check_inputs, supported, _check_exempt, HEAD_DIMS, DTYPES, CARRY_M, HAS_TRITON
+
+What differs underneath: the device work is done by ``libselective_attention_b200.so`` (CUDA-core fp32
+engine for "ieee"/"tf32", tcgen05 tensor-core engine for bf16), the launch-tuning keywords are
+validated but have no effect, the softmax statistics are kept as one log-sum-exp per row
+(``aux["rmax"]`` holds it, ``aux["rden"]`` is all ones, so ``exp2(z - rmax) / rden`` still rebuilds the
+attention), and ``aux["carry"]`` has a checkpoint every ``aux["carry_m"]`` query rows (32 or 128).
+There is no fallback: without the library every kernel entry raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+import os
+
+import torch
+from torch.autograd.function import once_differentiable
+
+from . import _lib
+
+HAS_KERNELS = _lib.available()
+HAS_TRITON = HAS_KERNELS          # the reference's tests and layer gate on this name
+HEAD_DIMS = (16, 32, 64, 128)
+DTYPES = (torch.float16, torch.bfloat16, torch.float32)
+CARRY_M = 32                      # checkpoint spacing of the CUDA-core engine; the tensor-core engine uses 128
+_BLOCK_QUANTUM = 32
+_DTYPE_CODE = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16}
+_TC_HEAD_DIMS = (64, 128)
+
+
+# ---- the paper listing (dense; the oracle the kernels are tested against, never a fallback) ---------
+
+def selective_logits(q: torch.Tensor, k: torch.Tensor, exempt: int = 1) -> tuple[torch.Tensor, torch.Tensor]:
+    """(L - F) as (B, H, T, T) fp32 with -inf above the diagonal, and the (B, T) selection totals."""
+    exempt = _check_exempt(exempt)
+    seq, dim = q.shape[-2], q.shape[-1]
+    raw = torch.matmul(q.float(), k.float().transpose(-2, -1)) * (1.0 / math.sqrt(dim))
+    idx = torch.arange(seq, device=q.device)
+    future = idx[None, :] > idx[:, None]
+    selectable = (idx[None, :] < idx[:, None]) & (idx[None, :] >= exempt)
+    sel = torch.relu(raw[:, 0]) * selectable
+    history = sel.cumsum(dim=-2) - sel
+    return raw.masked_fill(future, float("-inf")) - history[:, None], sel.sum(dim=-2)
+
+
+def selective_attention_reference(q, k, v, exempt: int = 1) -> torch.Tensor:
+    """softmax(L - F) @ v in fp32, (B, H, T, D)."""
+    return torch.matmul(torch.softmax(selective_logits(q, k, exempt)[0], dim=-1), v.float())
+
+
+# ---- argument contract --------------------------------------------------------------------------------
+
+def check_inputs(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> None:
+    """ValueError / RuntimeError unless the kernels can take these tensors."""
+    if not HAS_KERNELS:
+        raise RuntimeError("the CUDA library is not built (python -m selective_attention_b200.build)")
+    shapes = tuple(tuple(t.shape) for t in (q, k, v))
+    if q.dim() != 4 or shapes[0] != shapes[1] or shapes[0] != shapes[2]:
+        raise ValueError(f"q, k, v must all be (B, H, T, D); got {shapes[0]}, {shapes[1]}, {shapes[2]}")
+    if not q.is_cuda or k.device != q.device or v.device != q.device:
+        raise ValueError("q, k, v must be CUDA tensors on one device")
+    for t in (q, k, v):
+        if t.dtype not in DTYPES:
+            raise ValueError(f"dtype must be float16, bfloat16 or float32; got {q.dtype}, {k.dtype}, {v.dtype}")
+    if q.shape[3] not in HEAD_DIMS:
+        raise ValueError(f"head_dim must be one of {HEAD_DIMS}; got {q.shape[3]}")
+    if q.shape[2] < 1:
+        raise ValueError("the sequence is empty")
+
+
+def supported(q: torch.Tensor, k: torch.Tensor | None = None, v: torch.Tensor | None = None) -> bool:
+    try:
+        check_inputs(q, q if k is None else k, q if v is None else v)
+        return True
+    except (ValueError, RuntimeError):
+        return False
+
+
+def _check_exempt(exempt: int) -> int:
+    if int(exempt) != exempt or exempt < 1:
+        raise ValueError(f"exempt must be an integer >= 1 (position 0, <BOS>, is always exempt); got {exempt}")
+    return int(exempt)
+
+
+def _check_blocks(*blocks) -> None:
+    for b in blocks:
+        if b is not None and (int(b) != b or b < _BLOCK_QUANTUM or b % _BLOCK_QUANTUM):
+            raise ValueError(f"block_m and block_n must be multiples of {_BLOCK_QUANTUM}")
+
+
+def _check_bwd_group(group) -> None:
+    if group not in (None, 1, 2):
+        raise ValueError(f"bwd_group must be None, 1 or 2; got {group}")
+
+
+def _lowp(dot_precision: str | None, dtype: torch.dtype) -> bool:
+    """True: bf16 tensor-core operands.  None follows the dtype (bf16 -> "bf16", else "tf32")."""
+    if dot_precision is None:
+        dot_precision = "bf16" if dtype == torch.bfloat16 else "tf32"
+    if dot_precision == "bf16":
+        return True
+    if dot_precision in ("tf32", "ieee"):
+        return False       # both run as exact fp32 products here, which is inside the tf32 envelope
+    raise ValueError(f"dot_precision must be None, 'bf16', 'tf32' or 'ieee', not {dot_precision!r}")
+
+
+# ---- library plumbing ---------------------------------------------------------------------------------
+
+def _strided(t: torch.Tensor, tc: bool) -> torch.Tensor:
+    """The kernels take any batch/head/token strides with a contiguous last axis; the TMA path also
+    needs 16-byte aligned rows."""
+    ok = t.stride(3) == 1 or t.shape[3] == 1
+    if ok and tc:
+        es = t.element_size()
+        ok = t.data_ptr() % 16 == 0 and all((s * es) % 16 == 0 for s in t.stride()[:3])
+    return t if ok else t.contiguous()
+
+
+def _engine(lowp: bool, head_dim: int) -> int:
+    forced = os.environ.get("SA_B200_ENGINE", "")
+    if forced == "simt":
+        return _lib.ENGINE_SIMT
+    if lowp and head_dim in _TC_HEAD_DIMS and _lib.load().sa_engine_available(_lib.ENGINE_TCGEN05):
+        return _lib.ENGINE_TCGEN05
+    return _lib.ENGINE_SIMT
+
+
+def _problem(q, k, v, engine: int, exempt: int, damp: int = 0, train_len: int = 0) -> _lib.Problem:
+    b, h, t, d = q.shape
+    p = _lib.Problem()
+    p.struct_bytes = ctypes.sizeof(_lib.Problem)
+    p.dtype = _DTYPE_CODE[q.dtype]
+    p.engine = engine
+    p.batch, p.heads, p.seq, p.head_dim = b, h, t, d
+    p.exempt, p.damp, p.train_len = exempt, damp, max(int(train_len), 0)
+    for field, ten in (("q_stride", q), ("k_stride", k), ("v_stride", v)):
+        getattr(p, field)[:] = list(ten.stride()[:3])
+    return p
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _prepare(q, k, v, lowp: bool):
+    """Operand dtype of the engines: bf16 when the products run on bf16 operands, otherwise a common
+    input dtype (the CUDA-core engine converts every element to fp32 as it loads it)."""
+    if lowp:
+        want = torch.bfloat16
+    elif q.dtype == k.dtype == v.dtype:
+        want = q.dtype
+    else:
+        want = torch.float32
+    return tuple(t if t.dtype == want else t.to(want) for t in (q, k, v))
+
+
+def _forward(q, k, v, lowp: bool, exempt: int, damp: int, train_len: int):
+    lib = _lib.load()
+    b, h, t, d = q.shape
+    engine = _engine(lowp, d)
+    if damp and engine == _lib.ENGINE_TCGEN05:
+        engine = _lib.ENGINE_SIMT          # row-scaled F is an evaluation-only option of the CUDA-core engine
+    tc = engine == _lib.ENGINE_TCGEN05
+    q, k, v = (_strided(x, tc) for x in _prepare(q, k, v, lowp))
+    dev = q.device
+    carry_m = lib.sa_carry_rows(engine)
+    out = torch.empty(b, h, t, d, device=dev, dtype=torch.float32)
+    lse2 = torch.empty(b, h, t, device=dev, dtype=torch.float32)
+    carry = torch.empty(b, (t + carry_m - 1) // carry_m, t, device=dev, dtype=torch.float32)
+    total = torch.empty(b, t, device=dev, dtype=torch.float32)
+    prob = _problem(q, k, v, engine, exempt, damp, train_len)
+    with torch.cuda.device(dev):
+        st = lib.sa_forward(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                            lse2.data_ptr(), carry.data_ptr(), total.data_ptr(), _stream(dev))
+    _lib.check("sa_forward", st)
+    return out, lse2, carry, total, (q, k, v), engine, carry_m
+
+
+def selective_attention_forward(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    dot_precision: str | None = None,
+    block_m: int | None = None,
+    block_n: int = 32,
+    return_aux: bool = False,
+    num_warps: int = 4,
+    num_stages: int | None = None,
+    group: int | None = None,
+    exempt: int = 1,
+    *,
+    damp: str = "none",
+    train_len: int = 0,
+):
+    """Forward without autograd: fp32 (B, H, T, D).  With ``return_aux`` also a dict with ``rmax``
+    (the row log-sum-exp in log2 units), ``rden`` (ones), ``carry``, ``carry_m`` and
+    ``selected_total`` (B, T): the selection each key received from all T queries, i.e. the cached
+    decode accumulator after this prefix.  ``damp`` ("none" | "linear" | "sqrt") with ``train_len``
+    scales the history term of query i by min(1, train_len / (i + 1)) or its square root
+    (evaluation only; the backward does not implement it).  block_m / block_n / num_warps /
+    num_stages / group are accepted for signature compatibility and only validated."""
+    check_inputs(q, k, v)
+    exempt = _check_exempt(exempt)
+    lowp = _lowp(dot_precision, q.dtype)
+    _check_blocks(block_m, block_n)
+    if damp not in _lib.DAMP_CODES:
+        raise ValueError(f"damp must be 'none', 'linear' or 'sqrt'; got {damp!r}")
+    if _lib.DAMP_CODES[damp] and train_len < 1:
+        raise ValueError("damp needs train_len (the trained context length)")
+    out, lse2, carry, total, _, _, carry_m = _forward(q, k, v, lowp, exempt, _lib.DAMP_CODES[damp], train_len)
+    if not return_aux:
+        return out
+    b, h, t, _ = q.shape
+    aux = dict(rmax=lse2.view(b * h, t), rden=torch.ones(b * h, t, device=q.device, dtype=torch.float32),
+               carry=carry, carry_m=carry_m, selected_total=total)
+    return out, aux
+
+
+class _SelectiveAttentionFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, dot_precision, block_m, block_n, num_warps, bwd_block_n, bwd_num_warps,
+                bwd_num_stages, group, bwd_group, num_stages, exempt):
+        check_inputs(q, k, v)
+        exempt = _check_exempt(exempt)
+        lowp = _lowp(dot_precision, q.dtype)
+        _check_blocks(block_m, block_n)
+        out, lse2, carry, _, operands, engine, _ = _forward(q, k, v, lowp, exempt, 0, 0)
+        ctx.save_for_backward(*operands, out, lse2, carry)
+        ctx.engine, ctx.exempt, ctx.bwd_group = engine, exempt, bwd_group
+        ctx.grad_dtypes = (q.dtype, k.dtype, v.dtype)
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dout):
+        _check_bwd_group(ctx.bwd_group)
+        q, k, v, out, lse2, carry = ctx.saved_tensors
+        lib = _lib.load()
+        dev = q.device
+        if dout.dtype not in _DTYPE_CODE:
+            dout = dout.float()
+        dout = dout.contiguous()
+        prob = _problem(q, k, v, ctx.engine, ctx.exempt)
+        need = lib.sa_backward_workspace_bytes(ctypes.byref(prob))
+        workspace = torch.empty(max(need, 1), device=dev, dtype=torch.uint8)
+        dq, dk, dv = (torch.empty(q.shape, device=dev, dtype=q.dtype) for _ in range(3))
+        with torch.cuda.device(dev):
+            st = lib.sa_backward(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
+                                 lse2.data_ptr(), carry.data_ptr(), dout.data_ptr(), _DTYPE_CODE[dout.dtype],
+                                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), workspace.data_ptr(), need,
+                                 _stream(dev))
+        _lib.check("sa_backward", st)
+        grads = tuple(g if g.dtype == want else g.to(want) for g, want in zip((dq, dk, dv), ctx.grad_dtypes))
+        return grads + (None,) * 11
+
+
+def selective_attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    dot_precision: str | None = None,
+    block_m: int | None = None,
+    block_n: int = 32,
+    num_warps: int = 4,
+    bwd_block_n: int = 32,
+    bwd_num_warps: int = 4,
+    bwd_num_stages: int = 1,
+    group: int | None = None,
+    bwd_group: int | None = None,
+    num_stages: int | None = None,
+    exempt: int = 1,
+) -> torch.Tensor:
+    """Differentiable Selective Attention.  q / k / v: (B, H, T, D) CUDA tensors (fp16, bf16 or fp32;
+    D in 16, 32, 64, 128; any strides).  Returns fp32 (B, H, T, D); gradients come back in the input
+    dtypes.  dot_precision: None -> "bf16" for bf16 inputs, otherwise "tf32"; "ieee" and "tf32" both
+    run exact fp32 products.  exempt: keys [0, exempt) are never selected (1 = <BOS>, the paper's rule).
+    The remaining keywords are the reference's launch-tuning knobs: validated, otherwise unused."""
+    return _SelectiveAttentionFn.apply(q, k, v, dot_precision, block_m, block_n, num_warps, bwd_block_n,
+                                       bwd_num_warps, bwd_num_stages, group, bwd_group, num_stages, exempt)
+
+
+# ---- cached decode ------------------------------------------------------------------------------------
+
+def decode_step(cache: dict, q1: torch.Tensor, k1: torch.Tensor, v1: torch.Tensor, exempt: int = 1) -> torch.Tensor:
+    """One cached decode step on the device (the reference does this with PyTorch ops,
+    ``mixers.py:115-130`` and ``model.py:86-93``).
+
+    cache: {"k", "v": (B, H, capacity, D) contiguous, "len": int, "selected": (B, G, capacity) fp32}.
+    q1, k1, v1: (B, H, 1, D).  Appends k1 / v1 at ``len``, returns y (B, H, 1, D) fp32 and then adds the
+    new query's own selection to ``selected`` in place.  G selectors: heads in G contiguous runs, the
+    first head of a run selects."""
+    lib = _lib.load()
+    exempt = _check_exempt(exempt)
+    kc, vc, selected = cache["k"], cache["v"], cache["selected"]
+    b, h, cap, d = kc.shape
+    length = int(cache["len"])
+    if length >= cap:
+        raise ValueError("decode step past the cache capacity (context_length)")
+    if not (kc.is_cuda and kc.is_contiguous() and vc.is_contiguous() and selected.is_contiguous()):
+        raise ValueError("the cache must be contiguous CUDA tensors")
+    if kc.dtype not in _DTYPE_CODE or vc.dtype != kc.dtype or selected.dtype != torch.float32:
+        raise ValueError("cache dtype must be float16, bfloat16 or float32 with fp32 `selected`")
+    if d not in HEAD_DIMS:
+        raise ValueError(f"head_dim must be one of {HEAD_DIMS}; got {d}")
+    groups = selected.shape[1]
+    q1, k1, v1 = (t.reshape(b, h, d).to(kc.dtype).contiguous() for t in (q1, k1, v1))
+    dev = kc.device
+    y = torch.empty(b, h, 1, d, device=dev, dtype=torch.float32)
+    need = lib.sa_decode_workspace_bytes(b, h, groups, length, d)
+    ws = torch.empty(max(need, 1), device=dev, dtype=torch.uint8)
+    with torch.cuda.device(dev):
+        st = lib.sa_decode_step(_DTYPE_CODE[kc.dtype], b, h, groups, length, cap, d, exempt, q1.data_ptr(),
+                                k1.data_ptr(), v1.data_ptr(), kc.data_ptr(), vc.data_ptr(), selected.data_ptr(),
+                                y.data_ptr(), ws.data_ptr(), need, _stream(dev))
+    _lib.check("sa_decode_step", st)
+    cache["len"] = length + 1
+    return y
