@@ -122,6 +122,17 @@ int sa_decode_step(int dtype, int batch, int heads, int groups, int length, int 
                    void* k_cache, void* v_cache, float* selected, float* y,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* Reads (synchronously) the status word the bounded device-side waits of the tensor-core engine
+ * report into; 0 means no wait ever ran out on the current device.  clear != 0 resets it.
+ * No counterpart in the reference (Triton kernels have no such waits). */
+int sa_device_status(unsigned int* value_host, int clear);
+
+/* Known-answer test of the tcgen05 / TMA operand encodings the tensor-core engine uses.
+ *   scratch  32 KiB of device memory, 1024-byte aligned
+ *   result   8 floats: result[m] = largest absolute error of operand form m (0 when correct)
+ * No counterpart in the reference. */
+int sa_selftest_tcgen05(void* scratch, float* result, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

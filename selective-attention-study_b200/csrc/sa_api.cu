@@ -4,6 +4,7 @@
 #include <math.h>
 
 #include "sa_common.cuh"
+#include "sa_tc_host.cuh"
 
 namespace sa {
 
@@ -169,6 +170,17 @@ int sa_backward(const sa_problem* in, const void* q, const void* k, const void* 
   if (st != SA_OK) return st;
   // The tensor-core backward accumulates dk (with head 0's selection share) in fp32 in dk_acc as well.
   return SA_ERR_UNSUPPORTED;
+}
+
+int sa_device_status(unsigned int* value_host, int clear) {
+  if (!value_host) return SA_ERR_BAD_ARGUMENT;
+  return tc::read_status(value_host, clear != 0);
+}
+
+int sa_selftest_tcgen05(void* scratch, float* result, void* stream) {
+  if (!scratch || !result) return SA_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(scratch) & 1023) != 0) return SA_ERR_ALIGNMENT;
+  return tc::selftest(scratch, result, static_cast<cudaStream_t>(stream));
 }
 
 size_t sa_decode_workspace_bytes(int batch, int heads, int groups, int length, int head_dim) {

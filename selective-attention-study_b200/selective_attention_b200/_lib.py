@@ -21,7 +21,7 @@ DAMP_CODES = {"none": 0, "linear": 1, "sqrt": 2}
 
 # every symbol include/selective_attention_b200.h declares
 EXPORTS = ("sa_abi_version", "sa_status_string", "sa_last_cuda_error", "sa_engine_available", "sa_carry_rows", "sa_forward",
-           "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step")
+           "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step", "sa_device_status", "sa_selftest_tcgen05")
 
 
 class Problem(ctypes.Structure):
@@ -73,8 +73,19 @@ def load() -> ctypes.CDLL:
     lib.sa_decode_workspace_bytes.argtypes = [i32] * 5
     lib.sa_decode_step.restype = i32
     lib.sa_decode_step.argtypes = [i32] * 8 + [vp] * 8 + [sz, vp]
+    lib.sa_device_status.restype = i32
+    lib.sa_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint), i32]
+    lib.sa_selftest_tcgen05.restype = i32
+    lib.sa_selftest_tcgen05.argtypes = [vp, vp, vp]
     _lib = lib
     return lib
+
+
+def device_status(clear: bool = True) -> int:
+    """Status word of the tensor-core engine's bounded waits on the current device (0 = fine)."""
+    value = ctypes.c_uint(0)
+    check("sa_device_status", load().sa_device_status(ctypes.byref(value), int(clear)))
+    return value.value
 
 
 def check(fn: str, status: int) -> None:
