@@ -75,14 +75,20 @@ int sa_engine_available(int engine);
  * Replaces the module constant CARRY_M (src/selective_attention/kernels.py:86-87). */
 int sa_carry_rows(int engine);
 
+/* Rows of the carry buffer for a sequence length: ceil(seq / carry_rows), plus one row holding the
+ * totals for the tensor-core engine (its backward sweeps query tiles last to first and starts from
+ * the checkpoint AFTER the tile).  Replaces `nb` in selective_attention_forward
+ * (src/selective_attention/kernels.py:573-576). */
+int sa_carry_checkpoints(int engine, int seq);
+
 /* Forward.  Replaces the two launches of selective_attention_forward
  * (src/selective_attention/kernels.py:526-605: _selective_carry :111-138 and
  * _selective_forward / _selective_forward_grouped :140-194, :366-424).
  *   out    (batch, heads, seq, head_dim) fp32, contiguous
  *   lse2   (batch, heads, seq) fp32: log2 of the softmax denominator in the log2 domain of
  *          z = (L - F) * log2(e); equals the reference's rmax + log2(rden)
- *   carry  (batch, ceil(seq / carry_rows), seq) fp32 scratch AND saved state for the backward: row r
- *          holds, for every key, the selection received from queries < r * carry_rows
+ *   carry  (batch, sa_carry_checkpoints(engine, seq), seq) fp32 scratch AND saved state for the
+ *          backward: row r holds, for every key, the selection received from queries < r * carry_rows
  *   total  (batch, seq) fp32: selection received from all queries ("selected_total")
  * carry needs no initialisation. */
 int sa_forward(const sa_problem* p, const void* q, const void* k, const void* v,

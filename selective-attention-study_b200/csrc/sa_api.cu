@@ -102,6 +102,13 @@ int sa_carry_rows(int engine) {
   return 0;
 }
 
+int sa_carry_checkpoints(int engine, int seq) {
+  if (seq < 1) return 0;
+  if (engine == SA_ENGINE_SIMT) return (seq + kSimtCarryRows - 1) / kSimtCarryRows;
+  if (engine == SA_ENGINE_TCGEN05) return (seq + kTcCarryRows - 1) / kTcCarryRows + 1;   // + the grand total
+  return 0;
+}
+
 int sa_forward(const sa_problem* in, const void* q, const void* k, const void* v, float* out, float* lse2,
                float* carry, float* total, void* stream) {
   Problem p;

@@ -1,0 +1,461 @@
+// Tensor-core engine, forward side (sm_100a: TMA loads, tcgen05 MMAs, fp32 accumulators in TMEM).
+//
+//   colsum_kernel   selection pass: for one 128-key tile and a run of 128-query tiles, the product
+//                   K0 Q0^T with KEYS on the TMEM lanes, so a thread owns one key and the column sum of
+//                   relu'd, masked logits over the tile's queries is a register reduction.  Writes
+//                   COLSUM[b][query tile][key].
+//   scan_kernel     exclusive prefix of COLSUM across query tiles, in place (-> CARRY), plus one extra
+//                   row holding the grand total.  One thread per key column; bandwidth-bound.
+//   forward_kernel  flash-style forward for one 128-query tile of one head over 64-key tiles:
+//                   S = Q K^T and L0 = Q0 K0^T by MMA; relu(L0) under the selection mask is written to
+//                   shared memory as bf16 and the in-tile exclusive running sum over queries is one more
+//                   MMA, (-strictly-lower-triangular ones) x selection, accumulated into S; then online
+//                   softmax in the log2 domain with the cross-tile carry subtracted per key, P V by MMA.
+//
+// Reference for the arithmetic: src/selective_attention/kernels.py:100-194 (selection, carry, forward).
+#include "sa_tc_host.cuh"
+#include "sa_tc_ptx.cuh"
+
+namespace sa {
+namespace tc {
+namespace {
+
+constexpr int kTile = 128;          // query rows per CTA; also the carry checkpoint spacing
+constexpr int kKeys = 64;           // keys per forward step
+constexpr int kRowTile = 16384;     // bytes of a [128][64] bf16 operand tile
+constexpr int kKeyTile = 8192;      // bytes of a [64][64] bf16 operand tile
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// selection column sums
+// ---------------------------------------------------------------------------------------------------
+constexpr int kColsumChunk = 8;     // query tiles per CTA
+
+template <int D>
+__global__ void __launch_bounds__(128) colsum_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                     const __grid_constant__ CUtensorMap map_k, float* __restrict__ carry,
+                                                     int seq, int ntiles, int exempt, float scale,
+                                                     unsigned int* status) {
+  constexpr int DK = D / 64;
+  const int nj = blockIdx.x, b = blockIdx.z;
+  const int mi0 = nj + blockIdx.y * kColsumChunk;
+  if (mi0 >= ntiles) return;
+  const int count = min(kColsumChunk, ntiles - mi0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint8_t* k0s = smem;                               // DK tiles [128 keys][64]
+  uint8_t* q0s = smem + DK * kRowTile;               // 2 stages x DK tiles [128 queries][64]
+  __shared__ uint64_t bar_k, bar_q[2], bar_mma[2];
+  __shared__ uint32_t tmem_base_s;
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(&bar_k, 1);
+    mbar_init(&bar_q[0], 1);
+    mbar_init(&bar_q[1], 1);
+    mbar_init(&bar_mma[0], 1);
+    mbar_init(&bar_mma[1], 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&tmem_base_s, 256);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t idesc = instr_desc_bf16(128, 128, false, false);
+  const uint32_t k0a = smem_u32(k0s), q0a = smem_u32(q0s);
+
+  auto load_q = [&](int it) {
+    uint64_t* bar = &bar_q[it & 1];
+    mbar_expect_tx(bar, DK * kRowTile);
+    for (int s = 0; s < DK; ++s)
+      tma_load_4d(q0s + ((it & 1) * DK + s) * kRowTile, &map_q, bar, s * 64, (mi0 + it) * kTile, 0, b);
+  };
+  auto issue = [&](int it) {
+    mbar_wait(&bar_q[it & 1], (it >> 1) & 1, status, 200);
+    tc_fence_after_sync();
+    for (int ks = 0; ks < 4 * DK; ++ks)
+      mma_ss(tmem + (it & 1) * 128, smem_desc(k0a + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+             smem_desc(q0a + ((it & 1) * DK + (ks >> 2)) * kRowTile + (ks & 3) * 32, 16, 1024), idesc, ks > 0);
+    mma_commit(&bar_mma[it & 1]);
+  };
+
+  if (tid == 0) {
+    mbar_expect_tx(&bar_k, DK * kRowTile);
+    for (int s = 0; s < DK; ++s) tma_load_4d(k0s + s * kRowTile, &map_k, &bar_k, s * 64, nj * kTile, 0, b);
+    load_q(0);
+    if (count > 1) load_q(1);
+    mbar_wait(&bar_k, 0, status, 201);
+    issue(0);
+  }
+  const int j = nj * kTile + tid;
+  for (int it = 0; it < count; ++it) {
+    if (tid == 0 && it + 1 < count) issue(it + 1);
+    mbar_wait(&bar_mma[it & 1], (it >> 1) & 1, status, 202);
+    tc_fence_after_sync();
+    if (tid == 0 && it + 2 < count) load_q(it + 2);     // stage (it & 1) is free: its MMA has completed
+    const int mi = mi0 + it;
+    const int i0 = mi * kTile;
+    const bool diag = (mi == nj);
+    float sum = 0.f;
+#pragma unroll
+    for (int c0 = 0; c0 < 128; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(lane_base + (it & 1) * 128 + c0, r);
+      tmem_ld_wait();
+      if (diag) {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) sum += (j < i0 + c0 + e) ? fmaxf(__uint_as_float(r[e]), 0.f) : 0.f;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) sum += fmaxf(__uint_as_float(r[e]), 0.f);
+      }
+    }
+    if (j < exempt) sum = 0.f;
+    if (j < seq) carry[((int64_t)b * (ntiles + 1) + mi) * seq + j] = sum * scale;
+    tc_fence_before_sync();
+    __syncthreads();
+  }
+  if (warp == 0) tmem_dealloc(tmem, 256);
+}
+
+// One thread per key column: CARRY[b][mi][j] = sum of COLSUM[b][m'][j] over m' < mi, in place; row `ntiles`
+// and total[b][j] receive the sum over all query tiles.  Only rows mi >= j / 128 exist.
+__global__ void __launch_bounds__(256) scan_kernel(float* __restrict__ carry, float* __restrict__ total, int seq,
+                                                   int ntiles) {
+  const int j = blockIdx.x * blockDim.x + threadIdx.x;
+  const int b = blockIdx.y;
+  if (j >= seq) return;
+  float* col = carry + (int64_t)b * (ntiles + 1) * seq + j;
+  float run = 0.f;
+  int mi = j / kTile;
+  for (; mi + 8 <= ntiles; mi += 8) {
+    float x[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) x[u] = col[(int64_t)(mi + u) * seq];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      col[(int64_t)(mi + u) * seq] = run;
+      run += x[u];
+    }
+  }
+  for (; mi < ntiles; ++mi) {
+    float x = col[(int64_t)mi * seq];
+    col[(int64_t)mi * seq] = run;
+    run += x;
+  }
+  col[(int64_t)ntiles * seq] = run;
+  total[(int64_t)b * seq + j] = run;
+}
+
+// ---------------------------------------------------------------------------------------------------
+// forward
+// ---------------------------------------------------------------------------------------------------
+template <int D>
+struct FwdSmem {
+  static constexpr int DK = D / 64;
+  static constexpr int q = 0;
+  static constexpr int q0 = q + DK * kRowTile;
+  static constexpr int tri = q0 + DK * kRowTile;      // [128][128] as two column tiles
+  static constexpr int selp = tri + 2 * kRowTile;     // [128][64]: selection (B operand), then P (A operand)
+  static constexpr int k = selp + kRowTile;           // DK tiles [64][64]
+  static constexpr int k0 = k + DK * kKeyTile;
+  static constexpr int v = k0 + DK * kKeyTile;        // DK tiles [64 keys][64]
+  static constexpr int total = v + DK * kKeyTile;
+};
+
+template <int D>
+__global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                      const __grid_constant__ CUtensorMap map_k,
+                                                      const __grid_constant__ CUtensorMap map_v,
+                                                      const float* __restrict__ carry, float* __restrict__ out,
+                                                      float* __restrict__ lse2, int heads, int seq, int ntiles,
+                                                      int exempt, float scale, unsigned int* status) {
+  using L = FwdSmem<D>;
+  constexpr int DK = D / 64;
+  constexpr uint32_t kTmemCols = (D == 64) ? 128 : 256;
+  constexpr uint32_t kColS = 0, kColL = 64, kColPV = (D == 64) ? 64 : 128;
+
+  const int nrows = gridDim.x / ntiles;                       // batch * heads
+  const int mi = ntiles - 1 - (int)(blockIdx.x / nrows);      // heaviest query tiles first
+  const int n = blockIdx.x % nrows;
+  const int b = n / heads, h = n - b * heads;
+  const int i0 = mi * kTile;
+  const int steps = min(i0 + kTile, seq) / kKeys + ((min(i0 + kTile, seq) % kKeys) ? 1 : 0);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  __shared__ uint64_t bar_q, bar_k, bar_v, bar_mma;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ float carry_s[2][kKeys];
+
+  const int tid = threadIdx.x, warp = tid >> 5;
+  if (tid == 0) {
+    mbar_init(&bar_q, 1);
+    mbar_init(&bar_k, 1);
+    mbar_init(&bar_v, 1);
+    mbar_init(&bar_mma, 1);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&tmem_base_s, kTmemCols);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t sa = smem_u32(smem);
+
+  auto load_k = [&](int t) {
+    mbar_expect_tx(&bar_k, 2 * DK * kKeyTile);
+    for (int s = 0; s < DK; ++s) {
+      tma_load_4d(smem + L::k + s * kKeyTile, &map_k, &bar_k, s * 64, t * kKeys, h, b);
+      tma_load_4d(smem + L::k0 + s * kKeyTile, &map_k, &bar_k, s * 64, t * kKeys, 0, b);
+    }
+  };
+  auto load_v = [&](int t) {
+    mbar_expect_tx(&bar_v, DK * kKeyTile);
+    for (int s = 0; s < DK; ++s) tma_load_4d(smem + L::v + s * kKeyTile, &map_v, &bar_v, s * 64, t * kKeys, h, b);
+  };
+  if (tid == 0) {
+    mbar_expect_tx(&bar_q, 2 * DK * kRowTile);
+    for (int s = 0; s < DK; ++s) {
+      tma_load_4d(smem + L::q + s * kRowTile, &map_q, &bar_q, s * 64, i0, h, b);
+      tma_load_4d(smem + L::q0 + s * kRowTile, &map_q, &bar_q, s * 64, i0, 0, b);
+    }
+    load_k(0);
+    load_v(0);
+  }
+  // strictly-lower-triangular ones: TRI[i][r] = 1 for r < i (row i written by thread i)
+  {
+    const int i = tid;
+#pragma unroll
+    for (int c = 0; c < 16; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int p = 0; p < 4; ++p) {
+        int r = c * 8 + p * 2;
+        w[p] = pack_bf16(r < i ? 1.f : 0.f, (r + 1) < i ? 1.f : 0.f);
+      }
+      *reinterpret_cast<uint4*>(smem + L::tri + (c >> 3) * kRowTile + swz_off(i, c & 7)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  fence_async_smem();
+  __syncthreads();
+
+  const uint32_t idesc_s = instr_desc_bf16(128, kKeys, false, false);
+  const uint32_t idesc_tri = instr_desc_bf16(128, kKeys, false, true, /*negate_a=*/true);
+  const uint32_t idesc_pv = instr_desc_bf16(128, D, false, true);
+  const float c1 = scale * kLog2e;
+  const float* carry_row = carry + ((int64_t)b * (ntiles + 1) + mi) * seq;
+
+  const int i = i0 + tid;
+  float run_max = -INFINITY, run_den = 0.f;
+  float acc[D];
+#pragma unroll
+  for (int d = 0; d < D; ++d) acc[d] = 0.f;
+  uint32_t mma_phase = 0;
+
+  if (tid == 0) mbar_wait(&bar_q, 0, status, 300);
+
+  for (int t = 0; t < steps; ++t) {
+    const int j0 = t * kKeys;
+    // ---- A: S = Q K^T, L0 = Q0 K0^T ------------------------------------------------------------------
+    if (tid == 0) {
+      mbar_wait(&bar_k, t & 1, status, 301);
+      tc_fence_after_sync();
+      for (int ks = 0; ks < 4 * DK; ++ks)
+        mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+               smem_desc(sa + L::k + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
+      for (int ks = 0; ks < 4 * DK; ++ks)
+        mma_ss(tmem + kColL, smem_desc(sa + L::q0 + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+               smem_desc(sa + L::k0 + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
+      mma_commit(&bar_mma);
+    }
+    if (tid < kKeys) {
+      const int j = j0 + tid;
+      carry_s[t & 1][tid] = (j < seq) ? carry_row[j] * kLog2e : 0.f;
+    }
+    mbar_wait(&bar_mma, mma_phase, status, 302);
+    mma_phase ^= 1;
+    tc_fence_after_sync();
+    if (tid == 0 && t + 1 < steps) load_k(t + 1);     // K and K0 tiles are free once both products are done
+
+    // ---- B: selection tile relu(L0) under the mask -> bf16, row = query ----------------------------------
+    {
+      const bool masked = (j0 + kKeys > i0) || (j0 < exempt);
+#pragma unroll
+      for (int c0 = 0; c0 < kKeys; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(lane_base + kColL + c0, r);
+        tmem_ld_wait();
+        float s[32];
+        if (masked) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int j = j0 + c0 + e;
+            s[e] = (j < i && j >= exempt) ? fmaxf(__uint_as_float(r[e]), 0.f) : 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) s[e] = fmaxf(__uint_as_float(r[e]), 0.f);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 w = make_uint4(pack_bf16(s[c * 8 + 0], s[c * 8 + 1]), pack_bf16(s[c * 8 + 2], s[c * 8 + 3]),
+                               pack_bf16(s[c * 8 + 4], s[c * 8 + 5]), pack_bf16(s[c * 8 + 6], s[c * 8 + 7]));
+          *reinterpret_cast<uint4*>(smem + L::selp + swz_off(tid, (c0 >> 3) + c)) = w;
+        }
+      }
+    }
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+
+    // ---- C: S -= TRI x selection (exclusive running sum over the tile's queries) --------------------------
+    if (tid == 0) {
+      tc_fence_after_sync();
+      for (int ks = 0; ks < 8; ++ks)
+        mma_ss(tmem + kColS, smem_desc(sa + L::tri + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+               smem_desc(sa + L::selp + ks * 2048, kRowTile, 1024), idesc_tri, 1);
+      mma_commit(&bar_mma);
+    }
+    mbar_wait(&bar_mma, mma_phase, status, 303);
+    mma_phase ^= 1;
+    tc_fence_after_sync();
+
+    // ---- D: online softmax of z = (S * scale - carry) * log2(e) -----------------------------------------------
+    const bool diag = (j0 + kKeys - 1 > i0);
+    const float* cs = carry_s[t & 1];
+    float tile_max = -INFINITY;
+#pragma unroll
+    for (int c0 = 0; c0 < kKeys; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(lane_base + kColS + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        float z = fmaf(__uint_as_float(r[e]), c1, -cs[c0 + e]);
+        if (diag && (j0 + c0 + e > i)) z = -INFINITY;
+        tile_max = fmaxf(tile_max, z);
+      }
+    }
+    const float new_max = fmaxf(run_max, tile_max);
+    const float alpha = ex2(run_max - new_max);
+    float rowsum = 0.f;
+#pragma unroll
+    for (int c0 = 0; c0 < kKeys; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(lane_base + kColS + c0, r);
+      tmem_ld_wait();
+      float p[32];
+#pragma unroll
+      for (int e = 0; e < 32; ++e) {
+        float z = fmaf(__uint_as_float(r[e]), c1, -cs[c0 + e]);
+        if (diag && (j0 + c0 + e > i)) z = -INFINITY;
+        p[e] = ex2(z - new_max);
+        rowsum += p[e];
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint4 w = make_uint4(pack_bf16(p[c * 8 + 0], p[c * 8 + 1]), pack_bf16(p[c * 8 + 2], p[c * 8 + 3]),
+                             pack_bf16(p[c * 8 + 4], p[c * 8 + 5]), pack_bf16(p[c * 8 + 6], p[c * 8 + 7]));
+        *reinterpret_cast<uint4*>(smem + L::selp + swz_off(tid, (c0 >> 3) + c)) = w;
+      }
+    }
+    run_den = run_den * alpha + rowsum;
+    run_max = new_max;
+#pragma unroll
+    for (int d = 0; d < D; ++d) acc[d] *= alpha;
+    fence_async_smem();
+    tc_fence_before_sync();
+    __syncthreads();
+
+    // ---- E: P V ---------------------------------------------------------------------------------------------
+    if (tid == 0) {
+      mbar_wait(&bar_v, t & 1, status, 304);
+      tc_fence_after_sync();
+      for (int ks = 0; ks < 4; ++ks)
+        mma_ss(tmem + kColPV, smem_desc(sa + L::selp + ks * 32, 16, 1024),
+               smem_desc(sa + L::v + ks * 2048, kKeyTile, 1024), idesc_pv, ks > 0);
+      mma_commit(&bar_mma);
+    }
+    mbar_wait(&bar_mma, mma_phase, status, 305);
+    mma_phase ^= 1;
+    tc_fence_after_sync();
+    if (tid == 0 && t + 1 < steps) load_v(t + 1);
+#pragma unroll
+    for (int c0 = 0; c0 < D; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(lane_base + kColPV + c0, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int e = 0; e < 32; ++e) acc[c0 + e] += __uint_as_float(r[e]);
+    }
+    tc_fence_before_sync();
+    __syncthreads();
+  }
+
+  if (i < seq) {
+    const float inv = 1.f / run_den;
+    float4* orow = reinterpret_cast<float4*>(out + ((int64_t)n * seq + i) * D);
+#pragma unroll
+    for (int d = 0; d < D; d += 4) orow[d >> 2] = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
+    lse2[(int64_t)n * seq + i] = run_max + log2f(run_den);
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+}
+
+template <int D>
+int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float* total, cudaStream_t s) {
+  const int ntiles = (p.seq + kTile - 1) / kTile;
+  CUtensorMap map_q, map_k, map_k128, map_v;
+  int st = make_map_16bit(&map_q, p.q.ptr, D, p.seq, p.heads, p.batch, p.q.st, p.q.sh, p.q.sb, kTile);
+  if (st != SA_OK) return st;
+  st = make_map_16bit(&map_k, p.k.ptr, D, p.seq, p.heads, p.batch, p.k.st, p.k.sh, p.k.sb, kKeys);
+  if (st != SA_OK) return st;
+  st = make_map_16bit(&map_k128, p.k.ptr, D, p.seq, p.heads, p.batch, p.k.st, p.k.sh, p.k.sb, kTile);
+  if (st != SA_OK) return st;
+  st = make_map_16bit(&map_v, p.v.ptr, D, p.seq, p.heads, p.batch, p.v.st, p.v.sh, p.v.sb, kKeys);
+  if (st != SA_OK) return st;
+  unsigned int* status = nullptr;
+  st = status_word(&status);
+  if (st != SA_OK) return st;
+
+  constexpr int DK = D / 64;
+  const int colsum_smem = 3 * DK * kRowTile + 1024;
+  SA_CUDA_CHECK(cudaFuncSetAttribute(colsum_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, colsum_smem));
+  dim3 gc(ntiles, (ntiles + kColsumChunk - 1) / kColsumChunk, p.batch);
+  colsum_kernel<D><<<gc, 128, colsum_smem, s>>>(map_q, map_k128, carry, p.seq, ntiles, p.exempt, p.scale, status);
+  SA_CUDA_CHECK(cudaGetLastError());
+  dim3 gs((p.seq + 255) / 256, p.batch);
+  scan_kernel<<<gs, 256, 0, s>>>(carry, total, p.seq, ntiles);
+  SA_CUDA_CHECK(cudaGetLastError());
+
+  const int fwd_smem = FwdSmem<D>::total + 1024;
+  SA_CUDA_CHECK(cudaFuncSetAttribute(forward_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem));
+  const unsigned grid = (unsigned)ntiles * p.batch * p.heads;
+  forward_kernel<D><<<grid, 128, fwd_smem, s>>>(map_q, map_k, map_v, carry, out, lse2, p.heads, p.seq, ntiles,
+                                                p.exempt, p.scale, status);
+  SA_CUDA_CHECK(cudaGetLastError());
+  return SA_OK;
+}
+
+}  // namespace
+
+int forward(const Problem& p, float* out, float* lse2, float* carry, float* total, cudaStream_t s) {
+  if (p.head_dim == 64) return forward_impl<64>(p, out, lse2, carry, total, s);
+  if (p.head_dim == 128) return forward_impl<128>(p, out, lse2, carry, total, s);
+  return SA_ERR_UNSUPPORTED;
+}
+
+}  // namespace tc
+}  // namespace sa

@@ -15,7 +15,7 @@ namespace tc {
 // ---- device status word -----------------------------------------------------------------------------
 // Kernels receive a pointer to one status word per device (status_word() on the host).  0 = fine;
 // otherwise (site << 8) | 1 of the first bounded wait that ran out.  sa_device_status() reads it.
-constexpr long long kWaitLimitCycles = 4000000000LL;   // ~2 s at 2 GHz; an honest wait is microseconds
+constexpr long long kWaitLimitCycles = 400000000LL;   // ~0.2 s at 2 GHz; an honest wait is microseconds
 
 __device__ __forceinline__ void report(unsigned int* status, unsigned int site) {
   atomicCAS(status, 0u, (site << 8) | 1u);
@@ -49,15 +49,20 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
-// Waits for the phase with the given parity to complete; gives up after kWaitLimitCycles.
+// Waits for the phase with the given parity to complete.  Gives up after kWaitLimitCycles, or at once
+// when another wait has already given up (the status word is set), so a broken kernel ends quickly.
+// Callable by a single thread of a warp: it contains no warp-wide operation.
 __device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int site) {
   if (mbar_try_wait(bar, parity)) return;
   const long long start = clock64();
   int spins = 0;
   while (!mbar_try_wait(bar, parity)) {
-    if ((++spins & 63) == 0 && clock64() - start > kWaitLimitCycles) {
-      report(status, site);
-      return;
+    if ((++spins & 63) == 0) {
+      if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
+      if (clock64() - start > kWaitLimitCycles) {
+        report(status, site);
+        return;
+      }
     }
   }
 }
@@ -83,16 +88,19 @@ __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
 // ---- tensor memory ----------------------------------------------------------------------------------------
 // One full warp allocates `cols` (power of two, 32..512) columns; the base address lands in *dst_smem.
 __device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
+  __syncwarp();
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols)
                : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
 }
 __device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
+  __syncwarp();
   asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
 }
 
 // 32 lanes x 32 consecutive 32-bit columns -> 32 registers (lane = this thread's TMEM lane).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+  __syncwarp();   // warp-wide instruction: reconverge after per-thread spin waits
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
       "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -106,6 +114,7 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  __syncwarp();
   asm volatile(
       "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
       "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "

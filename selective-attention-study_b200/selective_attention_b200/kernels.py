@@ -176,7 +176,7 @@ def _forward(q, k, v, lowp: bool, exempt: int, damp: int, train_len: int):
     carry_m = lib.sa_carry_rows(engine)
     out = torch.empty(b, h, t, d, device=dev, dtype=torch.float32)
     lse2 = torch.empty(b, h, t, device=dev, dtype=torch.float32)
-    carry = torch.empty(b, (t + carry_m - 1) // carry_m, t, device=dev, dtype=torch.float32)
+    carry = torch.empty(b, lib.sa_carry_checkpoints(engine, t), t, device=dev, dtype=torch.float32)
     total = torch.empty(b, t, device=dev, dtype=torch.float32)
     prob = _problem(q, k, v, engine, exempt, damp, train_len)
     with torch.cuda.device(dev):
@@ -222,7 +222,7 @@ def selective_attention_forward(
         return out
     b, h, t, _ = q.shape
     aux = dict(rmax=lse2.view(b * h, t), rden=torch.ones(b * h, t, device=q.device, dtype=torch.float32),
-               carry=carry, carry_m=carry_m, selected_total=total)
+               carry=carry[:, :(t + carry_m - 1) // carry_m], carry_m=carry_m, selected_total=total)
     return out, aux
 
 

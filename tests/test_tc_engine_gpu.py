@@ -1,0 +1,65 @@
+"""Tensor-core (tcgen05) engine against the CPU oracle on bf16-rounded inputs.
+
+Tolerances: the bf16 bar is 2e-2 (relative norm) on outputs and gradients; the selection totals and the
+carry come from fp32 accumulators of bf16 products and are held to 1e-3."""
+
+import pytest
+import torch
+
+import selective_oracle as oracle
+from selective_attention_b200 import _lib, kernels
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(batch, heads, seq, dim, seed, scale=1.0, n=4):
+    g = torch.Generator("cpu").manual_seed(seed)
+    return tuple((scale * torch.randn(batch, heads, seq, dim, generator=g)).bfloat16() for _ in range(n))
+
+
+def _rel(got, want):
+    return float((got.float() - want).norm() / want.norm().clamp_min(1e-30))
+
+
+@pytest.mark.parametrize("seq", [1, 2, 63, 64, 65, 128, 129, 300, 1000, 2049])
+@pytest.mark.parametrize("dim,scale", [(64, 1.0), (64, 0.3), (128, 0.5)])
+def test_forward_matches_oracle(seq, dim, scale):
+    heads = 3
+    q, k, v, _ = _inputs(2, heads, seq, dim, seed=seq + dim, scale=scale)
+    out, aux = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda(), return_aux=True)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert aux["carry_m"] == 128
+    want = oracle.attention(q.float(), k.float(), v.float())
+    assert _rel(out.cpu(), want) < 2e-2, _rel(out.cpu(), want)
+    assert (out.cpu() - want).abs().max() < 3e-2
+    total = oracle.selected_total(q.float(), k.float())[:, 0]
+    torch.testing.assert_close(aux["selected_total"].cpu(), total, atol=1e-3, rtol=1e-3)
+    # carry row r = selection received from queries < 128 r
+    sel = oracle.selection_matrix(q[:, 0].float(), k[:, 0].float())
+    for r in range(aux["carry"].shape[1]):
+        want_row = sel[:, : 128 * r].sum(dim=1)
+        got_row = aux["carry"][:, r].cpu()
+        valid = torch.arange(seq) < 128 * (r + 1)          # keys past the tile are never read
+        torch.testing.assert_close(got_row[:, valid], want_row[:, valid], atol=1e-3, rtol=1e-3)
+
+
+@pytest.mark.parametrize("exempt", [3, 16, 70, 200])
+def test_forward_exempt_prefix(exempt):
+    q, k, v, _ = _inputs(1, 2, 333, 64, seed=exempt)
+    out, aux = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda(), return_aux=True, exempt=exempt)
+    want = oracle.attention(q.float(), k.float(), v.float(), exempt=exempt)
+    assert _rel(out.cpu(), want) < 2e-2
+    torch.testing.assert_close(aux["selected_total"].cpu(), oracle.selected_total(q.float(), k.float(), exempt)[:, 0],
+                               atol=1e-3, rtol=1e-3)
+
+
+def test_forward_takes_strided_views_without_a_copy():
+    b, h, t, d = 2, 4, 260, 64
+    g = torch.Generator("cpu").manual_seed(5)
+    packed = torch.randn(b, t, 3, h, d, generator=g).bfloat16().cuda()       # fused QKV projection layout
+    q, k, v = (packed[:, :, i].transpose(1, 2) for i in range(3))
+    assert not q.is_contiguous()
+    out = kernels.selective_attention_forward(q, k, v)
+    want = oracle.attention(q.float().cpu(), k.float().cpu(), v.float().cpu())
+    assert _rel(out.cpu(), want) < 2e-2
