@@ -71,6 +71,9 @@ int sa_last_cuda_error(void);              /* cudaError_t of the most recent SA_
 /* 1 when the engine is compiled into this build of the library, else 0. */
 int sa_engine_available(int engine);
 
+/* 1 when the engine runs this element type and head_dim (forward only, or forward and backward). */
+int sa_engine_supports(int engine, int dtype, int head_dim, int with_backward);
+
 /* Query rows between two checkpoints of the running selection sum for an engine (32 or 128).
  * Replaces the module constant CARRY_M (src/selective_attention/kernels.py:86-87). */
 int sa_carry_rows(int engine);

@@ -54,8 +54,7 @@ BackwardWorkspace carve(const sa_problem* in) {
   BackwardWorkspace w{};
   size_t off = 0;
   w.dq_acc = off; off = align_up(off + elems * 4, 256);
-  w.dk_acc = off;
-  if (in->engine == SA_ENGINE_SIMT) off = align_up(off + elems * 4, 256);   // tensor-core engine stores dk directly
+  w.dk_acc = off; off = align_up(off + elems * 4, 256);
   w.dq0 = off; off = align_up(off + elems0 * 4, 256);
   w.dk0 = off; off = align_up(off + elems0 * 4, 256);
   w.dbar = off; off = align_up(off + rows * 4, 256);
@@ -94,6 +93,17 @@ int sa_engine_available(int engine) {
   if (engine == SA_ENGINE_SIMT) return 1;
   if (engine == SA_ENGINE_TCGEN05) return tc_available();
   return 0;
+}
+
+int sa_engine_supports(int engine, int dtype, int head_dim, int with_backward) {
+  if (!dtype_ok(dtype) || !dim_ok(head_dim)) return 0;
+  if (engine == SA_ENGINE_SIMT) return 1;
+  if (engine != SA_ENGINE_TCGEN05 || !tc_available()) return 0;
+  Problem p{};
+  p.dtype = dtype;
+  p.head_dim = head_dim;
+  p.damp = SA_DAMP_NONE;
+  return (with_backward ? tc_backward_supported(p) : tc_supported(p)) == SA_OK;
 }
 
 int sa_carry_rows(int engine) {
@@ -170,13 +180,16 @@ int sa_backward(const sa_problem* in, const void* q, const void* k, const void* 
     if (st != SA_OK) return st;
     return launch_fold_cast(dq_acc, dq0, dq, p.dtype, p.batch, p.heads, per_head, s);
   }
-  st = tc_supported(p);
+  st = tc_backward_supported(p);
   if (st != SA_OK) return st;
   void* d_out_lowp = base + w.d_out_lowp;
   st = launch_dbar(out, d_out, d_out_dtype, rows, p.head_dim, dbar, d_out_lowp, p.dtype, s);
   if (st != SA_OK) return st;
-  // The tensor-core backward accumulates dk (with head 0's selection share) in fp32 in dk_acc as well.
-  return SA_ERR_UNSUPPORTED;
+  st = tc_backward(p, lse2, carry, dbar, d_out_lowp, dq_acc, dk_acc, dq0, dk0, dv, s);
+  if (st != SA_OK) return st;
+  st = launch_fold_cast(dk_acc, dk0, dk, p.dtype, p.batch, p.heads, per_head, s);
+  if (st != SA_OK) return st;
+  return launch_fold_cast(dq_acc, dq0, dq, p.dtype, p.batch, p.heads, per_head, s);
 }
 
 int sa_device_status(unsigned int* value_host, int clear) {

@@ -47,9 +47,10 @@ int simt_backward(const Problem& p, const float* lse2, const float* carry, const
 int tc_available();
 int tc_supported(const Problem& p);
 int tc_forward(const Problem& p, float* out, float* lse2, float* carry, float* total, cudaStream_t s);
+int tc_backward_supported(const Problem& p);
 int tc_backward(const Problem& p, const float* lse2, const float* carry, const float* dbar,
-                const void* d_out_lowp, float* dq_acc, float* dq0, float* dk0,
-                void* dk, void* dv, cudaStream_t s);
+                const void* d_out_lowp, float* dq_acc, float* dk_acc, float* dq0, float* dk0,
+                void* dv, cudaStream_t s);
 
 // ---- helper launches shared by both engines --------------------------------------------------------
 // dbar[row] = sum_d d_out[row, d] * out[row, d]; optionally also writes d_out rounded to `lowp_dtype`.

@@ -20,7 +20,7 @@ ENGINE_SIMT, ENGINE_TCGEN05 = 0, 1
 DAMP_CODES = {"none": 0, "linear": 1, "sqrt": 2}
 
 # every symbol include/selective_attention_b200.h declares
-EXPORTS = ("sa_abi_version", "sa_status_string", "sa_last_cuda_error", "sa_engine_available", "sa_carry_rows", "sa_carry_checkpoints", "sa_forward",
+EXPORTS = ("sa_abi_version", "sa_status_string", "sa_last_cuda_error", "sa_engine_available", "sa_engine_supports", "sa_carry_rows", "sa_carry_checkpoints", "sa_forward",
            "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step", "sa_device_status", "sa_selftest_tcgen05")
 
 
@@ -61,6 +61,8 @@ def load() -> ctypes.CDLL:
     lib.sa_last_cuda_error.restype = i32
     lib.sa_engine_available.restype = i32
     lib.sa_engine_available.argtypes = [i32]
+    lib.sa_engine_supports.restype = i32
+    lib.sa_engine_supports.argtypes = [i32] * 4
     lib.sa_carry_rows.restype = i32
     lib.sa_carry_rows.argtypes = [i32]
     lib.sa_carry_checkpoints.restype = i32

@@ -35,7 +35,6 @@ DTYPES = (torch.float16, torch.bfloat16, torch.float32)
 CARRY_M = 32                      # checkpoint spacing of the CUDA-core engine; the tensor-core engine uses 128
 _BLOCK_QUANTUM = 32
 _DTYPE_CODE = {torch.float32: _lib.DTYPE_F32, torch.bfloat16: _lib.DTYPE_BF16, torch.float16: _lib.DTYPE_F16}
-_TC_HEAD_DIMS = (64, 128)
 
 
 # ---- the paper listing (dense; the oracle the kernels are tested against, never a fallback) ---------
@@ -126,11 +125,11 @@ def _strided(t: torch.Tensor, tc: bool) -> torch.Tensor:
     return t if ok else t.contiguous()
 
 
-def _engine(lowp: bool, head_dim: int) -> int:
-    forced = os.environ.get("SA_B200_ENGINE", "")
-    if forced == "simt":
+def _engine(lowp: bool, head_dim: int, with_backward: bool) -> int:
+    """Tensor-core engine for bf16 operands where it covers the call, else the CUDA-core engine."""
+    if os.environ.get("SA_B200_ENGINE", "") == "simt":
         return _lib.ENGINE_SIMT
-    if lowp and head_dim in _TC_HEAD_DIMS and _lib.load().sa_engine_available(_lib.ENGINE_TCGEN05):
+    if lowp and _lib.load().sa_engine_supports(_lib.ENGINE_TCGEN05, _lib.DTYPE_BF16, head_dim, int(with_backward)):
         return _lib.ENGINE_TCGEN05
     return _lib.ENGINE_SIMT
 
@@ -164,10 +163,10 @@ def _prepare(q, k, v, lowp: bool):
     return tuple(t if t.dtype == want else t.to(want) for t in (q, k, v))
 
 
-def _forward(q, k, v, lowp: bool, exempt: int, damp: int, train_len: int):
+def _forward(q, k, v, lowp: bool, exempt: int, damp: int, train_len: int, with_backward: bool = False):
     lib = _lib.load()
     b, h, t, d = q.shape
-    engine = _engine(lowp, d)
+    engine = _engine(lowp, d, with_backward)
     if damp and engine == _lib.ENGINE_TCGEN05:
         engine = _lib.ENGINE_SIMT          # row-scaled F is an evaluation-only option of the CUDA-core engine
     tc = engine == _lib.ENGINE_TCGEN05
@@ -234,7 +233,7 @@ class _SelectiveAttentionFn(torch.autograd.Function):
         exempt = _check_exempt(exempt)
         lowp = _lowp(dot_precision, q.dtype)
         _check_blocks(block_m, block_n)
-        out, lse2, carry, _, operands, engine, _ = _forward(q, k, v, lowp, exempt, 0, 0)
+        out, lse2, carry, _, operands, engine, _ = _forward(q, k, v, lowp, exempt, 0, 0, with_backward=True)
         ctx.save_for_backward(*operands, out, lse2, carry)
         ctx.engine, ctx.exempt, ctx.bwd_group = engine, exempt, bwd_group
         ctx.grad_dtypes = (q.dtype, k.dtype, v.dtype)
