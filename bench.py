@@ -1,0 +1,366 @@
+"""Benchmark of the Selective Attention operator on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
+
+A step is one forward + backward of the operator over one batch of synthetic input (workload c2:
+B=4, H=16, T=16384, D=64, bf16 q/k/v/dO ~ N(0,1), causal, <BOS> exempt, head 0 selects for all heads).
+With N > 1 every rank runs its own batch of the same shape (weak scaling, no communication inside the
+operator) and the reported value is the tokens of all ranks over the slowest rank's device time.
+
+One JSON line is printed by rank 0:
+  value        tokens/s with inputs resident in HBM (device time of the forward and backward calls)
+  e2e          the same through the public Python API with host buffers: pinned host -> device copies of
+               q, k, v, dO and device -> host copies of out and the three gradients inside the timed region
+  roofline     the backward kernel (the dominant launch): algorithmic FLOPs over its device time, measured
+               with CUDA events around that launch, against the measured bf16 tensor peak
+  cpu_baseline the CPU oracle timed on this host on a bounded sample (rank 0, N = 1 only)
+--impl reference times the CPU restatement of the reference's algorithm instead (oracle/), on a bounded
+sample of the same workload, with all host threads.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for sub in ("selective-attention-study_b200", "oracle"):
+    sys.path.insert(0, os.path.join(ROOT, sub))
+
+import torch
+
+WORKLOADS = {
+    # name: (batch, heads, seq, dim, per_head selection, backward?)
+    "c2": dict(batch=4, heads=16, seq=16384, dim=64, per_head=False, backward=True),
+    "c3": dict(batch=4, heads=16, seq=16384, dim=64, per_head=True, backward=True),
+    "c4": dict(batch=1, heads=16, seq=131072, dim=64, per_head=False, backward=False),
+}
+METRIC = "selective-attn fwd+bwd tokens/s/GPU @T=16K bf16; % of tcgen05 bf16 peak"
+NOMINAL_BF16_TFLOPS = 2250.0
+FALLBACK_BF16_TFLOPS = 1590.0      # earlier measurement on this pool (burst); used only without MEASURED_PEAKS.json
+
+# dram__bytes_read.sum + dram__bytes_write.sum per launch of the backward kernel, from the ncu capture
+# summarised under profiles/ (captured on a smaller case and scaled by head-tiles; None = not captured).
+BACKWARD_DRAM_TRAFFIC_PER_HEAD_TILE = None
+
+
+def pairs(seq: int) -> float:
+    return seq * (seq + 1) / 2.0
+
+
+def algorithmic_flops(w: dict) -> dict:
+    """Counted once per selector, whatever a kernel recomputes.  P = causal pairs, N = batch * heads,
+    Nsel = selectors.  Forward: attention 4 D P N, selection logits 2 D P Nsel, the column-sum pass
+    2 D P Nsel, the triangular running-sum MMA 2 * 128 P Nsel.  Backward: attention 10 D P N, selection
+    logits again 2 D P Nsel, head-0 gradient products 4 D P Nsel; its running sums are register
+    recurrences, not MMAs, so no triangular term.  The per-head variant's selection logit is the head's
+    own logit (no extra product)."""
+    n = w["batch"] * w["heads"]
+    nsel = n if w["per_head"] else w["batch"]
+    p, d = pairs(w["seq"]), w["dim"]
+    sel_logits = 0.0 if w["per_head"] else 2 * d * p * nsel
+    fwd = 4 * d * p * n + sel_logits + 2 * d * p * nsel + 2 * 128 * p * nsel
+    bwd = (10 * d * p * n + sel_logits + 4 * d * p * nsel) if w["backward"] else 0.0
+    return dict(forward=fwd, backward=bwd, attention_only=(14 if w["backward"] else 4) * d * p * n)
+
+
+def measured_peaks() -> tuple[float, str]:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as fh:
+            data = json.load(fh)
+        return float(data["bf16_tflops_sustained"]), "measured (cuBLAS bf16, sustained)"
+    return FALLBACK_BF16_TFLOPS, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
+                                         stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
+
+    def __exit__(self, *exc):
+        if self.proc is not None:
+            self.proc.terminate()
+            self.thread.join(timeout=2)
+
+    def summary(self) -> dict:
+        clocks = sorted(int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit())
+        reasons = set()
+        for r in self.rows:
+            if len(r) >= 6:
+                for name, val in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), r[2:6]):
+                    if val.lower().startswith("active"):
+                        reasons.add(name)
+        mx = max((int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()), default=None)
+        return {"sm_mhz": clocks[len(clocks) // 2] if clocks else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(clocks)}
+
+
+def make_inputs(w: dict, seed: int):
+    """q, k, v, dO ~ N(0, 1) drawn in fp32 in that order from a CPU generator, rounded to bf16 once."""
+    g = torch.Generator("cpu").manual_seed(seed)
+    shape = (w["batch"], w["heads"], w["seq"], w["dim"])
+    return tuple(torch.randn(shape, generator=g).bfloat16() for _ in range(4))
+
+
+def selector_view(t, w):
+    if not w["per_head"]:
+        return t
+    b, h, s, d = t.shape
+    return t.reshape(b * h, 1, s, d)
+
+
+def run_ours(args, w, rank, world, device):
+    from selective_attention_b200 import _lib, kernels
+
+    if not kernels.HAS_KERNELS:
+        raise RuntimeError("the CUDA library is missing; build it first (python __graft_entry__.py)")
+    q_h, k_h, v_h, do_h = (selector_view(t, w).contiguous() for t in make_inputs(w, seed=rank))
+    tokens = w["batch"] * w["seq"]
+    flops = algorithmic_flops(w)
+
+    # ---- device-resident arm --------------------------------------------------------------------------
+    q, k, v = (t.to(device).requires_grad_(w["backward"]) for t in (q_h, k_h, v_h))
+    d_out = do_h.to(device).float()            # the operator returns fp32, so its cotangent is fp32
+
+    def step(record=None):
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e2 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        if w["backward"]:
+            out = kernels.selective_attention(q, k, v)
+            e1.record()
+            out.backward(d_out)
+            q.grad = k.grad = v.grad = None
+        else:
+            with torch.no_grad():
+                out, aux = kernels.selective_attention_forward(q, k, v, return_aux=True)
+            e1.record()
+        e2.record()
+        if record is not None:
+            record.append((e0, e1, e2))
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        step()
+    dominant = "tc_backward" if w["backward"] else "tc_forward"
+    _lib.profile_enable(dominant)
+    events = []
+    barrier()
+    with ClockSampler(device.index) as sampler:
+        for _ in range(args.steps):
+            step(events)
+        barrier()
+    kernel_ms = _lib.profile_collect()
+    _lib.profile_enable("none")
+    fwd_ms = sum(a.elapsed_time(b) for a, b, _ in events)
+    bwd_ms = sum(b.elapsed_time(c) for _, b, c in events)
+    total_ms = torch.tensor([fwd_ms + bwd_ms], device=device)
+    if world > 1:
+        torch.distributed.all_reduce(total_ms, op=torch.distributed.ReduceOp.MAX)
+    total_ms = float(total_ms.item())
+    status = _lib.device_status()
+    if status:
+        raise RuntimeError(f"a bounded device-side wait ran out (status {status:#x}); the timing is invalid")
+
+    # ---- end-to-end arm: host buffers in, host buffers out ------------------------------------------------
+    pinned_in = [t.pin_memory() for t in (q_h, k_h, v_h, do_h)]
+    pinned_out = [torch.empty(q_h.shape, dtype=torch.bfloat16).pin_memory() for _ in range(4 if w["backward"] else 1)]
+    h2d = sum(t.numel() * t.element_size() for t in (pinned_in if w["backward"] else pinned_in[:3]))
+    d2h = sum(t.numel() * t.element_size() for t in pinned_out)
+
+    def e2e_step():
+        qd, kd, vd = (t.to(device, non_blocking=True) for t in pinned_in[:3])
+        if w["backward"]:
+            dd = pinned_in[3].to(device, non_blocking=True).float()
+            qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
+            out = kernels.selective_attention(qd, kd, vd)
+            out.backward(dd)
+            results = (out.detach().to(torch.bfloat16), qd.grad, kd.grad, vd.grad)
+        else:
+            with torch.no_grad():
+                results = (kernels.selective_attention_forward(qd, kd, vd).to(torch.bfloat16),)
+        for dst, src in zip(pinned_out, results):
+            dst.copy_(src, non_blocking=True)
+
+    e2e_steps = max(1, min(args.steps, 5))
+    for _ in range(min(args.warmup, 2)):
+        e2e_step()
+    barrier()
+    s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
+    s0.record()
+    for _ in range(e2e_steps):
+        e2e_step()
+    s1.record()
+    barrier()
+    e2e_ms = torch.tensor([s0.elapsed_time(s1) / e2e_steps], device=device)
+    if world > 1:
+        torch.distributed.all_reduce(e2e_ms, op=torch.distributed.ReduceOp.MAX)
+    e2e_ms = float(e2e_ms.item())
+
+    ms_per_step = total_ms / args.steps
+    value = world * tokens / (ms_per_step * 1e-3)
+    peak, peak_kind = measured_peaks()
+    kflops = flops["backward"] if w["backward"] else flops["forward"]
+    kernel_avg_ms = sum(kernel_ms) / max(len(kernel_ms), 1)
+    achieved = kflops / (kernel_avg_ms * 1e-3) / 1e12 if kernel_ms else None
+    head_tiles = w["batch"] * w["heads"] * (math.ceil(w["seq"] / 128) * (math.ceil(w["seq"] / 128) + 1) // 2)
+    line = {
+        "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"{args.workload}: selective attention fwd{'+bwd' if w['backward'] else ''} B={w['batch']} "
+                               f"H={w['heads']} T={w['seq']} D={w['dim']} bf16, "
+                               f"{'per-head' if w['per_head'] else 'shared head-0'} selection, per GPU",
+                   "l2": "inputs (q, k, v, dO) exceed the 126 MB L2; no explicit flush",
+                   "engine": "tcgen05", "fwd_ms": fwd_ms / args.steps, "bwd_ms": bwd_ms / args.steps,
+                   "algorithmic_tflop_per_step": (flops["forward"] + flops["backward"]) / 1e12,
+                   "attention_only_tflop_per_step": flops["attention_only"] / 1e12,
+                   "step_tflops": (flops["forward"] + flops["backward"]) / (ms_per_step * 1e-3) / 1e12,
+                   "frac_of_nominal_2250": (flops["forward"] + flops["backward"]) / (ms_per_step * 1e-3) / 1e12
+                                           / NOMINAL_BF16_TFLOPS},
+        "e2e": {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
+        "gpu_launches": args.steps * (7 if w["backward"] else 3),
+        "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                     "frac": (achieved / peak) if achieved else None, "peak_kind": peak_kind,
+                     "launch_ms": kernel_avg_ms, "launches_timed": len(kernel_ms),
+                     "traffic": (BACKWARD_DRAM_TRAFFIC_PER_HEAD_TILE * head_tiles
+                                 if BACKWARD_DRAM_TRAFFIC_PER_HEAD_TILE and w["backward"] else None)},
+        "clocks": sampler.summary(),
+    }
+    return line
+
+
+def cpu_baseline(seconds: float = 12.0) -> dict:
+    """The CPU oracle (a port of the reference's paper listing and its backward algebra) on the
+    reference's own CPU-sized case: B=2, H=4, T=1024, D=64, fp32, seed 0."""
+    import selective_oracle as oracle
+
+    g = torch.Generator("cpu").manual_seed(0)
+    q, k, v, w = (torch.randn(2, 4, 1024, 64, generator=g) for _ in range(4))
+    oracle.attention_grads(q, k, v, w)
+    reps, t0 = 0, time.perf_counter()
+    while time.perf_counter() - t0 < seconds:
+        oracle.attention_grads(q, k, v, w)
+        reps += 1
+    dt = (time.perf_counter() - t0) / reps
+    return {"value": 2 * 1024 / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"oracle fwd+bwd at B=2 H=4 T=1024 D=64 fp32 (the reference's CPU case), {reps} passes, "
+                      f"{dt * 1e3:.1f} ms each"}
+
+
+def run_reference(args, w):
+    """The reference's algorithm on the host CPU: the oracle port (the reference itself is a Python
+    package that does not travel with this repository).  Each step is one sequence of the workload
+    restricted to 2 of its heads (head 0, the selector, and one more) at the full sequence length;
+    per-head work is equal, so the full-sequence time is the sample's time x heads / 2."""
+    import selective_oracle as oracle
+
+    heads_sample = min(2, w["heads"])
+    seq = w["seq"]
+    g = torch.Generator("cpu").manual_seed(0)
+    q, k, v, d = (torch.randn(heads_sample, seq, w["dim"], generator=g).bfloat16().float() for _ in range(4))
+
+    def one():
+        if w["backward"]:
+            oracle.sequence_fwd_bwd(q, k, v, d, head_chunk=1)
+        else:
+            oracle.tail_rows(q[None], k[None], v[None], tail=min(4096, seq), chunk=4096)
+
+    for _ in range(min(args.warmup, 1)):
+        one()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        one()
+    dt = (time.perf_counter() - t0) / args.steps
+    scale = w["heads"] / heads_sample if w["backward"] else w["heads"] / heads_sample * seq / min(4096, seq)
+    value = seq / (dt * scale)
+    sample = (f"1 sequence x {heads_sample} of {w['heads']} heads at T={seq}, D={w['dim']}, "
+              f"{'fwd+bwd' if w['backward'] else 'last 4096 query rows, forward'}; {dt:.2f} s per step, scaled x{scale:g}")
+    return {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+            "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: CPU oracle port on a bounded sample"},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
+                             "sample": sample},
+            "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+
+
+def main():
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
+    ap.add_argument("--seq", type=int, default=None, help="override T (profiling on a small case)")
+    ap.add_argument("--batch", type=int, default=None, help="override B (profiling on a small case)")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 0)
+    w = dict(WORKLOADS[args.workload])
+    if args.seq:
+        w["seq"] = args.seq
+    if args.batch:
+        w["batch"] = args.batch
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+
+    if args.impl == "reference":
+        if rank == 0:
+            print(json.dumps(run_reference(args, w)), flush=True)
+        return
+
+    if not torch.cuda.is_available():
+        raise RuntimeError("bench.py needs a CUDA device (there is no CPU path for the product)")
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        torch.distributed.init_process_group("nccl", device_id=device)
+    if args.warmup < 3:
+        args.warmup = 3
+    line = run_ours(args, w, rank, world, device)
+    if rank == 0:
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_baseline()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -131,6 +131,24 @@ int sa_decode_step(int dtype, int batch, int heads, int groups, int length, int 
                    void* k_cache, void* v_cache, float* selected, float* y,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* Per-kernel device timing for benchmarks.  sa_profile_enable(id) makes every later launch of that
+ * kernel record a CUDA event pair on its stream (id 0 disables); sa_profile_collect waits for the
+ * recorded pairs, writes their durations in milliseconds (launch order) to ms_host, forgets them and
+ * returns how many it wrote (-1 on error).  At most 512 launches are kept between two collects.  Not
+ * thread-safe; meant for one benchmarking thread.  No counterpart in the reference (it times whole
+ * steps with the host clock, scripts/bench_kernels.py:36-55). */
+enum sa_kernel {
+  SA_KERNEL_NONE = 0,
+  SA_KERNEL_TC_COLSUM = 1,
+  SA_KERNEL_TC_SCAN = 2,
+  SA_KERNEL_TC_FORWARD = 3,
+  SA_KERNEL_TC_BACKWARD = 4,
+  SA_KERNEL_DBAR = 5,
+  SA_KERNEL_DECODE = 6
+};
+int sa_profile_enable(int kernel_id);
+int sa_profile_collect(float* ms_host, int capacity);
+
 /* Reads (synchronously) the status word the bounded device-side waits of the tensor-core engine
  * report into; 0 means no wait ever ran out on the current device.  clear != 0 resets it.
  * No counterpart in the reference (Triton kernels have no such waits). */

@@ -11,6 +11,29 @@ namespace sa {
 static thread_local int g_last_cuda_error = 0;
 void set_last_cuda_error(int code) { g_last_cuda_error = code; }
 
+// Event pairs recorded around the enabled kernel; created on demand, reused after sa_profile_collect.
+namespace {
+constexpr int kMaxProfile = 512;
+int g_profile_kernel = 0;
+int g_profile_count = 0;
+int g_profile_created = 0;
+cudaEvent_t g_profile_start[kMaxProfile], g_profile_stop[kMaxProfile];
+}  // namespace
+
+ProfileScope::ProfileScope(int kernel_id, cudaStream_t s) : slot(-1), stream(s) {
+  if (kernel_id != g_profile_kernel || g_profile_count >= kMaxProfile) return;
+  if (g_profile_count >= g_profile_created) {
+    if (cudaEventCreate(&g_profile_start[g_profile_created]) != cudaSuccess) return;
+    if (cudaEventCreate(&g_profile_stop[g_profile_created]) != cudaSuccess) return;
+    ++g_profile_created;
+  }
+  slot = g_profile_count++;
+  cudaEventRecord(g_profile_start[slot], stream);
+}
+ProfileScope::~ProfileScope() {
+  if (slot >= 0) cudaEventRecord(g_profile_stop[slot], stream);
+}
+
 namespace {
 
 size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
@@ -190,6 +213,24 @@ int sa_backward(const sa_problem* in, const void* q, const void* k, const void* 
   st = launch_fold_cast(dk_acc, dk0, dk, p.dtype, p.batch, p.heads, per_head, s);
   if (st != SA_OK) return st;
   return launch_fold_cast(dq_acc, dq0, dq, p.dtype, p.batch, p.heads, per_head, s);
+}
+
+int sa_profile_enable(int kernel_id) {
+  if (kernel_id < 0 || kernel_id > SA_KERNEL_DECODE) return SA_ERR_BAD_ARGUMENT;
+  g_profile_kernel = kernel_id;
+  g_profile_count = 0;
+  return SA_OK;
+}
+
+int sa_profile_collect(float* ms_host, int capacity) {
+  if (!ms_host || capacity < 0) return -1;
+  int n = g_profile_count < capacity ? g_profile_count : capacity;
+  for (int i = 0; i < n; ++i) {
+    if (cudaEventSynchronize(g_profile_stop[i]) != cudaSuccess) return -1;
+    if (cudaEventElapsedTime(&ms_host[i], g_profile_start[i], g_profile_stop[i]) != cudaSuccess) return -1;
+  }
+  g_profile_count = 0;
+  return n;
 }
 
 int sa_device_status(unsigned int* value_host, int clear) {

@@ -67,6 +67,16 @@ int decode_step(int dtype, int batch, int heads, int groups, int length, int cap
 
 void set_last_cuda_error(int code);
 
+// ---- per-kernel timing hook (sa_profile_*) ------------------------------------------------------------
+// Kernel ids of include/selective_attention_b200.h (SA_KERNEL_*).  When a kernel id is enabled, the
+// launch site brackets that kernel with a CUDA event pair on the launching stream.
+struct ProfileScope {
+  ProfileScope(int kernel_id, cudaStream_t s);
+  ~ProfileScope();
+  int slot;
+  cudaStream_t stream;
+};
+
 #define SA_CUDA_CHECK(expr)                                   \
   do {                                                        \
     cudaError_t _e = (expr);                                  \

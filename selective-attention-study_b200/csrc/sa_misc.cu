@@ -43,6 +43,7 @@ int dbar_by_dim(const float* out, const void* d_out, int64_t rows, int head_dim,
   const unsigned blocks = (unsigned)((threads + 255) / 256);
   const TDO* g = static_cast<const TDO*>(d_out);
   TLOW* l = static_cast<TLOW*>(low);
+  ProfileScope prof(SA_KERNEL_DBAR, s);
   switch (head_dim) {
     case 16: dbar_kernel<TDO, TLOW, 16, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
     case 32: dbar_kernel<TDO, TLOW, 32, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
@@ -226,6 +227,7 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
                                                          length, D);
   SA_CUDA_CHECK(cudaGetLastError());
   dim3 grid(splits, rows);
+  ProfileScope prof(SA_KERNEL_DECODE, s);   // the whole step: append, attend, combine, update
   const float scale = 1.0f / sqrtf((float)D);
   const T* q = static_cast<const T*>(q1);
   const T* kk = static_cast<const T*>(kc);

@@ -322,9 +322,12 @@ int backward(const Problem& p, const float* lse2, const float* carry, const floa
   if (st != SA_OK) return st;
   const int smem = BwdSmem::total + 1024;
   SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  backward_kernel<<<(unsigned)ntiles * nrows, 128, smem, s>>>(
-      map_q, map_k, map_v, map_do, lse2, carry, dbar, dq_acc, dk_acc, dq0, dk0, static_cast<__nv_bfloat16*>(dv),
-      p.heads, p.seq, ntiles, p.exempt, p.scale, status);
+  {
+    ProfileScope prof(SA_KERNEL_TC_BACKWARD, s);
+    backward_kernel<<<(unsigned)ntiles * nrows, 128, smem, s>>>(
+        map_q, map_k, map_v, map_do, lse2, carry, dbar, dq_acc, dk_acc, dq0, dk0, static_cast<__nv_bfloat16*>(dv),
+        p.heads, p.seq, ntiles, p.exempt, p.scale, status);
+  }
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;
 }

@@ -434,17 +434,26 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   const int colsum_smem = 3 * DK * kRowTile + 1024;
   SA_CUDA_CHECK(cudaFuncSetAttribute(colsum_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, colsum_smem));
   dim3 gc(ntiles, (ntiles + kColsumChunk - 1) / kColsumChunk, p.batch);
-  colsum_kernel<D><<<gc, 128, colsum_smem, s>>>(map_q, map_k128, carry, p.seq, ntiles, p.exempt, p.scale, status);
+  {
+    ProfileScope prof(SA_KERNEL_TC_COLSUM, s);
+    colsum_kernel<D><<<gc, 128, colsum_smem, s>>>(map_q, map_k128, carry, p.seq, ntiles, p.exempt, p.scale, status);
+  }
   SA_CUDA_CHECK(cudaGetLastError());
   dim3 gs((p.seq + 255) / 256, p.batch);
-  scan_kernel<<<gs, 256, 0, s>>>(carry, total, p.seq, ntiles);
+  {
+    ProfileScope prof(SA_KERNEL_TC_SCAN, s);
+    scan_kernel<<<gs, 256, 0, s>>>(carry, total, p.seq, ntiles);
+  }
   SA_CUDA_CHECK(cudaGetLastError());
 
   const int fwd_smem = FwdSmem<D>::total + 1024;
   SA_CUDA_CHECK(cudaFuncSetAttribute(forward_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem));
   const unsigned grid = (unsigned)ntiles * p.batch * p.heads;
-  forward_kernel<D><<<grid, 128, fwd_smem, s>>>(map_q, map_k, map_v, carry, out, lse2, p.heads, p.seq, ntiles,
-                                                p.exempt, p.scale, status);
+  {
+    ProfileScope prof(SA_KERNEL_TC_FORWARD, s);
+    forward_kernel<D><<<grid, 128, fwd_smem, s>>>(map_q, map_k, map_v, carry, out, lse2, p.heads, p.seq, ntiles,
+                                                  p.exempt, p.scale, status);
+  }
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;
 }

@@ -21,7 +21,8 @@ DAMP_CODES = {"none": 0, "linear": 1, "sqrt": 2}
 
 # every symbol include/selective_attention_b200.h declares
 EXPORTS = ("sa_abi_version", "sa_status_string", "sa_last_cuda_error", "sa_engine_available", "sa_engine_supports", "sa_carry_rows", "sa_carry_checkpoints", "sa_forward",
-           "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step", "sa_device_status", "sa_selftest_tcgen05")
+           "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step", "sa_device_status", "sa_selftest_tcgen05", "sa_profile_enable",
+           "sa_profile_collect")
 
 
 class Problem(ctypes.Structure):
@@ -81,8 +82,28 @@ def load() -> ctypes.CDLL:
     lib.sa_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint), i32]
     lib.sa_selftest_tcgen05.restype = i32
     lib.sa_selftest_tcgen05.argtypes = [vp, vp, vp]
+    lib.sa_profile_enable.restype = i32
+    lib.sa_profile_enable.argtypes = [i32]
+    lib.sa_profile_collect.restype = i32
+    lib.sa_profile_collect.argtypes = [ctypes.POINTER(ctypes.c_float), i32]
     _lib = lib
     return lib
+
+
+KERNEL_IDS = {"none": 0, "tc_colsum": 1, "tc_scan": 2, "tc_forward": 3, "tc_backward": 4, "dbar": 5, "decode": 6}
+
+
+def profile_enable(kernel: str) -> None:
+    check("sa_profile_enable", load().sa_profile_enable(KERNEL_IDS[kernel]))
+
+
+def profile_collect(capacity: int = 512) -> list[float]:
+    """Durations (ms) of the launches of the enabled kernel since the last collect."""
+    buf = (ctypes.c_float * capacity)()
+    n = load().sa_profile_collect(buf, capacity)
+    if n < 0:
+        raise RuntimeError("sa_profile_collect failed")
+    return [buf[i] for i in range(n)]
 
 
 def device_status(clear: bool = True) -> int:
