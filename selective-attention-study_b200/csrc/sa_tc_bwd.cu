@@ -27,7 +27,6 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ float round_bf16(float x) { return __bfloat162float(__float2bfloat16_rn(x)); }
 __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
   asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
@@ -56,7 +55,114 @@ __device__ __forceinline__ void put8(uint8_t* base, int row, int c0, const float
   *reinterpret_cast<uint4*>(base + (c0 >> 6) * kRowTile + swz_off(row, (c0 & 63) >> 3)) = w;
 }
 
-__global__ void __launch_bounds__(128) backward_kernel(
+constexpr int kGroups = 4;                    // warpgroups per CTA; each owns 16 of a half's 64 query columns
+constexpr int kChunk = 64 / kGroups;
+constexpr int kThreads = 128 * kGroups;
+
+struct HalfCtx {
+  uint8_t* smem;
+  uint32_t lane_base;
+  int row;                 // key row of this thread inside the tile (its TMEM lane)
+  int wg;                  // warpgroup: which 16-column chunk of the half
+  int hf;                  // which half of the query tile
+  bool selectable;         // key >= exempt
+  float cnl;               // log2(e) * selection received through the END of this query tile
+  float c1;                // scale * log2(e)
+  const float* lse_s;
+  const float* dbar_s;
+  float (*sel_tot)[kTile];
+  float (*dz_tot)[kTile];
+};
+
+// One 64-query half of a (key tile, query tile) pair; this thread handles 16 of its query columns for
+// its key row.  The two running sums run from the last query to the first; a chunk computes them
+// locally (two independent chains of 8) and picks up the totals of the chunks to its right, and the
+// carried state, through shared memory.
+template <bool DIAG>
+__device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state, float& dz_state) {
+  using L = BwdSmem;
+  const int colw = c.wg * kChunk;
+  const int col0 = c.hf * 64 + colw;
+  uint32_t r[16];
+  float negon[16], ls[16], p[16], lx[16];
+
+  tmem_ld16(c.lane_base + kColL0T + colw, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    const float l0 = __uint_as_float(r[e]);
+    bool on = c.selectable && (l0 > 0.f);
+    if (DIAG) on = on && (c.row < col0 + e);          // key strictly before the query
+    negon[e] = on ? -1.f : 0.f;
+    ls[e] = on ? l0 : 0.f;
+  }
+#pragma unroll
+  for (int e = 6; e >= 0; --e) {                        // inclusive suffix sums, two chains
+    ls[e] += ls[e + 1];
+    ls[e + 8] += ls[e + 9];
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) ls[e] += ls[8];
+  c.sel_tot[c.wg][c.row] = ls[0];
+  __syncthreads();
+  float later = 0.f, all = 0.f;
+#pragma unroll
+  for (int w = 0; w < kGroups; ++w) {
+    const float t = c.sel_tot[w][c.row];
+    all += t;
+    if (w > c.wg) later += t;
+  }
+  // F * log2e = cnl - c1 * (sel_state + later + ls[e]);   z = S * c1 - F * log2e - lse
+  const float cb = c.cnl - c.c1 * (sel_state + later);
+  sel_state += all;
+
+  tmem_ld16(c.lane_base + kColST + colw, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int e = 0; e < 16; ++e) {
+    const float t2 = fmaf(c.c1, ls[e], -(cb + c.lse_s[col0 + e]));
+    p[e] = ex2(fmaf(__uint_as_float(r[e]), c.c1, t2));
+    if (DIAG && (c.row > col0 + e)) p[e] = 0.f;       // key after the query
+  }
+  put8(c.smem + L::pt, c.row, col0, p);
+  put8(c.smem + L::pt, c.row, col0 + 8, p + 8);
+
+  tmem_ld16(c.lane_base + kColDPT + colw, r);
+  tmem_ld_wait();
+#pragma unroll
+  for (int e = 0; e < 16; ++e) p[e] = p[e] * (__uint_as_float(r[e]) - c.dbar_s[col0 + e]);     // dz
+  put8(c.smem + L::dz, c.row, col0, p);
+  put8(c.smem + L::dz, c.row, col0 + 8, p + 8);
+
+  lx[15] = 0.f;                                          // exclusive suffix sums of dz, two chains
+  lx[7] = 0.f;
+#pragma unroll
+  for (int e = 6; e >= 0; --e) {
+    lx[e] = lx[e + 1] + p[e + 1];
+    lx[e + 8] = lx[e + 9] + p[e + 9];
+  }
+  const float tot_hi = lx[8] + p[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) lx[e] += tot_hi;
+  c.dz_tot[c.wg][c.row] = lx[0] + p[0];
+  __syncthreads();
+  later = 0.f;
+  all = 0.f;
+#pragma unroll
+  for (int w = 0; w < kGroups; ++w) {
+    const float t = c.dz_tot[w][c.row];
+    all += t;
+    if (w > c.wg) later += t;
+  }
+  const float base = dz_state + later;
+  dz_state += all;
+#pragma unroll
+  for (int e = 0; e < 16; ++e) lx[e] = negon[e] * (base + lx[e]);                                  // g
+  put8(c.smem + L::g, c.row, col0, lx);
+  put8(c.smem + L::g, c.row, col0 + 8, lx + 8);
+}
+
+__global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
     const float* __restrict__ lse2, const float* __restrict__ carry, const float* __restrict__ dbar,
@@ -75,8 +181,11 @@ __global__ void __launch_bounds__(128) backward_kernel(
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(16) float lse_s[kTile];
   __shared__ __align__(16) float dbar_s[kTile];
+  __shared__ float sel_tot[kGroups][kTile];
+  __shared__ float dz_tot[kGroups][kTile];
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int row = tid & 127, wg = tid >> 7;
   if (tid == 0) {
     mbar_init(&bar_kv, 1);
     mbar_init(&bar_ld, 1);
@@ -88,7 +197,7 @@ __global__ void __launch_bounds__(128) backward_kernel(
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // a warp reaches lanes 32 (warp % 4) ..
   const uint32_t sa = smem_u32(smem);
 
   auto load_queries = [&](int mi) {
@@ -109,23 +218,33 @@ __global__ void __launch_bounds__(128) backward_kernel(
   const uint32_t idesc_t = instr_desc_bf16(128, 64, false, false);     // keys x 64 queries, K = D
   const uint32_t idesc_acc = instr_desc_bf16(128, 64, false, true);    // A K-major (keys x queries), B MN-major
   const uint32_t idesc_dq = instr_desc_bf16(128, 64, true, true);      // A MN-major (queries x keys), B MN-major
-  const float c1 = scale * kLog2e;
-  const int j = nj * kTile + tid;
-  const bool key_selectable = (j >= exempt);
-  float dz_suffix = 0.f;             // sum of dz over the queries of the tiles already visited
+  const int j = nj * kTile + row;
+  float dz_state = 0.f;              // sum of dz over the queries already visited (later queries), this key
   uint32_t mma_phase = 0;
   int iter = 0;
+
+  HalfCtx ctx;
+  ctx.smem = smem;
+  ctx.lane_base = lane_base;
+  ctx.row = row;
+  ctx.wg = wg;
+  ctx.selectable = (j >= exempt);
+  ctx.c1 = scale * kLog2e;
+  ctx.lse_s = lse_s;
+  ctx.dbar_s = dbar_s;
+  ctx.sel_tot = sel_tot;
+  ctx.dz_tot = dz_tot;
 
   for (int mi = ntiles - 1; mi >= nj; --mi, ++iter) {
     const int i0 = mi * kTile;
     const bool diag = (mi == nj);
-    {
+    if (tid < kTile) {
       const int i = i0 + tid;
       lse_s[tid] = (i < seq) ? lse2[(int64_t)n * seq + i] : INFINITY;     // +inf: P = 0 for padded queries
       dbar_s[tid] = (i < seq) ? dbar[(int64_t)n * seq + i] : 0.f;
     }
-    const float carry_next = (j < seq) ? carry[((int64_t)b * (ntiles + 1) + mi + 1) * seq + j] : 0.f;
-    float sel_suffix = 0.f;          // sum over the tile's queries >= i of the (bf16-rounded) selection
+    ctx.cnl = (j < seq) ? carry[((int64_t)b * (ntiles + 1) + mi + 1) * seq + j] * kLog2e : 0.f;
+    float sel_state = 0.f;           // selection of the tile's queries already visited, this key (raw logit units)
     __syncthreads();
 
     for (int hf = 1; hf >= 0; --hf) {
@@ -134,63 +253,22 @@ __global__ void __launch_bounds__(128) backward_kernel(
         tc_fence_after_sync();
         const uint32_t qoff = hf * 8192;                                    // rows 64 hf .. 64 hf + 63
         for (int ks = 0; ks < 4; ++ks)
+          mma_ss(tmem + kColL0T, smem_desc(sa + L::k0 + ks * 32, 16, 1024),
+                 smem_desc(sa + L::q0 + qoff + ks * 32, 16, 1024), idesc_t, ks > 0);
+        for (int ks = 0; ks < 4; ++ks)
           mma_ss(tmem + kColST, smem_desc(sa + L::k + ks * 32, 16, 1024),
                  smem_desc(sa + L::q + qoff + ks * 32, 16, 1024), idesc_t, ks > 0);
         for (int ks = 0; ks < 4; ++ks)
           mma_ss(tmem + kColDPT, smem_desc(sa + L::v + ks * 32, 16, 1024),
                  smem_desc(sa + L::dout + qoff + ks * 32, 16, 1024), idesc_t, ks > 0);
-        for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColL0T, smem_desc(sa + L::k0 + ks * 32, 16, 1024),
-                 smem_desc(sa + L::q0 + qoff + ks * 32, 16, 1024), idesc_t, ks > 0);
         mma_commit(&bar_mma);
       }
       mbar_wait(&bar_mma, mma_phase, status, 402);
       mma_phase ^= 1;
       tc_fence_after_sync();
-
-#pragma unroll 1
-      for (int c0 = 32; c0 >= 0; c0 -= 32) {
-        const int col0 = hf * 64 + c0;                 // first query column of this chunk within the tile
-        uint32_t r[32];
-        float f[32];                                   // history term F, then reused
-        uint32_t gate = 0;
-        tmem_ld32(lane_base + kColL0T + c0, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 31; e >= 0; --e) {
-          const float l0 = __uint_as_float(r[e]);
-          bool on = key_selectable && (l0 > 0.f);
-          if (diag) on = on && (tid < col0 + e);       // key strictly before the query
-          const float s = on ? round_bf16(l0) : 0.f;
-          sel_suffix += s;
-          f[e] = (carry_next - scale * sel_suffix) * kLog2e;
-          gate |= (on ? 1u : 0u) << e;
-        }
-        float p[32];
-        tmem_ld32(lane_base + kColST + c0, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          float z = fmaf(__uint_as_float(r[e]), c1, -f[e]) - lse_s[col0 + e];
-          p[e] = ex2(z);
-          if (diag && (tid > col0 + e)) p[e] = 0.f;    // key after the query
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) put8(smem + L::pt, tid, col0 + c * 8, p + c * 8);
-        tmem_ld32(lane_base + kColDPT + c0, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) p[e] = p[e] * (__uint_as_float(r[e]) - dbar_s[col0 + e]);     // dz
-#pragma unroll
-        for (int c = 0; c < 4; ++c) put8(smem + L::dz, tid, col0 + c * 8, p + c * 8);
-#pragma unroll
-        for (int e = 31; e >= 0; --e) {
-          f[e] = ((gate >> e) & 1u) ? -dz_suffix : 0.f;                  // g
-          dz_suffix += p[e];
-        }
-#pragma unroll
-        for (int c = 0; c < 4; ++c) put8(smem + L::g, tid, col0 + c * 8, f + c * 8);
-      }
+      ctx.hf = hf;
+      if (diag) process_half<true>(ctx, sel_state, dz_state);
+      else process_half<false>(ctx, sel_state, dz_state);
       fence_async_smem();
       tc_fence_before_sync();
       __syncthreads();
@@ -200,6 +278,12 @@ __global__ void __launch_bounds__(128) backward_kernel(
     if (tid == 0) {
       tc_fence_after_sync();
       const uint32_t first = (iter == 0) ? 0u : 1u;
+      for (int ks = 0; ks < 8; ++ks)                                      // MN-major A: K = key index
+        mma_ss(tmem + kColDQ, smem_desc(sa + L::dz + ks * 2048, kRowTile, 1024),
+               smem_desc(sa + L::k + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
+      for (int ks = 0; ks < 8; ++ks)
+        mma_ss(tmem + kColDQ0, smem_desc(sa + L::g + ks * 2048, kRowTile, 1024),
+               smem_desc(sa + L::k0 + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
       for (int ks = 0; ks < 8; ++ks) {
         const uint32_t a_off = (ks >> 2) * kRowTile + (ks & 3) * 32;      // K-major A: K = query index
         mma_ss(tmem + kColDV, smem_desc(sa + L::pt + a_off, 16, 1024),
@@ -215,12 +299,6 @@ __global__ void __launch_bounds__(128) backward_kernel(
         mma_ss(tmem + kColDK0, smem_desc(sa + L::g + a_off, 16, 1024),
                smem_desc(sa + L::q0 + ks * 2048, kRowTile, 1024), idesc_acc, (ks > 0) ? 1u : first);
       }
-      for (int ks = 0; ks < 8; ++ks)                                      // MN-major A: K = key index
-        mma_ss(tmem + kColDQ, smem_desc(sa + L::dz + ks * 2048, kRowTile, 1024),
-               smem_desc(sa + L::k + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
-      for (int ks = 0; ks < 8; ++ks)
-        mma_ss(tmem + kColDQ0, smem_desc(sa + L::g + ks * 2048, kRowTile, 1024),
-               smem_desc(sa + L::k0 + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
       mma_commit(&bar_mma);
     }
     mbar_wait(&bar_mma, mma_phase, status, 403);
@@ -228,27 +306,21 @@ __global__ void __launch_bounds__(128) backward_kernel(
     tc_fence_after_sync();
     if (tid == 0 && mi > nj) load_queries(mi - 1);      // Q, Q0, dO tiles are free: every MMA reading them is done
     {
-      const int i = i0 + tid;                           // here the lane is a QUERY row
-      float* dq_row = dq_acc + ((int64_t)n * seq + i) * D;
-      float* dq0_row = dq0 + ((int64_t)b * seq + i) * D;
+      const int i = i0 + row;                           // here the lane is a QUERY row
+      const int c0 = wg * kChunk;
+      float* dq_row = dq_acc + ((int64_t)n * seq + i) * D + c0;
+      float* dq0_row = dq0 + ((int64_t)b * seq + i) * D + c0;
+      uint32_t r[16], r0[16];
+      tmem_ld16(lane_base + kColDQ + c0, r);
+      tmem_ld16(lane_base + kColDQ0 + c0, r0);
+      tmem_ld_wait();
+      if (i < seq) {
 #pragma unroll
-      for (int c0 = 0; c0 < D; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + kColDQ + c0, r);
-        tmem_ld_wait();
-        if (i < seq) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            red_add_v4(dq_row + c0 + e, __uint_as_float(r[e]) * scale, __uint_as_float(r[e + 1]) * scale,
-                       __uint_as_float(r[e + 2]) * scale, __uint_as_float(r[e + 3]) * scale);
-        }
-        tmem_ld32(lane_base + kColDQ0 + c0, r);
-        tmem_ld_wait();
-        if (i < seq) {
-#pragma unroll
-          for (int e = 0; e < 32; e += 4)
-            red_add_v4(dq0_row + c0 + e, __uint_as_float(r[e]) * scale, __uint_as_float(r[e + 1]) * scale,
-                       __uint_as_float(r[e + 2]) * scale, __uint_as_float(r[e + 3]) * scale);
+        for (int e = 0; e < 16; e += 4) {
+          red_add_v4(dq_row + e, __uint_as_float(r[e]) * scale, __uint_as_float(r[e + 1]) * scale,
+                     __uint_as_float(r[e + 2]) * scale, __uint_as_float(r[e + 3]) * scale);
+          red_add_v4(dq0_row + e, __uint_as_float(r0[e]) * scale, __uint_as_float(r0[e + 1]) * scale,
+                     __uint_as_float(r0[e + 2]) * scale, __uint_as_float(r0[e + 3]) * scale);
         }
       }
     }
@@ -258,40 +330,31 @@ __global__ void __launch_bounds__(128) backward_kernel(
 
   // ---- epilogue: dV, dK (this head) and this head's share of dK0 --------------------------------------------
   {
-    __nv_bfloat16* dv_row = dv + ((int64_t)n * seq + j) * D;
-    float* dk_row = dk_acc + ((int64_t)n * seq + j) * D;
-    float* dk0_row = dk0 + ((int64_t)b * seq + j) * D;
+    const int c0 = wg * kChunk;
+    __nv_bfloat16* dv_row = dv + ((int64_t)n * seq + j) * D + c0;
+    float* dk_row = dk_acc + ((int64_t)n * seq + j) * D + c0;
+    float* dk0_row = dk0 + ((int64_t)b * seq + j) * D + c0;
+    uint32_t rv[16], rk[16], r0[16];
+    tmem_ld16(lane_base + kColDV + c0, rv);
+    tmem_ld16(lane_base + kColDK + c0, rk);
+    tmem_ld16(lane_base + kColDK0 + c0, r0);
+    tmem_ld_wait();
+    if (j < seq) {
 #pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(lane_base + kColDV + c0, r);
-      tmem_ld_wait();
-      if (j < seq) {
-#pragma unroll
-        for (int e = 0; e < 32; e += 8) {
-          uint4 w = make_uint4(pack_bf16(__uint_as_float(r[e]), __uint_as_float(r[e + 1])),
-                               pack_bf16(__uint_as_float(r[e + 2]), __uint_as_float(r[e + 3])),
-                               pack_bf16(__uint_as_float(r[e + 4]), __uint_as_float(r[e + 5])),
-                               pack_bf16(__uint_as_float(r[e + 6]), __uint_as_float(r[e + 7])));
-          *reinterpret_cast<uint4*>(dv_row + c0 + e) = w;
-        }
+      for (int e = 0; e < 16; e += 8) {
+        uint4 w = make_uint4(pack_bf16(__uint_as_float(rv[e]), __uint_as_float(rv[e + 1])),
+                             pack_bf16(__uint_as_float(rv[e + 2]), __uint_as_float(rv[e + 3])),
+                             pack_bf16(__uint_as_float(rv[e + 4]), __uint_as_float(rv[e + 5])),
+                             pack_bf16(__uint_as_float(rv[e + 6]), __uint_as_float(rv[e + 7])));
+        *reinterpret_cast<uint4*>(dv_row + e) = w;
       }
-      tmem_ld32(lane_base + kColDK + c0, r);
-      tmem_ld_wait();
-      if (j < seq) {
 #pragma unroll
-        for (int e = 0; e < 32; e += 4)
-          *reinterpret_cast<float4*>(dk_row + c0 + e) =
-              make_float4(__uint_as_float(r[e]) * scale, __uint_as_float(r[e + 1]) * scale,
-                          __uint_as_float(r[e + 2]) * scale, __uint_as_float(r[e + 3]) * scale);
-      }
-      tmem_ld32(lane_base + kColDK0 + c0, r);
-      tmem_ld_wait();
-      if (j < seq) {
-#pragma unroll
-        for (int e = 0; e < 32; e += 4)
-          red_add_v4(dk0_row + c0 + e, __uint_as_float(r[e]) * scale, __uint_as_float(r[e + 1]) * scale,
-                     __uint_as_float(r[e + 2]) * scale, __uint_as_float(r[e + 3]) * scale);
+      for (int e = 0; e < 16; e += 4) {
+        *reinterpret_cast<float4*>(dk_row + e) =
+            make_float4(__uint_as_float(rk[e]) * scale, __uint_as_float(rk[e + 1]) * scale,
+                        __uint_as_float(rk[e + 2]) * scale, __uint_as_float(rk[e + 3]) * scale);
+        red_add_v4(dk0_row + e, __uint_as_float(r0[e]) * scale, __uint_as_float(r0[e + 1]) * scale,
+                   __uint_as_float(r0[e + 2]) * scale, __uint_as_float(r0[e + 3]) * scale);
       }
     }
   }
@@ -324,7 +387,7 @@ int backward(const Problem& p, const float* lse2, const float* carry, const floa
   SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   {
     ProfileScope prof(SA_KERNEL_TC_BACKWARD, s);
-    backward_kernel<<<(unsigned)ntiles * nrows, 128, smem, s>>>(
+    backward_kernel<<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
         map_q, map_k, map_v, map_do, lse2, carry, dbar, dq_acc, dk_acc, dq0, dk0, static_cast<__nv_bfloat16*>(dv),
         p.heads, p.seq, ntiles, p.exempt, p.scale, status);
   }
