@@ -1,4 +1,4 @@
-// Tensor-core engine, backward (sm_100a: TMA loads, tcgen05 MMAs, fp32 accumulators in TMEM).
+// Tensor-core engine, backward (sm_100a: TMA loads and reduce-adds, tcgen05 MMAs, fp32 accumulators in TMEM).
 //
 // One CTA owns one 128-key tile of one head and walks the 128-query tiles LAST TO FIRST.  All
 // score-shaped tiles are computed transposed, KEYS on the TMEM lanes: S^T = K Q^T, dP^T = V dO^T,
@@ -7,10 +7,18 @@
 // query to the first:
 //     F[i]  = carry_after_tile - sum_{r >= i} sel[r]          (history term rebuilt per key)
 //     U[i]  = suffix + sum_{i' > i} dz[i']                      (logit gradient of later queries)
-// with  P = exp2(z - lse),  dz = P (dP - dbar),  g = gate ? -U : 0.  P^T, dz^T and g^T go to shared
-// memory as bf16 and feed five more MMAs per query tile:
-//     dV += P^T dO    dK += dz^T Q    dK0 += g^T Q0    (accumulated in TMEM across query tiles)
-//     dQ  = dz K      dQ0 = g K0                        (per query tile; added to global fp32 with red.v4)
+// with  P = exp2(z - lse),  dz = P (dP - dbar),  g = gate ? -U : 0.
+//
+// Roles.  Warps 0-15 (four warpgroups) do the arithmetic: a query tile is handled as two 64-query
+// halves, and within a half each warpgroup takes 16 query columns of every key row; chunk totals are
+// exchanged through shared memory so the recurrences chain across chunks, halves and tiles.  Warp 16 is
+// the control warp: one lane issues every TMA load and every MMA, so MMA issue never stalls arithmetic.
+//
+// Products per query tile (all on tcgen05, fp32 accumulation in TMEM):
+//     per half : S^T, dP^T, L0^T (N = 64);  dV += P^T dO with P^T read from TMEM as bf16;
+//                dK += dz^T Q;  dK0 += g^T Q0
+//     per tile : dQ = dz K;  dQ0 = g K0  (dz, g read from shared memory M-major) -> scaled, staged in
+//                shared memory and added to the fp32 global accumulators with TMA reduce-add.
 // Reference for the arithmetic: src/selective_attention/kernels.py:196-268.
 #include "sa_tc_host.cuh"
 #include "sa_tc_ptx.cuh"
@@ -21,30 +29,29 @@ namespace {
 
 constexpr int kTile = 128;
 constexpr int kRowTile = 16384;     // bytes of a [128][64] bf16 operand tile
+constexpr int kGroups = 4;          // arithmetic warpgroups; each owns 16 of a half's 64 query columns
+constexpr int kChunk = 64 / kGroups;
+constexpr int kComputeThreads = 128 * kGroups;
+constexpr int kThreads = kComputeThreads + 32;
+constexpr int kComputeBarrier = 1;  // hardware barrier id of the arithmetic warps
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
-__device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float c, float d) {
-  asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
-}
 
 struct BwdSmem {
-  static constexpr int k = 0;                       // [128 keys][64]
+  static constexpr int k = 0;                       // [128 keys][64], stationary
   static constexpr int v = k + kRowTile;
   static constexpr int k0 = v + kRowTile;
-  static constexpr int q = k0 + kRowTile;           // [128 queries][64]
-  static constexpr int q0 = q + kRowTile;
-  static constexpr int dout = q0 + kRowTile;
-  static constexpr int pt = dout + kRowTile;        // [128 keys][128 queries] as two query-half tiles
-  static constexpr int dz = pt + 2 * kRowTile;
-  static constexpr int g = dz + 2 * kRowTile;
+  static constexpr int stage = k0 + kRowTile;       // 2 stages x (Q, Q0, dO) tiles [128 queries][64]
+  static constexpr int dz = stage + 6 * kRowTile;   // [128 keys][128 queries] bf16 as two query-half tiles;
+  static constexpr int g = dz + 2 * kRowTile;       //   after the tile's MMAs: fp32 staging of dQ / dQ0
   static constexpr int total = g + 2 * kRowTile;
 };
 
-// TMEM columns
+// TMEM columns.  L0T doubles as the home of P^T (bf16 pairs, 32 columns) once L0^T has been read.
 constexpr uint32_t kColST = 0, kColDPT = 64, kColL0T = 128, kColDV = 192, kColDK = 256, kColDK0 = 320, kColDQ = 384,
                    kColDQ0 = 448;
 
@@ -55,9 +62,26 @@ __device__ __forceinline__ void put8(uint8_t* base, int row, int c0, const float
   *reinterpret_cast<uint4*>(base + (c0 >> 6) * kRowTile + swz_off(row, (c0 & 63) >> 3)) = w;
 }
 
-constexpr int kGroups = 4;                    // warpgroups per CTA; each owns 16 of a half's 64 query columns
-constexpr int kChunk = 64 / kGroups;
-constexpr int kThreads = 128 * kGroups;
+#ifdef SA_BWD_TIMING
+__device__ unsigned long long g_bwd_timing[16];
+struct Marks {
+  unsigned long long acc[16];
+  long long last;
+  bool on;
+};
+#define SA_MARK(m, k)                                     \
+  if ((m).on) {                                           \
+    long long _now = clock64();                           \
+    (m).acc[k] += (unsigned long long)(_now - (m).last);  \
+    (m).last = _now;                                      \
+  }
+#define SA_MARKS_ARG , Marks& marks
+#define SA_MARKS_PASS , marks
+#else
+#define SA_MARK(m, k)
+#define SA_MARKS_ARG
+#define SA_MARKS_PASS
+#endif
 
 struct HalfCtx {
   uint8_t* smem;
@@ -79,7 +103,7 @@ struct HalfCtx {
 // locally (two independent chains of 8) and picks up the totals of the chunks to its right, and the
 // carried state, through shared memory.
 template <bool DIAG>
-__device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state, float& dz_state) {
+__device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state, float& dz_state SA_MARKS_ARG) {
   using L = BwdSmem;
   const int colw = c.wg * kChunk;
   const int col0 = c.hf * 64 + colw;
@@ -104,7 +128,11 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
 #pragma unroll
   for (int e = 0; e < 8; ++e) ls[e] += ls[8];
   c.sel_tot[c.wg][c.row] = ls[0];
-  __syncthreads();
+  tc_fence_before_sync();
+  SA_MARK(marks, 2)
+  named_barrier(kComputeBarrier, kComputeThreads);      // also: every thread has finished reading L0^T
+  tc_fence_after_sync();
+  SA_MARK(marks, 3)
   float later = 0.f, all = 0.f;
 #pragma unroll
   for (int w = 0; w < kGroups; ++w) {
@@ -124,8 +152,12 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
     p[e] = ex2(fmaf(__uint_as_float(r[e]), c.c1, t2));
     if (DIAG && (c.row > col0 + e)) p[e] = 0.f;       // key after the query
   }
-  put8(c.smem + L::pt, c.row, col0, p);
-  put8(c.smem + L::pt, c.row, col0 + 8, p + 8);
+  {                                                     // P^T as bf16 pairs into the (consumed) L0^T columns
+    uint32_t w8[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w8[e] = pack_bf16(p[2 * e], p[2 * e + 1]);
+    tmem_st8(c.lane_base + kColL0T + (colw >> 1), w8);
+  }
 
   tmem_ld16(c.lane_base + kColDPT + colw, r);
   tmem_ld_wait();
@@ -145,7 +177,9 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
 #pragma unroll
   for (int e = 0; e < 8; ++e) lx[e] += tot_hi;
   c.dz_tot[c.wg][c.row] = lx[0] + p[0];
-  __syncthreads();
+  SA_MARK(marks, 4)
+  named_barrier(kComputeBarrier, kComputeThreads);
+  SA_MARK(marks, 5)
   later = 0.f;
   all = 0.f;
 #pragma unroll
@@ -160,36 +194,41 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   for (int e = 0; e < 16; ++e) lx[e] = negon[e] * (base + lx[e]);                                  // g
   put8(c.smem + L::g, c.row, col0, lx);
   put8(c.smem + L::g, c.row, col0 + 8, lx + 8);
+  SA_MARK(marks, 6)
 }
 
 __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+    const __grid_constant__ CUtensorMap map_dq, const __grid_constant__ CUtensorMap map_dq0,
     const float* __restrict__ lse2, const float* __restrict__ carry, const float* __restrict__ dbar,
-    float* __restrict__ dq_acc, float* __restrict__ dk_acc, float* __restrict__ dq0, float* __restrict__ dk0,
-    __nv_bfloat16* __restrict__ dv, int heads, int seq, int ntiles, int exempt, float scale, unsigned int* status) {
+    float* __restrict__ dk_acc, float* __restrict__ dk0, __nv_bfloat16* __restrict__ dv, int heads, int seq,
+    int ntiles, int exempt, float scale, unsigned int* status) {
   using L = BwdSmem;
   constexpr int D = 64;
   const int nrows = gridDim.x / ntiles;                  // batch * heads
   const int nj = (int)(blockIdx.x / nrows);              // key tiles with the most query tiles first
   const int n = blockIdx.x % nrows;
   const int b = n / heads, h = n - b * heads;
+  const int n_iter = ntiles - nj;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar_kv, bar_ld, bar_mma;
+  __shared__ uint64_t bar_kv, bar_ld[2], bar_a, bar_b, bar_half;
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(16) float lse_s[kTile];
   __shared__ __align__(16) float dbar_s[kTile];
   __shared__ float sel_tot[kGroups][kTile];
   __shared__ float dz_tot[kGroups][kTile];
 
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int row = tid & 127, wg = tid >> 7;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     mbar_init(&bar_kv, 1);
-    mbar_init(&bar_ld, 1);
-    mbar_init(&bar_mma, 1);
+    mbar_init(&bar_ld[0], 1);
+    mbar_init(&bar_ld[1], 1);
+    mbar_init(&bar_a, 1);
+    mbar_init(&bar_b, 1);
+    mbar_init(&bar_half, kComputeThreads / 32);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&tmem_base_s, 512);
@@ -197,166 +236,243 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // a warp reaches lanes 32 (warp % 4) ..
   const uint32_t sa = smem_u32(smem);
 
-  auto load_queries = [&](int mi) {
-    mbar_expect_tx(&bar_ld, 3 * kRowTile);
-    tma_load_4d(smem + L::q, &map_q, &bar_ld, 0, mi * kTile, h, b);
-    tma_load_4d(smem + L::q0, &map_q, &bar_ld, 0, mi * kTile, 0, b);
-    tma_load_4d(smem + L::dout, &map_do, &bar_ld, 0, mi * kTile, n, 0);
-  };
-  if (tid == 0) {
-    mbar_expect_tx(&bar_kv, 3 * kRowTile);
-    tma_load_4d(smem + L::k, &map_k, &bar_kv, 0, nj * kTile, h, b);
-    tma_load_4d(smem + L::v, &map_v, &bar_kv, 0, nj * kTile, h, b);
-    tma_load_4d(smem + L::k0, &map_k, &bar_kv, 0, nj * kTile, 0, b);
-    load_queries(ntiles - 1);
-    mbar_wait(&bar_kv, 0, status, 400);
-  }
-
-  const uint32_t idesc_t = instr_desc_bf16(128, 64, false, false);     // keys x 64 queries, K = D
-  const uint32_t idesc_acc = instr_desc_bf16(128, 64, false, true);    // A K-major (keys x queries), B MN-major
-  const uint32_t idesc_dq = instr_desc_bf16(128, 64, true, true);      // A MN-major (queries x keys), B MN-major
-  const int j = nj * kTile + row;
-  float dz_state = 0.f;              // sum of dz over the queries already visited (later queries), this key
-  uint32_t mma_phase = 0;
-  int iter = 0;
-
-  HalfCtx ctx;
-  ctx.smem = smem;
-  ctx.lane_base = lane_base;
-  ctx.row = row;
-  ctx.wg = wg;
-  ctx.selectable = (j >= exempt);
-  ctx.c1 = scale * kLog2e;
-  ctx.lse_s = lse_s;
-  ctx.dbar_s = dbar_s;
-  ctx.sel_tot = sel_tot;
-  ctx.dz_tot = dz_tot;
-
-  for (int mi = ntiles - 1; mi >= nj; --mi, ++iter) {
-    const int i0 = mi * kTile;
-    const bool diag = (mi == nj);
-    if (tid < kTile) {
-      const int i = i0 + tid;
-      lse_s[tid] = (i < seq) ? lse2[(int64_t)n * seq + i] : INFINITY;     // +inf: P = 0 for padded queries
-      dbar_s[tid] = (i < seq) ? dbar[(int64_t)n * seq + i] : 0.f;
-    }
-    ctx.cnl = (j < seq) ? carry[((int64_t)b * (ntiles + 1) + mi + 1) * seq + j] * kLog2e : 0.f;
-    float sel_state = 0.f;           // selection of the tile's queries already visited, this key (raw logit units)
-    __syncthreads();
-
-    for (int hf = 1; hf >= 0; --hf) {
-      if (tid == 0) {
-        if (hf == 1) mbar_wait(&bar_ld, iter & 1, status, 401);
-        tc_fence_after_sync();
-        const uint32_t qoff = hf * 8192;                                    // rows 64 hf .. 64 hf + 63
+  if (warp == kComputeThreads / 32) {
+    // =============================== control warp: TMA loads and MMA issue ===============================
+    if (lane == 0) {
+      const uint32_t idesc_t = instr_desc_bf16(128, 64, false, false);     // keys x 64 queries, K = D
+      const uint32_t idesc_acc = instr_desc_bf16(128, 64, false, true);    // A K-major (keys x queries), B MN-major
+      const uint32_t idesc_dq = instr_desc_bf16(128, 64, true, true);      // A MN-major (queries x keys), B MN-major
+      auto load_stage = [&](int it) {
+        const int mi = ntiles - 1 - it;
+        uint8_t* st = smem + L::stage + (it & 1) * 3 * kRowTile;
+        mbar_expect_tx(&bar_ld[it & 1], 3 * kRowTile);
+        tma_load_4d(st, &map_q, &bar_ld[it & 1], 0, mi * kTile, h, b);
+        tma_load_4d(st + kRowTile, &map_q, &bar_ld[it & 1], 0, mi * kTile, 0, b);
+        tma_load_4d(st + 2 * kRowTile, &map_do, &bar_ld[it & 1], 0, mi * kTile, n, 0);
+      };
+      // S^T, dP^T, L0^T of one 64-query half
+      auto issue_scores = [&](int it, int hf) {
+        const uint32_t st = sa + L::stage + (it & 1) * 3 * kRowTile + hf * 8192;   // rows 64 hf .. 64 hf + 63
         for (int ks = 0; ks < 4; ++ks)
           mma_ss(tmem + kColL0T, smem_desc(sa + L::k0 + ks * 32, 16, 1024),
-                 smem_desc(sa + L::q0 + qoff + ks * 32, 16, 1024), idesc_t, ks > 0);
+                 smem_desc(st + kRowTile + ks * 32, 16, 1024), idesc_t, ks > 0);
         for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColST, smem_desc(sa + L::k + ks * 32, 16, 1024),
-                 smem_desc(sa + L::q + qoff + ks * 32, 16, 1024), idesc_t, ks > 0);
+          mma_ss(tmem + kColST, smem_desc(sa + L::k + ks * 32, 16, 1024), smem_desc(st + ks * 32, 16, 1024), idesc_t,
+                 ks > 0);
         for (int ks = 0; ks < 4; ++ks)
           mma_ss(tmem + kColDPT, smem_desc(sa + L::v + ks * 32, 16, 1024),
-                 smem_desc(sa + L::dout + qoff + ks * 32, 16, 1024), idesc_t, ks > 0);
-        mma_commit(&bar_mma);
-      }
-      mbar_wait(&bar_mma, mma_phase, status, 402);
-      mma_phase ^= 1;
+                 smem_desc(st + 2 * kRowTile + ks * 32, 16, 1024), idesc_t, ks > 0);
+        mma_commit(&bar_a);
+      };
+      // dV += P^T dO over the half's 64 queries, P^T from TMEM
+      auto issue_dv = [&](int it, int hf, bool first) {
+        const uint32_t st = sa + L::stage + (it & 1) * 3 * kRowTile + hf * 8192;
+        for (int ks = 0; ks < 4; ++ks)
+          mma_ts(tmem + kColDV, tmem + kColL0T + ks * 8, smem_desc(st + 2 * kRowTile + ks * 2048, kRowTile, 1024),
+                 idesc_acc, (first && ks == 0) ? 0u : 1u);
+      };
+      // dK += dz^T Q, dK0 += g^T Q0 over the half's 64 queries
+      auto issue_dk = [&](int it, int hf, bool first) {
+        const uint32_t st = sa + L::stage + (it & 1) * 3 * kRowTile + hf * 8192;
+        for (int ks = 0; ks < 4; ++ks)
+          mma_ss(tmem + kColDK, smem_desc(sa + L::dz + hf * kRowTile + ks * 32, 16, 1024),
+                 smem_desc(st + ks * 2048, kRowTile, 1024), idesc_acc, (first && ks == 0) ? 0u : 1u);
+        for (int ks = 0; ks < 4; ++ks)
+          mma_ss(tmem + kColDK0, smem_desc(sa + L::g + hf * kRowTile + ks * 32, 16, 1024),
+                 smem_desc(st + kRowTile + ks * 2048, kRowTile, 1024), idesc_acc, (first && ks == 0) ? 0u : 1u);
+      };
+
+      mbar_expect_tx(&bar_kv, 3 * kRowTile);
+      tma_load_4d(smem + L::k, &map_k, &bar_kv, 0, nj * kTile, h, b);
+      tma_load_4d(smem + L::v, &map_v, &bar_kv, 0, nj * kTile, h, b);
+      tma_load_4d(smem + L::k0, &map_k, &bar_kv, 0, nj * kTile, 0, b);
+      load_stage(0);
+      if (n_iter > 1) load_stage(1);
+      mbar_wait(&bar_kv, 0, status, 400);
+      mbar_wait(&bar_ld[0], 0, status, 401);
       tc_fence_after_sync();
-      ctx.hf = hf;
-      if (diag) process_half<true>(ctx, sel_state, dz_state);
-      else process_half<false>(ctx, sel_state, dz_state);
+      issue_scores(0, 1);
+
+      uint32_t half_phase = 0;
+      for (int it = 0; it < n_iter; ++it) {
+        mbar_wait(&bar_half, half_phase, status, 402);       // half 1 processed: P^T in TMEM, dz / g half in smem
+        half_phase ^= 1;
+        tc_fence_after_sync();
+        issue_dv(it, 1, it == 0);                             // reads P^T before the next scores overwrite it
+        issue_scores(it, 0);
+        issue_dk(it, 1, it == 0);
+        mbar_wait(&bar_half, half_phase, status, 403);       // half 0 processed
+        half_phase ^= 1;
+        tc_fence_after_sync();
+        for (int ks = 0; ks < 8; ++ks)                        // dQ = dz K, dQ0 = g K0: A M-major, K = key index
+          mma_ss(tmem + kColDQ, smem_desc(sa + L::dz + ks * 2048, kRowTile, 1024),
+                 smem_desc(sa + L::k + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem + kColDQ0, smem_desc(sa + L::g + ks * 2048, kRowTile, 1024),
+                 smem_desc(sa + L::k0 + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
+        issue_dv(it, 0, false);
+        issue_dk(it, 0, false);
+        mma_commit(&bar_b);
+        if (it + 1 < n_iter) {
+          mbar_wait(&bar_ld[(it + 1) & 1], ((it + 1) >> 1) & 1, status, 404);
+          tc_fence_after_sync();
+          issue_scores(it + 1, 1);
+        }
+        mbar_wait(&bar_b, it & 1, status, 405);               // every MMA reading stage (it & 1) has completed
+        if (it + 2 < n_iter) load_stage(it + 2);
+      }
+    }
+    __syncwarp();
+  } else {
+    // ======================================= arithmetic warps ============================================
+    const int row = tid & 127, wg = tid >> 7;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // a warp reaches lanes 32 (warp % 4) ..
+    const int j = nj * kTile + row;
+    float dz_state = 0.f;            // sum of dz over the queries already visited (later queries), this key
+    uint32_t a_phase = 0;
+
+    HalfCtx ctx;
+    ctx.smem = smem;
+    ctx.lane_base = lane_base;
+    ctx.row = row;
+    ctx.wg = wg;
+    ctx.selectable = (j >= exempt);
+    ctx.c1 = scale * kLog2e;
+    ctx.lse_s = lse_s;
+    ctx.dbar_s = dbar_s;
+    ctx.sel_tot = sel_tot;
+    ctx.dz_tot = dz_tot;
+
+    // per-tile row statistics and carry, fetched one tile ahead
+    auto fetch_lse = [&](int mi) {
+      const int i = mi * kTile + tid;
+      return (tid < kTile && i < seq) ? lse2[(int64_t)n * seq + i] : INFINITY;   // +inf: P = 0 for padded queries
+    };
+    auto fetch_dbar = [&](int mi) {
+      const int i = mi * kTile + tid;
+      return (tid < kTile && i < seq) ? dbar[(int64_t)n * seq + i] : 0.f;
+    };
+    auto fetch_carry = [&](int mi) {
+      return (j < seq) ? carry[((int64_t)b * (ntiles + 1) + mi + 1) * seq + j] * kLog2e : 0.f;
+    };
+    float next_lse = fetch_lse(ntiles - 1), next_dbar = fetch_dbar(ntiles - 1), next_carry = fetch_carry(ntiles - 1);
+#ifdef SA_BWD_TIMING
+    Marks marks;
+    for (int k2 = 0; k2 < 16; ++k2) marks.acc[k2] = 0;
+    marks.on = (tid == 0);
+    marks.last = clock64();
+#endif
+
+    for (int it = 0; it < n_iter; ++it) {
+      const int mi = ntiles - 1 - it;
+      const int i0 = mi * kTile;
+      const bool diag = (mi == nj);
+      if (tid < kTile) {
+        lse_s[tid] = next_lse;
+        dbar_s[tid] = next_dbar;
+      }
+      ctx.cnl = next_carry;
+      if (it + 1 < n_iter) {
+        next_lse = fetch_lse(mi - 1);
+        next_dbar = fetch_dbar(mi - 1);
+        next_carry = fetch_carry(mi - 1);
+      }
+      float sel_state = 0.f;         // selection of the tile's queries already visited, this key (raw logit units)
+      if (tid == 0) bulk_wait_read();                         // the previous tile's dQ reduce-adds have left dz / g
+      named_barrier(kComputeBarrier, kComputeThreads);
+      SA_MARK(marks, 0)
+
+      for (int hf = 1; hf >= 0; --hf) {
+        mbar_wait(&bar_a, a_phase, status, 410);
+        a_phase ^= 1;
+        tc_fence_after_sync();
+        SA_MARK(marks, 1)
+        ctx.hf = hf;
+        if (diag) process_half<true>(ctx, sel_state, dz_state SA_MARKS_PASS);
+        else process_half<false>(ctx, sel_state, dz_state SA_MARKS_PASS);
+        fence_async_smem();
+        tmem_st_wait();
+        tc_fence_before_sync();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_half);
+        SA_MARK(marks, 7)
+      }
+
+      // ---- dQ, dQ0 of this query tile: TMEM -> scaled fp32 staging in shared memory -> TMA reduce-add ------
+      mbar_wait(&bar_b, it & 1, status, 411);
+      tc_fence_after_sync();
+      SA_MARK(marks, 8)
+      {
+        const int c0 = wg * kChunk;                           // here the lane is a QUERY row, columns are d
+        uint32_t r[16], r0[16];
+        tmem_ld16(lane_base + kColDQ + c0, r);
+        tmem_ld16(lane_base + kColDQ0 + c0, r0);
+        tmem_ld_wait();
+        uint8_t* sq = smem + L::dz + (wg >> 1) * kRowTile;    // [128 queries][32 floats] tiles, 128-byte swizzle
+        uint8_t* sq0 = smem + L::g + (wg >> 1) * kRowTile;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const uint32_t off = swz_off(row, (wg & 1) * 4 + c);
+          *reinterpret_cast<float4*>(sq + off) =
+              make_float4(__uint_as_float(r[4 * c]) * scale, __uint_as_float(r[4 * c + 1]) * scale,
+                          __uint_as_float(r[4 * c + 2]) * scale, __uint_as_float(r[4 * c + 3]) * scale);
+          *reinterpret_cast<float4*>(sq0 + off) =
+              make_float4(__uint_as_float(r0[4 * c]) * scale, __uint_as_float(r0[4 * c + 1]) * scale,
+                          __uint_as_float(r0[4 * c + 2]) * scale, __uint_as_float(r0[4 * c + 3]) * scale);
+        }
+      }
       fence_async_smem();
       tc_fence_before_sync();
-      __syncthreads();
+      named_barrier(kComputeBarrier, kComputeThreads);
+      if (tid == 0) {
+        tma_reduce_add_4d(&map_dq, smem + L::dz, 0, i0, n, 0);
+        tma_reduce_add_4d(&map_dq, smem + L::dz + kRowTile, 32, i0, n, 0);
+        tma_reduce_add_4d(&map_dq0, smem + L::g, 0, i0, b, 0);
+        tma_reduce_add_4d(&map_dq0, smem + L::g + kRowTile, 32, i0, b, 0);
+        bulk_commit();
+      }
+      SA_MARK(marks, 9)
     }
+#ifdef SA_BWD_TIMING
+    if (tid == 0)
+      for (int k2 = 0; k2 < 16; ++k2) atomicAdd(&g_bwd_timing[k2], marks.acc[k2]);
+#endif
 
-    // ---- accumulating products and the per-query-tile dQ, dQ0 ----------------------------------------
-    if (tid == 0) {
-      tc_fence_after_sync();
-      const uint32_t first = (iter == 0) ? 0u : 1u;
-      for (int ks = 0; ks < 8; ++ks)                                      // MN-major A: K = key index
-        mma_ss(tmem + kColDQ, smem_desc(sa + L::dz + ks * 2048, kRowTile, 1024),
-               smem_desc(sa + L::k + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
-      for (int ks = 0; ks < 8; ++ks)
-        mma_ss(tmem + kColDQ0, smem_desc(sa + L::g + ks * 2048, kRowTile, 1024),
-               smem_desc(sa + L::k0 + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t a_off = (ks >> 2) * kRowTile + (ks & 3) * 32;      // K-major A: K = query index
-        mma_ss(tmem + kColDV, smem_desc(sa + L::pt + a_off, 16, 1024),
-               smem_desc(sa + L::dout + ks * 2048, kRowTile, 1024), idesc_acc, (ks > 0) ? 1u : first);
-      }
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t a_off = (ks >> 2) * kRowTile + (ks & 3) * 32;
-        mma_ss(tmem + kColDK, smem_desc(sa + L::dz + a_off, 16, 1024),
-               smem_desc(sa + L::q + ks * 2048, kRowTile, 1024), idesc_acc, (ks > 0) ? 1u : first);
-      }
-      for (int ks = 0; ks < 8; ++ks) {
-        const uint32_t a_off = (ks >> 2) * kRowTile + (ks & 3) * 32;
-        mma_ss(tmem + kColDK0, smem_desc(sa + L::g + a_off, 16, 1024),
-               smem_desc(sa + L::q0 + ks * 2048, kRowTile, 1024), idesc_acc, (ks > 0) ? 1u : first);
-      }
-      mma_commit(&bar_mma);
-    }
-    mbar_wait(&bar_mma, mma_phase, status, 403);
-    mma_phase ^= 1;
-    tc_fence_after_sync();
-    if (tid == 0 && mi > nj) load_queries(mi - 1);      // Q, Q0, dO tiles are free: every MMA reading them is done
+    // ---- epilogue: dV, dK (this head) and this head's share of dK0 ------------------------------------------
     {
-      const int i = i0 + row;                           // here the lane is a QUERY row
       const int c0 = wg * kChunk;
-      float* dq_row = dq_acc + ((int64_t)n * seq + i) * D + c0;
-      float* dq0_row = dq0 + ((int64_t)b * seq + i) * D + c0;
-      uint32_t r[16], r0[16];
-      tmem_ld16(lane_base + kColDQ + c0, r);
-      tmem_ld16(lane_base + kColDQ0 + c0, r0);
+      __nv_bfloat16* dv_row = dv + ((int64_t)n * seq + j) * D + c0;
+      float* dk_row = dk_acc + ((int64_t)n * seq + j) * D + c0;
+      float* dk0_row = dk0 + ((int64_t)b * seq + j) * D + c0;
+      uint32_t rv[16], rk[16], r0[16];
+      tmem_ld16(lane_base + kColDV + c0, rv);
+      tmem_ld16(lane_base + kColDK + c0, rk);
+      tmem_ld16(lane_base + kColDK0 + c0, r0);
       tmem_ld_wait();
-      if (i < seq) {
+      if (j < seq) {
+#pragma unroll
+        for (int e = 0; e < 16; e += 8) {
+          uint4 w = make_uint4(pack_bf16(__uint_as_float(rv[e]), __uint_as_float(rv[e + 1])),
+                               pack_bf16(__uint_as_float(rv[e + 2]), __uint_as_float(rv[e + 3])),
+                               pack_bf16(__uint_as_float(rv[e + 4]), __uint_as_float(rv[e + 5])),
+                               pack_bf16(__uint_as_float(rv[e + 6]), __uint_as_float(rv[e + 7])));
+          *reinterpret_cast<uint4*>(dv_row + e) = w;
+        }
 #pragma unroll
         for (int e = 0; e < 16; e += 4) {
-          red_add_v4(dq_row + e, __uint_as_float(r[e]) * scale, __uint_as_float(r[e + 1]) * scale,
-                     __uint_as_float(r[e + 2]) * scale, __uint_as_float(r[e + 3]) * scale);
-          red_add_v4(dq0_row + e, __uint_as_float(r0[e]) * scale, __uint_as_float(r0[e + 1]) * scale,
-                     __uint_as_float(r0[e + 2]) * scale, __uint_as_float(r0[e + 3]) * scale);
+          *reinterpret_cast<float4*>(dk_row + e) =
+              make_float4(__uint_as_float(rk[e]) * scale, __uint_as_float(rk[e + 1]) * scale,
+                          __uint_as_float(rk[e + 2]) * scale, __uint_as_float(rk[e + 3]) * scale);
+          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dk0_row + e),
+                       "f"(__uint_as_float(r0[e]) * scale), "f"(__uint_as_float(r0[e + 1]) * scale),
+                       "f"(__uint_as_float(r0[e + 2]) * scale), "f"(__uint_as_float(r0[e + 3]) * scale)
+                       : "memory");
         }
       }
     }
-    tc_fence_before_sync();
-    __syncthreads();
-  }
-
-  // ---- epilogue: dV, dK (this head) and this head's share of dK0 --------------------------------------------
-  {
-    const int c0 = wg * kChunk;
-    __nv_bfloat16* dv_row = dv + ((int64_t)n * seq + j) * D + c0;
-    float* dk_row = dk_acc + ((int64_t)n * seq + j) * D + c0;
-    float* dk0_row = dk0 + ((int64_t)b * seq + j) * D + c0;
-    uint32_t rv[16], rk[16], r0[16];
-    tmem_ld16(lane_base + kColDV + c0, rv);
-    tmem_ld16(lane_base + kColDK + c0, rk);
-    tmem_ld16(lane_base + kColDK0 + c0, r0);
-    tmem_ld_wait();
-    if (j < seq) {
-#pragma unroll
-      for (int e = 0; e < 16; e += 8) {
-        uint4 w = make_uint4(pack_bf16(__uint_as_float(rv[e]), __uint_as_float(rv[e + 1])),
-                             pack_bf16(__uint_as_float(rv[e + 2]), __uint_as_float(rv[e + 3])),
-                             pack_bf16(__uint_as_float(rv[e + 4]), __uint_as_float(rv[e + 5])),
-                             pack_bf16(__uint_as_float(rv[e + 6]), __uint_as_float(rv[e + 7])));
-        *reinterpret_cast<uint4*>(dv_row + e) = w;
-      }
-#pragma unroll
-      for (int e = 0; e < 16; e += 4) {
-        *reinterpret_cast<float4*>(dk_row + e) =
-            make_float4(__uint_as_float(rk[e]) * scale, __uint_as_float(rk[e + 1]) * scale,
-                        __uint_as_float(rk[e + 2]) * scale, __uint_as_float(rk[e + 3]) * scale);
-        red_add_v4(dk0_row + e, __uint_as_float(r0[e]) * scale, __uint_as_float(r0[e + 1]) * scale,
-                   __uint_as_float(r0[e + 2]) * scale, __uint_as_float(r0[e + 3]) * scale);
-      }
-    }
+    if (tid == 0) bulk_wait_all();                            // the last reduce-adds must land before the CTA exits
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -365,12 +481,23 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 
 }  // namespace
 
+#ifdef SA_BWD_TIMING
+extern "C" int sa_debug_bwd_timing(unsigned long long* host16, int clear) {
+  SA_CUDA_CHECK(cudaMemcpyFromSymbol(host16, g_bwd_timing, 16 * sizeof(unsigned long long)));
+  if (clear) {
+    unsigned long long z[16] = {0};
+    SA_CUDA_CHECK(cudaMemcpyToSymbol(g_bwd_timing, z, sizeof(z)));
+  }
+  return 0;
+}
+#endif
+
 int backward(const Problem& p, const float* lse2, const float* carry, const float* dbar, const void* d_out_bf16,
              float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv, cudaStream_t s) {
   if (p.head_dim != 64) return SA_ERR_UNSUPPORTED;
   const int ntiles = (p.seq + kTile - 1) / kTile;
   const int nrows = p.batch * p.heads;
-  CUtensorMap map_q, map_k, map_v, map_do;
+  CUtensorMap map_q, map_k, map_v, map_do, map_dq, map_dq0;
   int st = make_map_16bit(&map_q, p.q.ptr, 64, p.seq, p.heads, p.batch, p.q.st, p.q.sh, p.q.sb, kTile);
   if (st != SA_OK) return st;
   st = make_map_16bit(&map_k, p.k.ptr, 64, p.seq, p.heads, p.batch, p.k.st, p.k.sh, p.k.sb, kTile);
@@ -380,6 +507,10 @@ int backward(const Problem& p, const float* lse2, const float* carry, const floa
   st = make_map_16bit(&map_do, d_out_bf16, 64, p.seq, nrows, 1, 64, (int64_t)p.seq * 64, (int64_t)nrows * p.seq * 64,
                       kTile);
   if (st != SA_OK) return st;
+  st = make_map_f32_rows(&map_dq, dq_acc, p.seq, nrows);
+  if (st != SA_OK) return st;
+  st = make_map_f32_rows(&map_dq0, dq0, p.seq, p.batch);
+  if (st != SA_OK) return st;
   unsigned int* status = nullptr;
   st = status_word(&status);
   if (st != SA_OK) return st;
@@ -388,7 +519,7 @@ int backward(const Problem& p, const float* lse2, const float* carry, const floa
   {
     ProfileScope prof(SA_KERNEL_TC_BACKWARD, s);
     backward_kernel<<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
-        map_q, map_k, map_v, map_do, lse2, carry, dbar, dq_acc, dk_acc, dq0, dk0, static_cast<__nv_bfloat16*>(dv),
+        map_q, map_k, map_v, map_do, map_dq, map_dq0, lse2, carry, dbar, dk_acc, dk0, static_cast<__nv_bfloat16*>(dv),
         p.heads, p.seq, ntiles, p.exempt, p.scale, status);
   }
   SA_CUDA_CHECK(cudaGetLastError());

@@ -48,6 +48,26 @@ inline int make_map_16bit(CUtensorMap* map, const void* base, int head_dim, int 
   return SA_OK;
 }
 
+// 4-D map over (d, token, row, 1) of a contiguous fp32 tensor (rows x seq x 64); box = (32 floats, 128
+// tokens, 1, 1) with the 128-byte swizzle: the target of the TMA reduce-add of dQ tiles.
+inline int make_map_f32_rows(CUtensorMap* map, const void* base, int seq, int rows) {
+  auto fn = encode_fn();
+  if (fn == nullptr) return SA_ERR_CUDA;
+  if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return SA_ERR_ALIGNMENT;
+  cuuint64_t dims[4] = {64, (cuuint64_t)seq, (cuuint64_t)rows, 1};
+  cuuint64_t strides[3] = {64 * 4, (cuuint64_t)seq * 64 * 4, (cuuint64_t)rows * seq * 64 * 4};
+  cuuint32_t box[4] = {32, 128, 1, 1};
+  cuuint32_t elem[4] = {1, 1, 1, 1};
+  CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 4, const_cast<void*>(base), dims, strides, box, elem,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                  CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) {
+    set_last_cuda_error(10000 + (int)r);
+    return SA_ERR_CUDA;
+  }
+  return SA_OK;
+}
+
 int status_word(unsigned int** device_ptr);            // per-device status word of the bounded waits
 int read_status(unsigned int* host_value, bool clear); // synchronous read (and reset) of that word
 int selftest(void* scratch, float* result, cudaStream_t s);
