@@ -97,6 +97,34 @@ int sa_carry_checkpoints(int engine, int seq);
 int sa_forward(const sa_problem* p, const void* q, const void* k, const void* v,
                float* out, float* lse2, float* carry, float* total, void* stream);
 
+/* Forward for callers that must not allocate.  It has no counterpart in the reference (whose forward
+ * allocates its CARRY scratch with torch on every call, src/selective_attention/kernels.py:573-580).
+ *
+ * Who needs it: a serving process that hands its whole HBM budget to a KV-cache pool at start-up and
+ * forbids allocation afterwards (an allocation can synchronise the device, fragment the pool or simply
+ * fail under load), and host runtimes without an allocator binding at all (a plain C caller holding
+ * only the q/k/v/out buffers it was given).  Such a caller cannot produce the `carry` buffer sa_forward
+ * asks for, so this variant keeps it inside the library: a file-scope device array of
+ * SA_STATIC_SCRATCH_FLOATS floats (8 MiB), which every GPU that loads the library holds until the
+ * process exits.  Same kernels and same results as sa_forward; the checkpoints are not returned, so the
+ * call serves inference / prefill (out, lse2 and the per-key totals), not a later sa_backward.
+ *
+ *   - limit: batch * sa_carry_checkpoints(engine, seq) * seq <= SA_STATIC_SCRATCH_FLOATS, else
+ *     SA_ERR_TOO_LARGE and nothing is launched (e.g. one sequence up to T = 16,000 on the tensor-core
+ *     engine, or batch 8 at T = 4,096);
+ *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current) and caches it; make that first call during set-up, before any stream
+ *     capture begins;
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine;
+ *   - all calls on a device share the one array and it keeps the previous call's contents.  Nothing in
+ *     it has to start at zero (every checkpoint that is read is written first by the same call), but
+ *     two calls whose kernels overlap on the GPU (different streams, or different host threads) race
+ *     on it: serialise them. */
+#define SA_STATIC_SCRATCH_FLOATS (2 * 1024 * 1024)
+size_t sa_static_scratch_floats(void);
+int sa_forward_static_scratch(const sa_problem* p, const void* q, const void* k, const void* v,
+                              float* out, float* lse2, float* total, void* stream);
+
 /* Bytes of scratch sa_backward needs for this problem (0 on a bad problem). */
 size_t sa_backward_workspace_bytes(const sa_problem* p);
 

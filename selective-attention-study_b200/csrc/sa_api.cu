@@ -3,6 +3,8 @@
 // are in include/selective_attention_b200.h.
 #include <math.h>
 
+#include <mutex>
+
 #include "sa_common.cuh"
 #include "sa_tc_host.cuh"
 
@@ -152,6 +154,55 @@ int sa_forward(const sa_problem* in, const void* q, const void* k, const void* v
   if (in->engine == SA_ENGINE_SIMT) return simt_forward(p, out, lse2, carry, total, s);
   st = tc_supported(p);
   if (st != SA_OK) return st;
+  return tc_forward(p, out, lse2, carry, total, s);
+}
+
+// ---- forward with library-owned scratch (no allocation anywhere on the call path) ----------------------
+// The running-selection checkpoints (`carry`) are the forward's only scratch.  Here they live in a
+// file-scope device array.  Its name is only a host-side handle; the device address is looked up once
+// per device with cudaGetSymbolAddress and cached.
+static __device__ __align__(256) float g_static_carry[SA_STATIC_SCRATCH_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_static_carry_ptr[kMaxDevices] = {};
+std::mutex g_static_carry_mutex;
+
+int static_carry_for_current_device(float** out) {
+  int dev = -1;
+  SA_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return SA_ERR_UNSUPPORTED;
+  std::lock_guard<std::mutex> lock(g_static_carry_mutex);
+  if (g_static_carry_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    SA_CUDA_CHECK(cudaGetSymbolAddress(&p, g_static_carry));
+    g_static_carry_ptr[dev] = static_cast<float*>(p);
+  }
+  *out = g_static_carry_ptr[dev];
+  return SA_OK;
+}
+}  // namespace
+
+size_t sa_static_scratch_floats(void) { return (size_t)SA_STATIC_SCRATCH_FLOATS; }
+
+int sa_forward_static_scratch(const sa_problem* in, const void* q, const void* k, const void* v, float* out,
+                              float* lse2, float* total, void* stream) {
+  Problem p;
+  int st = to_problem(in, q, k, v, &p);
+  if (st != SA_OK) return st;
+  if (!q || !k || !v || !out || !lse2 || !total) return SA_ERR_BAD_ARGUMENT;
+  const size_t need = (size_t)p.batch * (size_t)sa_carry_checkpoints(in->engine, p.seq) * (size_t)p.seq;
+  if (need > (size_t)SA_STATIC_SCRATCH_FLOATS) return SA_ERR_TOO_LARGE;
+  if (in->engine == SA_ENGINE_TCGEN05) {
+    st = tc_supported(p);
+    if (st != SA_OK) return st;
+  }
+  float* carry = nullptr;
+  st = static_carry_for_current_device(&carry);
+  if (st != SA_OK) return st;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // Nothing in the array has to start at zero: both engines write every checkpoint they later read.
+  if (in->engine == SA_ENGINE_SIMT) return simt_forward(p, out, lse2, carry, total, s);
   return tc_forward(p, out, lse2, carry, total, s);
 }
 

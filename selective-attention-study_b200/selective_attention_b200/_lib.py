@@ -22,7 +22,7 @@ DAMP_CODES = {"none": 0, "linear": 1, "sqrt": 2}
 # every symbol include/selective_attention_b200.h declares
 EXPORTS = ("sa_abi_version", "sa_status_string", "sa_last_cuda_error", "sa_engine_available", "sa_engine_supports", "sa_carry_rows", "sa_carry_checkpoints", "sa_forward",
            "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step", "sa_device_status", "sa_selftest_tcgen05", "sa_profile_enable",
-           "sa_profile_collect")
+           "sa_profile_collect", "sa_static_scratch_floats", "sa_forward_static_scratch")
 
 
 class Problem(ctypes.Structure):
@@ -82,6 +82,9 @@ def load() -> ctypes.CDLL:
     lib.sa_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint), i32]
     lib.sa_selftest_tcgen05.restype = i32
     lib.sa_selftest_tcgen05.argtypes = [vp, vp, vp]
+    lib.sa_static_scratch_floats.restype = sz
+    lib.sa_forward_static_scratch.restype = i32
+    lib.sa_forward_static_scratch.argtypes = [pp, vp, vp, vp, f32p, f32p, f32p, vp]
     lib.sa_profile_enable.restype = i32
     lib.sa_profile_enable.argtypes = [i32]
     lib.sa_profile_collect.restype = i32
