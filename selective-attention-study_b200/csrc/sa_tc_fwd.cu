@@ -171,15 +171,17 @@ struct FwdSmem {
   static constexpr int total = v + DK * kKeyTile;
 };
 
+constexpr int kFwdThreads = 256;      // two warpgroups: each owns 32 of a step's 64 key columns and half of D
+
 template <int D>
-__global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CUtensorMap map_q,
-                                                      const __grid_constant__ CUtensorMap map_k,
-                                                      const __grid_constant__ CUtensorMap map_v,
-                                                      const float* __restrict__ carry, float* __restrict__ out,
-                                                      float* __restrict__ lse2, int heads, int seq, int ntiles,
-                                                      int exempt, float scale, unsigned int* status) {
+__global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
+    forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                   const __grid_constant__ CUtensorMap map_v, const float* __restrict__ carry,
+                   float* __restrict__ out, float* __restrict__ lse2, int heads, int seq, int ntiles, int exempt,
+                   float scale, unsigned int* status) {
   using L = FwdSmem<D>;
   constexpr int DK = D / 64;
+  constexpr int DH = D / 2;                                   // output columns per warpgroup
   constexpr uint32_t kTmemCols = (D == 64) ? 128 : 256;
   constexpr uint32_t kColS = 0, kColL = 64, kColPV = (D == 64) ? 64 : 128;
 
@@ -188,15 +190,17 @@ __global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CU
   const int n = blockIdx.x % nrows;
   const int b = n / heads, h = n - b * heads;
   const int i0 = mi * kTile;
-  const int steps = min(i0 + kTile, seq) / kKeys + ((min(i0 + kTile, seq) % kKeys) ? 1 : 0);
+  const int steps = (min(i0 + kTile, seq) + kKeys - 1) / kKeys;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   __shared__ uint64_t bar_q, bar_k, bar_v, bar_mma;
   __shared__ uint32_t tmem_base_s;
-  __shared__ float carry_s[2][kKeys];
+  __shared__ __align__(16) float carry_s[2][kKeys];
+  __shared__ float rmax_s[2][kTile];
 
   const int tid = threadIdx.x, warp = tid >> 5;
+  const int row = tid & 127, wg = tid >> 7;
   if (tid == 0) {
     mbar_init(&bar_q, 1);
     mbar_init(&bar_k, 1);
@@ -209,7 +213,7 @@ __global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CU
   __syncthreads();
   tc_fence_after_sync();
   const uint32_t tmem = tmem_base_s;
-  const uint32_t lane_base = tmem + ((uint32_t)(warp * 32) << 16);
+  const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
   const uint32_t sa = smem_u32(smem);
 
   auto load_k = [&](int t) {
@@ -232,18 +236,17 @@ __global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CU
     load_k(0);
     load_v(0);
   }
-  // strictly-lower-triangular ones: TRI[i][r] = 1 for r < i (row i written by thread i)
+  // strictly-lower-triangular ones: TRI[i][r] = 1 for r < i; thread (row, wg) writes columns 64 wg .. 64 wg + 63
   {
-    const int i = tid;
 #pragma unroll
-    for (int c = 0; c < 16; ++c) {
+    for (int c = 0; c < 8; ++c) {
       uint32_t w[4];
 #pragma unroll
       for (int p = 0; p < 4; ++p) {
-        int r = c * 8 + p * 2;
-        w[p] = pack_bf16(r < i ? 1.f : 0.f, (r + 1) < i ? 1.f : 0.f);
+        const int r = wg * 64 + c * 8 + p * 2;
+        w[p] = pack_bf16(r < row ? 1.f : 0.f, (r + 1) < row ? 1.f : 0.f);
       }
-      *reinterpret_cast<uint4*>(smem + L::tri + (c >> 3) * kRowTile + swz_off(i, c & 7)) = make_uint4(w[0], w[1], w[2], w[3]);
+      *reinterpret_cast<uint4*>(smem + L::tri + wg * kRowTile + swz_off(row, c)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
   }
   fence_async_smem();
@@ -255,11 +258,12 @@ __global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CU
   const float c1 = scale * kLog2e;
   const float* carry_row = carry + ((int64_t)b * (ntiles + 1) + mi) * seq;
 
-  const int i = i0 + tid;
-  float run_max = -INFINITY, run_den = 0.f;
-  float acc[D];
+  const int i = i0 + row;
+  const int cw = wg * 32;                                     // this warpgroup's key columns within a step
+  float run_max = -INFINITY, run_den = 0.f;                   // run_den: this warpgroup's share of the denominator
+  float acc[DH];
 #pragma unroll
-  for (int d = 0; d < D; ++d) acc[d] = 0.f;
+  for (int d = 0; d < DH; ++d) acc[d] = 0.f;
   uint32_t mma_phase = 0;
 
   if (tid == 0) mbar_wait(&bar_q, 0, status, 300);
@@ -271,11 +275,11 @@ __global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CU
       mbar_wait(&bar_k, t & 1, status, 301);
       tc_fence_after_sync();
       for (int ks = 0; ks < 4 * DK; ++ks)
-        mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
-               smem_desc(sa + L::k + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
-      for (int ks = 0; ks < 4 * DK; ++ks)
         mma_ss(tmem + kColL, smem_desc(sa + L::q0 + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
                smem_desc(sa + L::k0 + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
+      for (int ks = 0; ks < 4 * DK; ++ks)
+        mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+               smem_desc(sa + L::k + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
       mma_commit(&bar_mma);
     }
     if (tid < kKeys) {
@@ -287,31 +291,27 @@ __global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CU
     tc_fence_after_sync();
     if (tid == 0 && t + 1 < steps) load_k(t + 1);     // K and K0 tiles are free once both products are done
 
-    // ---- B: selection tile relu(L0) under the mask -> bf16, row = query ----------------------------------
+    // ---- B: selection relu(L0) under the mask -> bf16, row = query, this warpgroup's 32 keys ----------------
     {
-      const bool masked = (j0 + kKeys > i0) || (j0 < exempt);
+      uint32_t r[32];
+      tmem_ld32(lane_base + kColL + cw, r);
+      tmem_ld_wait();
+      float s[32];
+      if ((j0 + kKeys > i0) || (j0 < exempt)) {
 #pragma unroll
-      for (int c0 = 0; c0 < kKeys; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + kColL + c0, r);
-        tmem_ld_wait();
-        float s[32];
-        if (masked) {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            const int j = j0 + c0 + e;
-            s[e] = (j < i && j >= exempt) ? fmaxf(__uint_as_float(r[e]), 0.f) : 0.f;
-          }
-        } else {
-#pragma unroll
-          for (int e = 0; e < 32; ++e) s[e] = fmaxf(__uint_as_float(r[e]), 0.f);
+        for (int e = 0; e < 32; ++e) {
+          const int j = j0 + cw + e;
+          s[e] = (j < i && j >= exempt) ? fmaxf(__uint_as_float(r[e]), 0.f) : 0.f;
         }
+      } else {
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          uint4 w = make_uint4(pack_bf16(s[c * 8 + 0], s[c * 8 + 1]), pack_bf16(s[c * 8 + 2], s[c * 8 + 3]),
-                               pack_bf16(s[c * 8 + 4], s[c * 8 + 5]), pack_bf16(s[c * 8 + 6], s[c * 8 + 7]));
-          *reinterpret_cast<uint4*>(smem + L::selp + swz_off(tid, (c0 >> 3) + c)) = w;
-        }
+        for (int e = 0; e < 32; ++e) s[e] = fmaxf(__uint_as_float(r[e]), 0.f);
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint4 w = make_uint4(pack_bf16(s[c * 8 + 0], s[c * 8 + 1]), pack_bf16(s[c * 8 + 2], s[c * 8 + 3]),
+                             pack_bf16(s[c * 8 + 4], s[c * 8 + 5]), pack_bf16(s[c * 8 + 6], s[c * 8 + 7]));
+        *reinterpret_cast<uint4*>(smem + L::selp + swz_off(row, wg * 4 + c)) = w;
       }
     }
     fence_async_smem();
@@ -331,48 +331,51 @@ __global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CU
     tc_fence_after_sync();
 
     // ---- D: online softmax of z = (S * scale - carry) * log2(e) -----------------------------------------------
-    const bool diag = (j0 + kKeys - 1 > i0);
-    const float* cs = carry_s[t & 1];
-    float tile_max = -INFINITY;
-#pragma unroll
-    for (int c0 = 0; c0 < kKeys; c0 += 32) {
+    float z[32];
+    {
       uint32_t r[32];
-      tmem_ld32(lane_base + kColS + c0, r);
+      tmem_ld32(lane_base + kColS + cw, r);
       tmem_ld_wait();
+      const float* cs = carry_s[t & 1] + cw;
+      float tile_max = -INFINITY;
+      if (j0 + kKeys - 1 > i0) {                               // a step that crosses the diagonal
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        float z = fmaf(__uint_as_float(r[e]), c1, -cs[c0 + e]);
-        if (diag && (j0 + c0 + e > i)) z = -INFINITY;
-        tile_max = fmaxf(tile_max, z);
+        for (int e = 0; e < 32; ++e) {
+          z[e] = (j0 + cw + e > i) ? -INFINITY : fmaf(__uint_as_float(r[e]), c1, -cs[e]);
+          tile_max = fmaxf(tile_max, z[e]);
+        }
+      } else {
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          z[e] = fmaf(__uint_as_float(r[e]), c1, -cs[e]);
+          tile_max = fmaxf(tile_max, z[e]);
+        }
       }
+      rmax_s[wg][row] = tile_max;
     }
-    const float new_max = fmaxf(run_max, tile_max);
+    tc_fence_before_sync();
+    __syncthreads();
+    tc_fence_after_sync();
+    const float new_max = fmaxf(run_max, fmaxf(rmax_s[0][row], rmax_s[1][row]));
     const float alpha = ex2(run_max - new_max);
+    run_max = new_max;
     float rowsum = 0.f;
 #pragma unroll
-    for (int c0 = 0; c0 < kKeys; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(lane_base + kColS + c0, r);
-      tmem_ld_wait();
-      float p[32];
+    for (int e = 0; e < 32; ++e) {
+      z[e] = ex2(z[e] - new_max);
+      rowsum += z[e];
+    }
 #pragma unroll
-      for (int e = 0; e < 32; ++e) {
-        float z = fmaf(__uint_as_float(r[e]), c1, -cs[c0 + e]);
-        if (diag && (j0 + c0 + e > i)) z = -INFINITY;
-        p[e] = ex2(z - new_max);
-        rowsum += p[e];
-      }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 w = make_uint4(pack_bf16(p[c * 8 + 0], p[c * 8 + 1]), pack_bf16(p[c * 8 + 2], p[c * 8 + 3]),
-                             pack_bf16(p[c * 8 + 4], p[c * 8 + 5]), pack_bf16(p[c * 8 + 6], p[c * 8 + 7]));
-        *reinterpret_cast<uint4*>(smem + L::selp + swz_off(tid, (c0 >> 3) + c)) = w;
-      }
+    for (int c = 0; c < 4; ++c) {
+      uint4 w = make_uint4(pack_bf16(z[c * 8 + 0], z[c * 8 + 1]), pack_bf16(z[c * 8 + 2], z[c * 8 + 3]),
+                           pack_bf16(z[c * 8 + 4], z[c * 8 + 5]), pack_bf16(z[c * 8 + 6], z[c * 8 + 7]));
+      *reinterpret_cast<uint4*>(smem + L::selp + swz_off(row, wg * 4 + c)) = w;
     }
     run_den = run_den * alpha + rowsum;
-    run_max = new_max;
+    if (__any_sync(0xffffffffu, alpha != 1.f)) {              // the running maximum rarely moves once F has grown
 #pragma unroll
-    for (int d = 0; d < D; ++d) acc[d] *= alpha;
+      for (int d = 0; d < DH; ++d) acc[d] *= alpha;
+    }
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
@@ -391,9 +394,9 @@ __global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CU
     tc_fence_after_sync();
     if (tid == 0 && t + 1 < steps) load_v(t + 1);
 #pragma unroll
-    for (int c0 = 0; c0 < D; c0 += 32) {
+    for (int c0 = 0; c0 < DH; c0 += 32) {
       uint32_t r[32];
-      tmem_ld32(lane_base + kColPV + c0, r);
+      tmem_ld32(lane_base + kColPV + wg * DH + c0, r);
       tmem_ld_wait();
 #pragma unroll
       for (int e = 0; e < 32; ++e) acc[c0 + e] += __uint_as_float(r[e]);
@@ -402,12 +405,16 @@ __global__ void __launch_bounds__(128) forward_kernel(const __grid_constant__ CU
     __syncthreads();
   }
 
+  // the two warpgroups hold disjoint shares of each row's denominator
+  rmax_s[wg][row] = run_den;
+  __syncthreads();
+  const float den = rmax_s[0][row] + rmax_s[1][row];
   if (i < seq) {
-    const float inv = 1.f / run_den;
-    float4* orow = reinterpret_cast<float4*>(out + ((int64_t)n * seq + i) * D);
+    const float inv = 1.f / den;
+    float4* orow = reinterpret_cast<float4*>(out + ((int64_t)n * seq + i) * D + wg * DH);
 #pragma unroll
-    for (int d = 0; d < D; d += 4) orow[d >> 2] = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
-    lse2[(int64_t)n * seq + i] = run_max + log2f(run_den);
+    for (int d = 0; d < DH; d += 4) orow[d >> 2] = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
+    if (wg == 0) lse2[(int64_t)n * seq + i] = run_max + log2f(den);
   }
   tc_fence_before_sync();
   __syncthreads();
@@ -451,7 +458,7 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   const unsigned grid = (unsigned)ntiles * p.batch * p.heads;
   {
     ProfileScope prof(SA_KERNEL_TC_FORWARD, s);
-    forward_kernel<D><<<grid, 128, fwd_smem, s>>>(map_q, map_k, map_v, carry, out, lse2, p.heads, p.seq, ntiles,
+    forward_kernel<D><<<grid, kFwdThreads, fwd_smem, s>>>(map_q, map_k, map_v, carry, out, lse2, p.heads, p.seq, ntiles,
                                                   p.exempt, p.scale, status);
   }
   SA_CUDA_CHECK(cudaGetLastError());
