@@ -122,6 +122,20 @@ class ClockSampler:
                 "samples": len(clocks)}
 
 
+def max_over_ranks(value_ms: float, world: int, device) -> float:
+    """Slowest rank's time: the denominator of the whole-job throughput (device time, not wall clock)."""
+    if world == 1:
+        return float(value_ms)
+    t = torch.tensor([float(value_ms)], dtype=torch.float64, device=device)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def whole_job_tokens_per_second(tokens_per_rank: int, world: int, ms_per_step: float) -> float:
+    """Every rank processes its own batch of `tokens_per_rank` tokens per step (weak scaling)."""
+    return world * tokens_per_rank / (ms_per_step * 1e-3)
+
+
 def make_inputs(w: dict, seed: int):
     """q, k, v, dO ~ N(0, 1) drawn in fp32 in that order from a CPU generator, rounded to bf16 once."""
     g = torch.Generator("cpu").manual_seed(seed)
@@ -185,10 +199,7 @@ def run_ours(args, w, rank, world, device):
     _lib.profile_enable("none")
     fwd_ms = sum(a.elapsed_time(b) for a, b, _ in events)
     bwd_ms = sum(b.elapsed_time(c) for _, b, c in events)
-    total_ms = torch.tensor([fwd_ms + bwd_ms], device=device)
-    if world > 1:
-        torch.distributed.all_reduce(total_ms, op=torch.distributed.ReduceOp.MAX)
-    total_ms = float(total_ms.item())
+    total_ms = max_over_ranks(fwd_ms + bwd_ms, world, device)
     status = _lib.device_status()
     if status:
         raise RuntimeError(f"a bounded device-side wait ran out (status {status:#x}); the timing is invalid")
@@ -223,13 +234,10 @@ def run_ours(args, w, rank, world, device):
         e2e_step()
     s1.record()
     barrier()
-    e2e_ms = torch.tensor([s0.elapsed_time(s1) / e2e_steps], device=device)
-    if world > 1:
-        torch.distributed.all_reduce(e2e_ms, op=torch.distributed.ReduceOp.MAX)
-    e2e_ms = float(e2e_ms.item())
+    e2e_ms = max_over_ranks(s0.elapsed_time(s1) / e2e_steps, world, device)
 
     ms_per_step = total_ms / args.steps
-    value = world * tokens / (ms_per_step * 1e-3)
+    value = whole_job_tokens_per_second(tokens, world, ms_per_step)
     peak, peak_kind = measured_peaks()
     kflops = flops["backward"] if w["backward"] else flops["forward"]
     kernel_avg_ms = sum(kernel_ms) / max(len(kernel_ms), 1)
@@ -249,7 +257,7 @@ def run_ours(args, w, rank, world, device):
                    "step_tflops": (flops["forward"] + flops["backward"]) / (ms_per_step * 1e-3) / 1e12,
                    "frac_of_nominal_2250": (flops["forward"] + flops["backward"]) / (ms_per_step * 1e-3) / 1e12
                                            / NOMINAL_BF16_TFLOPS},
-        "e2e": {"value": world * tokens / (e2e_ms * 1e-3), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+        "e2e": {"value": whole_job_tokens_per_second(tokens, world, e2e_ms), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
         "gpu_launches": args.steps * (7 if w["backward"] else 3),
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
