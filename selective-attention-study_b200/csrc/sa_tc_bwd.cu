@@ -96,6 +96,8 @@ struct HalfCtx {
   const float* dbar_s;
   float (*sel_tot)[kTile];
   float (*dz_tot)[kTile];
+  uint64_t* bar_early;     // arrived once per half when P^T and dz are in place and the score columns are free
+  bool drain_reduce;       // first half of a tile: the previous tile's reduce-adds still read the dz / g buffers
 };
 
 // One 64-query half of a (key tile, query tile) pair; this thread handles 16 of its query columns for
@@ -129,6 +131,7 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   for (int e = 0; e < 8; ++e) ls[e] += ls[8];
   c.sel_tot[c.wg][c.row] = ls[0];
   tc_fence_before_sync();
+  if (c.drain_reduce && threadIdx.x == 0) bulk_wait_read();
   SA_MARK(marks, 2)
   named_barrier(kComputeBarrier, kComputeThreads);      // also: every thread has finished reading L0^T
   tc_fence_after_sync();
@@ -177,8 +180,12 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
 #pragma unroll
   for (int e = 0; e < 8; ++e) lx[e] += tot_hi;
   c.dz_tot[c.wg][c.row] = lx[0] + p[0];
+  fence_async_smem();                                    // dz tile half -> visible to the MMAs
+  tmem_st_wait();                                        // P^T in TMEM
+  tc_fence_before_sync();
   SA_MARK(marks, 4)
-  named_barrier(kComputeBarrier, kComputeThreads);
+  named_barrier(kComputeBarrier, kComputeThreads);      // every thread is done with S^T, dP^T and L0^T
+  if (threadIdx.x == 0) mbar_arrive(c.bar_early);
   SA_MARK(marks, 5)
   later = 0.f;
   all = 0.f;
@@ -214,7 +221,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar_kv, bar_ld[2], bar_a, bar_b, bar_half;
+  __shared__ uint64_t bar_kv, bar_ld[2], bar_a, bar_b, bar_half, bar_early;
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(16) float lse_s[kTile];
   __shared__ __align__(16) float dbar_s[kTile];
@@ -229,6 +236,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     mbar_init(&bar_a, 1);
     mbar_init(&bar_b, 1);
     mbar_init(&bar_half, kComputeThreads / 32);
+    mbar_init(&bar_early, 1);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&tmem_base_s, 512);
@@ -273,12 +281,15 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
           mma_ts(tmem + kColDV, tmem + kColL0T + ks * 8, smem_desc(st + 2 * kRowTile + ks * 2048, kRowTile, 1024),
                  idesc_acc, (first && ks == 0) ? 0u : 1u);
       };
-      // dK += dz^T Q, dK0 += g^T Q0 over the half's 64 queries
-      auto issue_dk = [&](int it, int hf, bool first) {
+      // dK += dz^T Q and dK0 += g^T Q0 over the half's 64 queries
+      auto issue_dk_only = [&](int it, int hf, bool first) {
         const uint32_t st = sa + L::stage + (it & 1) * 3 * kRowTile + hf * 8192;
         for (int ks = 0; ks < 4; ++ks)
           mma_ss(tmem + kColDK, smem_desc(sa + L::dz + hf * kRowTile + ks * 32, 16, 1024),
                  smem_desc(st + ks * 2048, kRowTile, 1024), idesc_acc, (first && ks == 0) ? 0u : 1u);
+      };
+      auto issue_dk0_only = [&](int it, int hf, bool first) {
+        const uint32_t st = sa + L::stage + (it & 1) * 3 * kRowTile + hf * 8192;
         for (int ks = 0; ks < 4; ++ks)
           mma_ss(tmem + kColDK0, smem_desc(sa + L::g + hf * kRowTile + ks * 32, 16, 1024),
                  smem_desc(st + kRowTile + ks * 2048, kRowTile, 1024), idesc_acc, (first && ks == 0) ? 0u : 1u);
@@ -295,25 +306,35 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       tc_fence_after_sync();
       issue_scores(0, 1);
 
-      uint32_t half_phase = 0;
+      uint32_t half_phase = 0, early_phase = 0;
       for (int it = 0; it < n_iter; ++it) {
-        mbar_wait(&bar_half, half_phase, status, 402);       // half 1 processed: P^T in TMEM, dz / g half in smem
-        half_phase ^= 1;
+        // half 1: P^T and dz are ready and the score columns are free while the g pass still runs
+        mbar_wait(&bar_early, early_phase, status, 402);
+        early_phase ^= 1;
         tc_fence_after_sync();
         issue_dv(it, 1, it == 0);                             // reads P^T before the next scores overwrite it
         issue_scores(it, 0);
-        issue_dk(it, 1, it == 0);
-        mbar_wait(&bar_half, half_phase, status, 403);       // half 0 processed
+        issue_dk_only(it, 1, it == 0);
+        mbar_wait(&bar_half, half_phase, status, 403);       // half 1: g written
         half_phase ^= 1;
         tc_fence_after_sync();
-        for (int ks = 0; ks < 8; ++ks)                        // dQ = dz K, dQ0 = g K0: A M-major, K = key index
+        issue_dk0_only(it, 1, it == 0);
+        // half 0
+        mbar_wait(&bar_early, early_phase, status, 406);
+        early_phase ^= 1;
+        tc_fence_after_sync();
+        issue_dv(it, 0, false);
+        issue_dk_only(it, 0, false);
+        for (int ks = 0; ks < 8; ++ks)                        // dQ = dz K: A M-major, K = key index
           mma_ss(tmem + kColDQ, smem_desc(sa + L::dz + ks * 2048, kRowTile, 1024),
                  smem_desc(sa + L::k + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
-        for (int ks = 0; ks < 8; ++ks)
+        mbar_wait(&bar_half, half_phase, status, 407);       // half 0: g written
+        half_phase ^= 1;
+        tc_fence_after_sync();
+        issue_dk0_only(it, 0, false);
+        for (int ks = 0; ks < 8; ++ks)                        // dQ0 = g K0
           mma_ss(tmem + kColDQ0, smem_desc(sa + L::g + ks * 2048, kRowTile, 1024),
                  smem_desc(sa + L::k0 + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
-        issue_dv(it, 0, false);
-        issue_dk(it, 0, false);
         mma_commit(&bar_b);
         if (it + 1 < n_iter) {
           mbar_wait(&bar_ld[(it + 1) & 1], ((it + 1) >> 1) & 1, status, 404);
@@ -344,6 +365,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     ctx.dbar_s = dbar_s;
     ctx.sel_tot = sel_tot;
     ctx.dz_tot = dz_tot;
+    ctx.bar_early = &bar_early;
 
     // per-tile row statistics and carry, fetched one tile ahead
     auto fetch_lse = [&](int mi) {
@@ -380,8 +402,6 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         next_carry = fetch_carry(mi - 1);
       }
       float sel_state = 0.f;         // selection of the tile's queries already visited, this key (raw logit units)
-      if (tid == 0) bulk_wait_read();                         // the previous tile's dQ reduce-adds have left dz / g
-      named_barrier(kComputeBarrier, kComputeThreads);
       SA_MARK(marks, 0)
 
       for (int hf = 1; hf >= 0; --hf) {
@@ -390,11 +410,10 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         tc_fence_after_sync();
         SA_MARK(marks, 1)
         ctx.hf = hf;
+        ctx.drain_reduce = (hf == 1) && (it > 0);
         if (diag) process_half<true>(ctx, sel_state, dz_state SA_MARKS_PASS);
         else process_half<false>(ctx, sel_state, dz_state SA_MARKS_PASS);
-        fence_async_smem();
-        tmem_st_wait();
-        tc_fence_before_sync();
+        fence_async_smem();                                    // g tile half -> visible to the MMAs
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_half);
         SA_MARK(marks, 7)
