@@ -260,39 +260,52 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         tma_load_4d(st + kRowTile, &map_q, &bar_ld[it & 1], 0, mi * kTile, 0, b);
         tma_load_4d(st + 2 * kRowTile, &map_do, &bar_ld[it & 1], 0, mi * kTile, n, 0);
       };
+      // Operand descriptors are built once; an MMA's descriptor is a base plus a byte offset / 16, so the
+      // issuing thread spends a couple of integer adds per MMA instead of rebuilding 64-bit descriptors.
+      auto at = [](uint64_t desc, uint32_t byte_off) { return desc + (uint64_t)(byte_off >> 4); };
+      const uint64_t kK = smem_desc(sa + L::k, 16, 1024), kV = smem_desc(sa + L::v, 16, 1024),
+                     kK0 = smem_desc(sa + L::k0, 16, 1024);                                   // K-major A (scores)
+      const uint64_t mK = smem_desc(sa + L::k, kRowTile, 1024), mK0 = smem_desc(sa + L::k0, kRowTile, 1024);
+      const uint64_t kDZ = smem_desc(sa + L::dz, 16, 1024), kG = smem_desc(sa + L::g, 16, 1024);   // K-major A
+      const uint64_t mDZ = smem_desc(sa + L::dz, kRowTile, 1024), mG = smem_desc(sa + L::g, kRowTile, 1024);
+      const uint64_t kStage = smem_desc(sa + L::stage, 16, 1024);            // Q, Q0, dO of stage 0, K-major B
+      const uint64_t mStage = smem_desc(sa + L::stage, kRowTile, 1024);      // the same tiles as "K rows" operands
       // S^T, dP^T, L0^T of one 64-query half
       auto issue_scores = [&](int it, int hf) {
-        const uint32_t st = sa + L::stage + (it & 1) * 3 * kRowTile + hf * 8192;   // rows 64 hf .. 64 hf + 63
+        const uint32_t st = (it & 1) * 3 * kRowTile + hf * 8192;                   // rows 64 hf .. 64 hf + 63
+#pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColL0T, smem_desc(sa + L::k0 + ks * 32, 16, 1024),
-                 smem_desc(st + kRowTile + ks * 32, 16, 1024), idesc_t, ks > 0);
+          mma_ss(tmem + kColL0T, at(kK0, ks * 32), at(kStage, st + kRowTile + ks * 32), idesc_t, ks > 0);
+#pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColST, smem_desc(sa + L::k + ks * 32, 16, 1024), smem_desc(st + ks * 32, 16, 1024), idesc_t,
-                 ks > 0);
+          mma_ss(tmem + kColST, at(kK, ks * 32), at(kStage, st + ks * 32), idesc_t, ks > 0);
+#pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColDPT, smem_desc(sa + L::v + ks * 32, 16, 1024),
-                 smem_desc(st + 2 * kRowTile + ks * 32, 16, 1024), idesc_t, ks > 0);
+          mma_ss(tmem + kColDPT, at(kV, ks * 32), at(kStage, st + 2 * kRowTile + ks * 32), idesc_t, ks > 0);
         mma_commit(&bar_a);
       };
       // dV += P^T dO over the half's 64 queries, P^T from TMEM
       auto issue_dv = [&](int it, int hf, bool first) {
-        const uint32_t st = sa + L::stage + (it & 1) * 3 * kRowTile + hf * 8192;
+        const uint32_t st = (it & 1) * 3 * kRowTile + hf * 8192;
+#pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ts(tmem + kColDV, tmem + kColL0T + ks * 8, smem_desc(st + 2 * kRowTile + ks * 2048, kRowTile, 1024),
-                 idesc_acc, (first && ks == 0) ? 0u : 1u);
+          mma_ts(tmem + kColDV, tmem + kColL0T + ks * 8, at(mStage, st + 2 * kRowTile + ks * 2048), idesc_acc,
+                 (first && ks == 0) ? 0u : 1u);
       };
       // dK += dz^T Q and dK0 += g^T Q0 over the half's 64 queries
       auto issue_dk_only = [&](int it, int hf, bool first) {
-        const uint32_t st = sa + L::stage + (it & 1) * 3 * kRowTile + hf * 8192;
+        const uint32_t st = (it & 1) * 3 * kRowTile + hf * 8192;
+#pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColDK, smem_desc(sa + L::dz + hf * kRowTile + ks * 32, 16, 1024),
-                 smem_desc(st + ks * 2048, kRowTile, 1024), idesc_acc, (first && ks == 0) ? 0u : 1u);
+          mma_ss(tmem + kColDK, at(kDZ, hf * kRowTile + ks * 32), at(mStage, st + ks * 2048), idesc_acc,
+                 (first && ks == 0) ? 0u : 1u);
       };
       auto issue_dk0_only = [&](int it, int hf, bool first) {
-        const uint32_t st = sa + L::stage + (it & 1) * 3 * kRowTile + hf * 8192;
+        const uint32_t st = (it & 1) * 3 * kRowTile + hf * 8192;
+#pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColDK0, smem_desc(sa + L::g + hf * kRowTile + ks * 32, 16, 1024),
-                 smem_desc(st + kRowTile + ks * 2048, kRowTile, 1024), idesc_acc, (first && ks == 0) ? 0u : 1u);
+          mma_ss(tmem + kColDK0, at(kG, hf * kRowTile + ks * 32), at(mStage, st + kRowTile + ks * 2048), idesc_acc,
+                 (first && ks == 0) ? 0u : 1u);
       };
 
       mbar_expect_tx(&bar_kv, 3 * kRowTile);
@@ -325,16 +338,16 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         tc_fence_after_sync();
         issue_dv(it, 0, false);
         issue_dk_only(it, 0, false);
+#pragma unroll
         for (int ks = 0; ks < 8; ++ks)                        // dQ = dz K: A M-major, K = key index
-          mma_ss(tmem + kColDQ, smem_desc(sa + L::dz + ks * 2048, kRowTile, 1024),
-                 smem_desc(sa + L::k + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
+          mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
         mbar_wait(&bar_half, half_phase, status, 407);       // half 0: g written
         half_phase ^= 1;
         tc_fence_after_sync();
         issue_dk0_only(it, 0, false);
+#pragma unroll
         for (int ks = 0; ks < 8; ++ks)                        // dQ0 = g K0
-          mma_ss(tmem + kColDQ0, smem_desc(sa + L::g + ks * 2048, kRowTile, 1024),
-                 smem_desc(sa + L::k0 + ks * 2048, kRowTile, 1024), idesc_dq, ks > 0);
+          mma_ss(tmem + kColDQ0, at(mG, ks * 2048), at(mK0, ks * 2048), idesc_dq, ks > 0);
         mma_commit(&bar_b);
         if (it + 1 < n_iter) {
           mbar_wait(&bar_ld[(it + 1) & 1], ((it + 1) >> 1) & 1, status, 404);
