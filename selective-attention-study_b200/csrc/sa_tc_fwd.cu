@@ -163,8 +163,7 @@ struct FwdSmem {
   static constexpr int DK = D / 64;
   static constexpr int q = 0;
   static constexpr int q0 = q + DK * kRowTile;
-  static constexpr int tri = q0 + DK * kRowTile;      // [128][128] as two column tiles
-  static constexpr int selp = tri + 2 * kRowTile;     // [128][64]: selection (B operand), then P (A operand)
+  static constexpr int selp = q0 + DK * kRowTile;     // [128][64]: selection (B operand), then P (A operand)
   static constexpr int k = selp + kRowTile;           // DK tiles [64][64]
   static constexpr int k0 = k + DK * kKeyTile;
   static constexpr int v = k0 + DK * kKeyTile;        // DK tiles [64 keys][64]
@@ -182,8 +181,11 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
   using L = FwdSmem<D>;
   constexpr int DK = D / 64;
   constexpr int DH = D / 2;                                   // output columns per warpgroup
-  constexpr uint32_t kTmemCols = (D == 64) ? 128 : 256;
+  // TMEM columns.  The stationary A operands live in TMEM as bf16 pairs (Q, Q0: D / 2 columns each; the
+  // strictly-lower-triangular ones matrix: 64 columns), so the per-step MMAs fetch only B from shared memory.
+  constexpr uint32_t kTmemCols = (D == 64) ? 256 : 512;
   constexpr uint32_t kColS = 0, kColL = 64, kColPV = (D == 64) ? 64 : 128;
+  constexpr uint32_t kColTri = (D == 64) ? 128 : 256, kColQ = kColTri + 64, kColQ0 = kColQ + D / 2;
 
   const int nrows = gridDim.x / ntiles;                       // batch * heads
   const int mi = ntiles - 1 - (int)(blockIdx.x / nrows);      // heaviest query tiles first
@@ -236,21 +238,39 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
     load_k(0);
     load_v(0);
   }
-  // strictly-lower-triangular ones: TRI[i][r] = 1 for r < i; thread (row, wg) writes columns 64 wg .. 64 wg + 63
+  // strictly-lower-triangular ones: TRI[i][r] = 1 for r < i; thread (row, wg) writes K columns 64 wg .. 64 wg + 63
   {
+    uint32_t w[32];
 #pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      uint32_t w[4];
+    for (int e = 0; e < 32; ++e) {
+      const int r = wg * 64 + 2 * e;
+      w[e] = pack_bf16(r < row ? 1.f : 0.f, (r + 1) < row ? 1.f : 0.f);
+    }
+    tmem_st32(lane_base + kColTri + wg * 32, w);
+  }
+  // Q and Q0 rows from the TMA landing tiles (128-byte swizzle) into TMEM; warpgroup wg moves D / 2 of the D columns
+  mbar_wait(&bar_q, 0, status, 300);
+  {
+    constexpr int kChunks = D / 16;                            // 16-byte chunks per thread and matrix
 #pragma unroll
-      for (int p = 0; p < 4; ++p) {
-        const int r = wg * 64 + c * 8 + p * 2;
-        w[p] = pack_bf16(r < row ? 1.f : 0.f, (r + 1) < row ? 1.f : 0.f);
+    for (int m = 0; m < 2; ++m) {
+      const uint8_t* src = smem + (m == 0 ? L::q : L::q0);
+      uint32_t w[kChunks * 4];
+#pragma unroll
+      for (int c = 0; c < kChunks; ++c) {
+        const int chunk = wg * kChunks + c;                   // chunk index along D (8 elements each)
+        const uint4 v4 = *reinterpret_cast<const uint4*>(src + (chunk >> 3) * kRowTile + swz_off(row, chunk & 7));
+        w[4 * c] = v4.x; w[4 * c + 1] = v4.y; w[4 * c + 2] = v4.z; w[4 * c + 3] = v4.w;
       }
-      *reinterpret_cast<uint4*>(smem + L::tri + wg * kRowTile + swz_off(row, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+      const uint32_t dst = lane_base + (m == 0 ? kColQ : kColQ0) + wg * (D / 4);
+      if constexpr (D == 64) tmem_st16(dst, w);
+      else tmem_st32(dst, w);
     }
   }
-  fence_async_smem();
+  tmem_st_wait();
+  tc_fence_before_sync();
   __syncthreads();
+  tc_fence_after_sync();
 
   const uint32_t idesc_s = instr_desc_bf16(128, kKeys, false, false);
   const uint32_t idesc_tri = instr_desc_bf16(128, kKeys, false, true, /*negate_a=*/true);
@@ -266,8 +286,6 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
   for (int d = 0; d < DH; ++d) acc[d] = 0.f;
   uint32_t mma_phase = 0;
 
-  if (tid == 0) mbar_wait(&bar_q, 0, status, 300);
-
   for (int t = 0; t < steps; ++t) {
     const int j0 = t * kKeys;
     // ---- A: S = Q K^T, L0 = Q0 K0^T ------------------------------------------------------------------
@@ -275,10 +293,10 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
       mbar_wait(&bar_k, t & 1, status, 301);
       tc_fence_after_sync();
       for (int ks = 0; ks < 4 * DK; ++ks)
-        mma_ss(tmem + kColL, smem_desc(sa + L::q0 + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+        mma_ts(tmem + kColL, tmem + kColQ0 + ks * 8,
                smem_desc(sa + L::k0 + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
       for (int ks = 0; ks < 4 * DK; ++ks)
-        mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+        mma_ts(tmem + kColS, tmem + kColQ + ks * 8,
                smem_desc(sa + L::k + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
       mma_commit(&bar_mma);
     }
@@ -322,8 +340,7 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
     if (tid == 0) {
       tc_fence_after_sync();
       for (int ks = 0; ks < 8; ++ks)
-        mma_ss(tmem + kColS, smem_desc(sa + L::tri + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
-               smem_desc(sa + L::selp + ks * 2048, kRowTile, 1024), idesc_tri, 1);
+        mma_ts(tmem + kColS, tmem + kColTri + ks * 8, smem_desc(sa + L::selp + ks * 2048, kRowTile, 1024), idesc_tri, 1);
       mma_commit(&bar_mma);
     }
     mbar_wait(&bar_mma, mma_phase, status, 303);
