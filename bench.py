@@ -41,6 +41,8 @@ WORKLOADS = {
     "c2": dict(batch=4, heads=16, seq=16384, dim=64, per_head=False, backward=True),
     "c3": dict(batch=4, heads=16, seq=16384, dim=64, per_head=True, backward=True),
     "c4": dict(batch=1, heads=16, seq=131072, dim=64, per_head=False, backward=False),
+    # one cached decode step against a 131,071-token cache (the serving continuation of c4)
+    "decode": dict(batch=1, heads=16, seq=131072, dim=64, per_head=False, backward=False),
 }
 METRIC = "selective-attn fwd+bwd tokens/s/GPU @T=16K bf16; % of tcgen05 bf16 peak"
 NOMINAL_BF16_TFLOPS = 2250.0
@@ -270,6 +272,68 @@ def run_ours(args, w, rank, world, device):
     return line
 
 
+def run_decode(args, w, rank, world, device):
+    """One cached decode step per 'step': K and V of the cache are streamed once (HBM-bound)."""
+    from selective_attention_b200 import _lib, kernels
+
+    b, h, t, d = w["batch"], w["heads"], w["seq"] - 1, w["dim"]
+    g = torch.Generator("cpu").manual_seed(rank)
+    cache = {"k": torch.randn(b, h, t + 1, d, generator=g).bfloat16().to(device),
+             "v": torch.randn(b, h, t + 1, d, generator=g).bfloat16().to(device), "len": t,
+             "selected": (3 * torch.rand(b, 1, t + 1, generator=g)).to(device)}
+    q1, k1, v1 = (torch.randn(b, h, 1, d, generator=g).bfloat16() for _ in range(3))
+    qd, kd, vd = (x.to(device) for x in (q1, k1, v1))
+    pinned = [x.pin_memory() for x in (q1, k1, v1)]
+    y_host = torch.empty(b, h, 1, d).pin_memory()
+
+    def step(host: bool):
+        cache["len"] = t
+        if host:
+            a, c, e = (x.to(device, non_blocking=True) for x in pinned)
+            y_host.copy_(kernels.decode_step(cache, a, c, e), non_blocking=True)
+        else:
+            kernels.decode_step(cache, qd, kd, vd)
+
+    results = {}
+    for host in (False, True):
+        for _ in range(args.warmup):
+            step(host)
+        if not host:
+            _lib.profile_enable("decode")
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        with ClockSampler(device.index) as sampler:
+            e0.record()
+            for _ in range(args.steps):
+                step(host)
+            e1.record()
+            torch.cuda.synchronize()
+        results[host] = max_over_ranks(e0.elapsed_time(e1) / args.steps, world, device)
+        if not host:
+            _lib.profile_enable("none")
+            clocks = sampler.summary()
+    algorithmic_bytes = 2 * b * h * (t + 1) * d * 2 + b * (t + 1) * 8       # K and V once, `selected` read + written
+    hbm_peak = 6550.1
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        hbm_peak = float(json.load(open(path))["hbm_gbs"])
+    achieved = algorithmic_bytes / (results[False] * 1e-3) / 1e9
+    return {"metric": "selective-attn cached decode steps/s (batch tokens/s) @131K-token cache bf16", "value":
+            world * b / (results[False] * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": results[False], "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"decode: one token, B={b} H={h} D={d}, cache of {t} tokens, bf16 K/V, fp32 selected",
+                       "l2": "the K and V cache (512 MiB) exceeds the 126 MB L2"},
+            "e2e": {"value": world * b / (results[True] * 1e-3), "unit": "tokens/s", "ms_per_step": results[True],
+                    "h2d_bytes_per_step": 3 * b * h * d * 2, "d2h_bytes_per_step": b * h * d * 4},
+            "gpu_launches": 4 * args.steps,
+            "roofline": {"bound": "hbm", "kernel": "decode step (append, attend, combine, update)", "achieved": achieved,
+                         "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None},
+            "clocks": clocks}
+
+
 def cpu_baseline(seconds: float = 12.0) -> dict:
     """The CPU oracle (a port of the reference's paper listing and its backward algebra) on the
     reference's own CPU-sized case: B=2, H=4, T=1024, D=64, fp32, seed 0."""
@@ -361,9 +425,9 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=device)
     if args.warmup < 3:
         args.warmup = 3
-    line = run_ours(args, w, rank, world, device)
+    line = run_decode(args, w, rank, world, device) if args.workload == "decode" else run_ours(args, w, rank, world, device)
     if rank == 0:
-        if world == 1 and not args.no_cpu_baseline:
+        if world == 1 and not args.no_cpu_baseline and args.workload != "decode":
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)
     if world > 1:

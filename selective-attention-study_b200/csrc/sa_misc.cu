@@ -89,7 +89,18 @@ __global__ void __launch_bounds__(256) fold_cast_kernel(const float* __restrict_
 
 // ---- decode -----------------------------------------------------------------------------------------
 constexpr int kDecThreads = 128;
-constexpr int kDecSplit = 512;                // keys per CTA
+constexpr int kDecSplitMin = 512;             // keys per CTA: a multiple of 512, chosen per call so that the grid
+constexpr int kDecSplitMax = 4096;            //   has a few waves of CTAs and the combine pass stays short
+
+// Keys per CTA for `t` cached keys and `rows` = batch * heads query rows.
+static int decode_split_keys(int t, int rows) {
+  const int target_splits = (148 * 8 + rows - 1) / rows;            // about eight CTAs per SM in total
+  int keys = (t + target_splits - 1) / target_splits;
+  keys = (keys + kDecSplitMin - 1) / kDecSplitMin * kDecSplitMin;
+  if (keys < kDecSplitMin) keys = kDecSplitMin;
+  if (keys > kDecSplitMax) keys = kDecSplitMax;
+  return keys;
+}
 
 template <typename T>
 __global__ void append_kernel(const T* __restrict__ k1, const T* __restrict__ v1, T* __restrict__ kc,
@@ -102,15 +113,32 @@ __global__ void append_kernel(const T* __restrict__ k1, const T* __restrict__ v1
   vc[dst] = v1[idx];
 }
 
-// grid (splits, batch * heads).  A group of D / 8 lanes owns one key per step.
+// 16-byte load of 8 (bf16 / fp16) or two 16-byte loads of 8 fp32 elements, converted to fp32.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&x)[8]) {
+  if constexpr (sizeof(T) == 2) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(p);
+    const T* h = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) x[e] = to_float<T>(h[e]);
+  } else {
+    const float4 a = *reinterpret_cast<const float4*>(p);
+    const float4 c = *reinterpret_cast<const float4*>(p + 4);
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = c.x; x[5] = c.y; x[6] = c.z; x[7] = c.w;
+  }
+}
+
+// grid (splits, batch * heads).  A group of D / 8 lanes owns one key per step; every thread keeps kUnroll
+// 16-byte loads in flight so that a CTA streams its 512 keys of K, then of V, at memory speed.
 template <typename T, int D>
 __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
     const T* __restrict__ q1, const T* __restrict__ kc, const T* __restrict__ vc, const float* __restrict__ selected,
     float* __restrict__ partial, float* __restrict__ sel_new, int heads, int groups, int t, int capacity,
-    int exempt, float scale) {
+    int exempt, float scale, int split_keys) {
   constexpr int kLanes = D / 8;                       // lanes per key
   constexpr int kKeysPerStep = kDecThreads / kLanes;  // keys the CTA covers per step
-  __shared__ float zs[kDecSplit];
+  constexpr int kUnroll = 4;
+  __shared__ float zs[kDecSplitMax];
   __shared__ float red[kDecThreads];
   __shared__ float accs[kKeysPerStep][D];
 
@@ -118,37 +146,51 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
   const int b = n / heads, h = n - b * heads;
   const int per = heads / groups, g = h / per;
   const bool selector = (h - g * per) == 0;
-  const int c0 = split * kDecSplit, c1 = min(t, c0 + kDecSplit);
+  const int c0 = split * split_keys, c1 = min(t, c0 + split_keys);
   const int grp = threadIdx.x / kLanes, lane = threadIdx.x % kLanes;
 
   float qv[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) qv[e] = to_float<T>(q1[(int64_t)n * D + lane * 8 + e]);
+  load8<T>(q1 + (int64_t)n * D + lane * 8, qv);
   const T* kb = kc + (int64_t)n * capacity * D;
   const T* vb = vc + (int64_t)n * capacity * D;
   const float* selb = selected + ((int64_t)b * groups + g) * capacity;
   float* selnb = sel_new + ((int64_t)b * groups + g) * t;
 
   float local_max = -INFINITY;
-  for (int base = c0; base < c1; base += kKeysPerStep) {   // uniform trip count: the shuffles need whole warps
-    const int j = base + grp;
-    const bool valid = j < c1;
-    float dot = 0.f;
-    if (valid) {
-      const T* kr = kb + (int64_t)j * D + lane * 8;
+  for (int base = c0; base < c1; base += kKeysPerStep * kUnroll) {   // uniform trip count: the shuffles need whole warps
+    float dot[kUnroll];
+    float kx[kUnroll][8];
+    const bool full = base + kKeysPerStep * kUnroll <= c1;       // CTA-uniform: loads without per-key guards
 #pragma unroll
-      for (int e = 0; e < 8; ++e) dot = fmaf(qv[e], to_float<T>(kr[e]), dot);
+    for (int u = 0; u < kUnroll; ++u) {
+      const int j = base + u * kKeysPerStep + grp;
+      if (full || j < c1) {
+        load8<T>(kb + (int64_t)j * D + lane * 8, kx[u]);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) kx[u][e] = 0.f;
+      }
     }
 #pragma unroll
-    for (int s = kLanes / 2; s > 0; s >>= 1) dot += __shfl_xor_sync(0xffffffffu, dot, s);
-    if (valid) {
-      float raw = dot * scale;
-      float z = (raw - selb[j]) * kLog2e;
-      if (lane == 0) {
-        zs[j - c0] = z;
-        if (selector) selnb[j] = (j >= exempt && j != t - 1 && raw > 0.f) ? raw : 0.f;
+    for (int u = 0; u < kUnroll; ++u) {
+      dot[u] = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot[u] = fmaf(qv[e], kx[u][e], dot[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+#pragma unroll
+      for (int s = kLanes / 2; s > 0; s >>= 1) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], s);
+      const int j = base + u * kKeysPerStep + grp;
+      if (j < c1) {
+        const float raw = dot[u] * scale;
+        const float z = (raw - selb[j]) * kLog2e;
+        if (lane == 0) {
+          zs[j - c0] = z;
+          if (selector) selnb[j] = (j >= exempt && j != t - 1 && raw > 0.f) ? raw : 0.f;
+        }
+        local_max = fmaxf(local_max, z);
       }
-      local_max = fmaxf(local_max, z);
     }
   }
   red[threadIdx.x] = local_max;
@@ -164,12 +206,27 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
   float den = 0.f;
-  for (int j = c0 + grp; j < c1; j += kKeysPerStep) {
-    float e2 = exp2f(zs[j - c0] - m);
-    den += e2;
-    const T* vr = vb + (int64_t)j * D + lane * 8;
+  for (int base = c0; base < c1; base += kKeysPerStep * kUnroll) {
+    float vx[kUnroll][8], w[kUnroll];
+    const bool full = base + kKeysPerStep * kUnroll <= c1;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = fmaf(e2, to_float<T>(vr[e]), acc[e]);
+    for (int u = 0; u < kUnroll; ++u) {
+      const int j = base + u * kKeysPerStep + grp;
+      if (full || j < c1) {
+        load8<T>(vb + (int64_t)j * D + lane * 8, vx[u]);
+        w[u] = exp2f(zs[j - c0] - m);
+      } else {
+        w[u] = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) vx[u][e] = 0.f;
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < kUnroll; ++u) {
+      den += w[u];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[u], vx[u][e], acc[e]);
+    }
   }
 #pragma unroll
   for (int e = 0; e < 8; ++e) accs[grp][lane * 8 + e] = acc[e];
@@ -191,19 +248,49 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
   }
 }
 
-// grid (batch * heads), D threads: merges the per-split partial softmaxes.
-__global__ void decode_combine_kernel(const float* __restrict__ partial, float* __restrict__ y, int splits, int D) {
-  const int n = blockIdx.x, d = threadIdx.x;
+// grid (batch * heads), 128 threads: merges the per-split partial softmaxes.  The global maximum is found
+// first so that the weighted sums over splits have no serial dependence: warp w folds splits w, w + 4, ...
+// (lane l owns output columns l, l + 32, ...), then the four warps are added through shared memory.
+__global__ void __launch_bounds__(128) decode_combine_kernel(const float* __restrict__ partial, float* __restrict__ y,
+                                                             int splits, int D) {
+  __shared__ float part[4][128 + 1];
+  __shared__ float red[128];
+  const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* prow = partial + (int64_t)n * splits * (D + 2);
   float m = -INFINITY;
-  for (int s = 0; s < splits; ++s) m = fmaxf(m, prow[s * (D + 2) + D]);
-  float num = 0.f, den = 0.f;
-  for (int s = 0; s < splits; ++s) {
-    float w = exp2f(prow[s * (D + 2) + D] - m);
-    num = fmaf(w, prow[s * (D + 2) + d], num);
-    den = fmaf(w, prow[s * (D + 2) + D + 1], den);
+  for (int s = threadIdx.x; s < splits; s += 128) m = fmaxf(m, prow[(int64_t)s * (D + 2) + D]);
+  red[threadIdx.x] = m;
+  __syncthreads();
+  for (int st = 64; st > 0; st >>= 1) {
+    if (threadIdx.x < st) red[threadIdx.x] = fmaxf(red[threadIdx.x], red[threadIdx.x + st]);
+    __syncthreads();
   }
-  y[(int64_t)n * D + d] = num / den;
+  m = red[0];
+  float den = 0.f, num[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll 4
+  for (int s = warp; s < splits; s += 4) {
+    const float* p = prow + (int64_t)s * (D + 2);
+    const float c = exp2f(p[D] - m);
+    den = fmaf(p[D + 1], c, den);
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int d = lane + 32 * u;
+      if (d < D) num[u] = fmaf(p[d], c, num[u]);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int d = lane + 32 * u;
+    if (d < D) part[warp][d] = num[u];
+  }
+  if (lane == 0) part[warp][128] = den;
+  __syncthreads();
+  const int d = threadIdx.x;
+  if (d < D) {
+    const float nn = part[0][d] + part[1][d] + part[2][d] + part[3][d];
+    const float dd = part[0][128] + part[1][128] + part[2][128] + part[3][128];
+    y[(int64_t)n * D + d] = nn / dd;
+  }
 }
 
 __global__ void decode_update_kernel(float* __restrict__ selected, const float* __restrict__ sel_new, int rows, int t,
@@ -219,7 +306,8 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
                 const void* k1, const void* v1, void* kc, void* vc, float* selected, float* y, float* ws,
                 cudaStream_t s) {
   const int rows = batch * heads, t = length + 1;
-  const int splits = (t + kDecSplit - 1) / kDecSplit;
+  const int split_keys = decode_split_keys(t, rows);
+  const int splits = (t + split_keys - 1) / split_keys;
   float* partial = ws;
   float* sel_new = ws + (size_t)rows * splits * (D + 2);
   append_kernel<T><<<(rows * D + 255) / 256, 256, 0, s>>>(static_cast<const T*>(k1), static_cast<const T*>(v1),
@@ -234,7 +322,7 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
   const T* vv = static_cast<const T*>(vc);
 #define SA_DECODE_LAUNCH(DIM)                                                                                   \
   decode_attend_kernel<T, DIM><<<grid, kDecThreads, 0, s>>>(q, kk, vv, selected, partial, sel_new, heads, groups, \
-                                                            t, capacity, exempt, scale)
+                                                            t, capacity, exempt, scale, split_keys)
   switch (D) {
     case 16: SA_DECODE_LAUNCH(16); break;
     case 32: SA_DECODE_LAUNCH(32); break;
@@ -244,7 +332,7 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
   }
 #undef SA_DECODE_LAUNCH
   SA_CUDA_CHECK(cudaGetLastError());
-  decode_combine_kernel<<<rows, D, 0, s>>>(partial, y, splits, D);
+  decode_combine_kernel<<<rows, 128, 0, s>>>(partial, y, splits, D);
   SA_CUDA_CHECK(cudaGetLastError());
   const int64_t upd = (int64_t)batch * groups * t;
   decode_update_kernel<<<(unsigned)((upd + 255) / 256), 256, 0, s>>>(selected, sel_new, batch * groups, t, capacity);
@@ -288,7 +376,7 @@ int launch_fold_cast(const float* acc, const float* acc0, void* dst, int dtype, 
 
 size_t decode_workspace_floats(int batch, int heads, int groups, int length, int head_dim) {
   const int t = length + 1;
-  const size_t splits = (size_t)(t + kDecSplit - 1) / kDecSplit;
+  const size_t splits = (size_t)(t + kDecSplitMin - 1) / kDecSplitMin;       // upper bound: the smallest split size
   return (size_t)batch * heads * splits * (head_dim + 2) + (size_t)batch * groups * t;
 }
 
