@@ -41,6 +41,14 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// A global load the compiler must issue where it is written (volatile asm keeps its place among the other
+// volatile asm statements), so a value fetched one tile ahead is really in flight during that tile.
+__device__ __forceinline__ float load_ahead(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
 struct BwdSmem {
   static constexpr int k = 0;                       // [128 keys][64], stationary
   static constexpr int v = k + kRowTile;
@@ -221,7 +229,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar_kv, bar_ld[2], bar_a, bar_b, bar_half, bar_early;
+  __shared__ uint64_t bar_kv, bar_ld[2], bar_a, bar_b, bar_dq, bar_half, bar_early;
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(16) float lse_s[kTile];
   __shared__ __align__(16) float dbar_s[kTile];
@@ -235,6 +243,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     mbar_init(&bar_ld[1], 1);
     mbar_init(&bar_a, 1);
     mbar_init(&bar_b, 1);
+    mbar_init(&bar_dq, 1);
     mbar_init(&bar_half, kComputeThreads / 32);
     mbar_init(&bar_early, 1);
     mbar_init_fence();
@@ -341,6 +350,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)                        // dQ = dz K: A M-major, K = key index
           mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
+        mma_commit(&bar_dq);                                  // dQ done => every MMA reading the dz tiles is done
         mbar_wait(&bar_half, half_phase, status, 407);       // half 0: g written
         half_phase ^= 1;
         tc_fence_after_sync();
@@ -383,14 +393,14 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     // per-tile row statistics and carry, fetched one tile ahead
     auto fetch_lse = [&](int mi) {
       const int i = mi * kTile + tid;
-      return (tid < kTile && i < seq) ? lse2[(int64_t)n * seq + i] : INFINITY;   // +inf: P = 0 for padded queries
+      return (tid < kTile && i < seq) ? load_ahead(lse2 + (int64_t)n * seq + i) : INFINITY;   // +inf: P = 0 for padded queries
     };
     auto fetch_dbar = [&](int mi) {
       const int i = mi * kTile + tid;
-      return (tid < kTile && i < seq) ? dbar[(int64_t)n * seq + i] : 0.f;
+      return (tid < kTile && i < seq) ? load_ahead(dbar + (int64_t)n * seq + i) : 0.f;
     };
     auto fetch_carry = [&](int mi) {
-      return (j < seq) ? carry[((int64_t)b * (ntiles + 1) + mi + 1) * seq + j] * kLog2e : 0.f;
+      return (j < seq) ? load_ahead(carry + ((int64_t)b * (ntiles + 1) + mi + 1) * seq + j) : 0.f;
     };
     float next_lse = fetch_lse(ntiles - 1), next_dbar = fetch_dbar(ntiles - 1), next_carry = fetch_carry(ntiles - 1);
 #ifdef SA_BWD_TIMING
@@ -404,11 +414,12 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       const int mi = ntiles - 1 - it;
       const int i0 = mi * kTile;
       const bool diag = (mi == nj);
+      SA_MARK(marks, 12)
       if (tid < kTile) {
         lse_s[tid] = next_lse;
         dbar_s[tid] = next_dbar;
       }
-      ctx.cnl = next_carry;
+      ctx.cnl = next_carry * kLog2e;
       if (it + 1 < n_iter) {
         next_lse = fetch_lse(mi - 1);
         next_dbar = fetch_dbar(mi - 1);
@@ -432,35 +443,38 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         SA_MARK(marks, 7)
       }
 
-      // ---- dQ, dQ0 of this query tile: TMEM -> scaled fp32 staging in shared memory -> TMA reduce-add ------
-      mbar_wait(&bar_b, it & 1, status, 411);
-      tc_fence_after_sync();
-      SA_MARK(marks, 8)
-      {
+      // ---- dQ, then dQ0, of this query tile: TMEM -> scaled fp32 staging in shared memory (the dz / g tiles,
+      // which no MMA reads any more) -> TMA reduce-add.  dQ is staged while the dK0 / dQ0 MMAs still run.
+      auto stage_tile = [&](uint32_t col, uint8_t* dst) {
         const int c0 = wg * kChunk;                           // here the lane is a QUERY row, columns are d
-        uint32_t r[16], r0[16];
-        tmem_ld16(lane_base + kColDQ + c0, r);
-        tmem_ld16(lane_base + kColDQ0 + c0, r0);
+        uint32_t r[16];
+        tmem_ld16(lane_base + col + c0, r);
         tmem_ld_wait();
-        uint8_t* sq = smem + L::dz + (wg >> 1) * kRowTile;    // [128 queries][32 floats] tiles, 128-byte swizzle
-        uint8_t* sq0 = smem + L::g + (wg >> 1) * kRowTile;
+        uint8_t* sq = dst + (wg >> 1) * kRowTile;             // [128 queries][32 floats] tiles, 128-byte swizzle
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
-          const uint32_t off = swz_off(row, (wg & 1) * 4 + c);
-          *reinterpret_cast<float4*>(sq + off) =
+        for (int c = 0; c < 4; ++c)
+          *reinterpret_cast<float4*>(sq + swz_off(row, (wg & 1) * 4 + c)) =
               make_float4(__uint_as_float(r[4 * c]) * scale, __uint_as_float(r[4 * c + 1]) * scale,
                           __uint_as_float(r[4 * c + 2]) * scale, __uint_as_float(r[4 * c + 3]) * scale);
-          *reinterpret_cast<float4*>(sq0 + off) =
-              make_float4(__uint_as_float(r0[4 * c]) * scale, __uint_as_float(r0[4 * c + 1]) * scale,
-                          __uint_as_float(r0[4 * c + 2]) * scale, __uint_as_float(r0[4 * c + 3]) * scale);
-        }
-      }
-      fence_async_smem();
-      tc_fence_before_sync();
-      named_barrier(kComputeBarrier, kComputeThreads);
+        fence_async_smem();
+        tc_fence_before_sync();
+        named_barrier(kComputeBarrier, kComputeThreads);
+      };
+      mbar_wait(&bar_dq, it & 1, status, 412);
+      tc_fence_after_sync();
+      SA_MARK(marks, 8)
+      stage_tile(kColDQ, smem + L::dz);
       if (tid == 0) {
         tma_reduce_add_4d(&map_dq, smem + L::dz, 0, i0, n, 0);
         tma_reduce_add_4d(&map_dq, smem + L::dz + kRowTile, 32, i0, n, 0);
+        bulk_commit();
+      }
+      SA_MARK(marks, 10)
+      mbar_wait(&bar_b, it & 1, status, 411);
+      tc_fence_after_sync();
+      SA_MARK(marks, 11)
+      stage_tile(kColDQ0, smem + L::g);
+      if (tid == 0) {
         tma_reduce_add_4d(&map_dq0, smem + L::g, 0, i0, b, 0);
         tma_reduce_add_4d(&map_dq0, smem + L::g + kRowTile, 32, i0, b, 0);
         bulk_commit();
