@@ -428,6 +428,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       float sel_state = 0.f;         // selection of the tile's queries already visited, this key (raw logit units)
       SA_MARK(marks, 0)
 
+#pragma unroll 1
       for (int hf = 1; hf >= 0; --hf) {
         mbar_wait(&bar_a, a_phase, status, 410);
         a_phase ^= 1;
