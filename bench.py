@@ -43,6 +43,8 @@ WORKLOADS = {
     "c4": dict(batch=1, heads=16, seq=131072, dim=64, per_head=False, backward=False),
     # one cached decode step against a 131,071-token cache (the serving continuation of c4)
     "decode": dict(batch=1, heads=16, seq=131072, dim=64, per_head=False, backward=False),
+    # full decoder training step, data parallel (one sequence per GPU)
+    "c5": dict(batch=1, heads=16, seq=16384, dim=64, per_head=False, backward=True, layers=24),
 }
 METRIC = "selective-attn fwd+bwd tokens/s/GPU @T=16K bf16; % of tcgen05 bf16 peak"
 NOMINAL_BF16_TFLOPS = 2250.0
@@ -334,6 +336,78 @@ def run_decode(args, w, rank, world, device):
             "clocks": clocks}
 
 
+def run_decoder(args, w, rank, world, device):
+    """Full decoder training step (24 layers, d_model 1024, 16 heads x 64, GELU MLP 4096, pre-LN, no position
+    signal, vocab 50304, T = 16384, bf16 autocast, fused AdamW): forward, backward, optimizer step.  Data
+    parallel: one sequence per GPU, gradients all-reduced by DistributedDataParallel (NCCL, bucketed and
+    overlapped with the backward)."""
+    from selective_attention_b200.decoder import SelectiveDecoder, synthetic_batch
+
+    torch.manual_seed(0)
+    model = SelectiveDecoder(vocab_size=50304, n_layers=w["layers"], d_model=w["heads"] * w["dim"],
+                             n_heads=w["heads"]).to(device)
+    params = sum(p.numel() for p in model.parameters())
+    net = model
+    if world > 1:
+        net = torch.nn.parallel.DistributedDataParallel(model, device_ids=[device.index], gradient_as_bucket_view=True)
+    opt = torch.optim.AdamW(model.parameters(), lr=6e-4, weight_decay=0.1, betas=(0.9, 0.95), fused=True)
+    gen = torch.Generator("cpu").manual_seed(1000 + rank)
+    idx_h, tgt_h = synthetic_batch(w["batch"], w["seq"], 50304, 50256, gen)
+    idx_h, tgt_h = idx_h.pin_memory(), tgt_h.pin_memory()
+    loss_host = torch.empty((), dtype=torch.float32).pin_memory()
+
+    def step(host: bool, idx_d=None, tgt_d=None):
+        if host:
+            idx_d, tgt_d = idx_h.to(device, non_blocking=True), tgt_h.to(device, non_blocking=True)
+        with torch.autocast("cuda", dtype=torch.bfloat16):
+            loss = net(idx_d, tgt_d)
+        loss.backward()
+        torch.nn.utils.clip_grad_norm_(model.parameters(), 1.0)
+        opt.step()
+        opt.zero_grad(set_to_none=True)
+        if host:
+            loss_host.copy_(loss.detach(), non_blocking=True)
+        return loss
+
+    idx_d, tgt_d = idx_h.to(device), tgt_h.to(device)
+    times = {}
+    for host in (False, True):
+        for _ in range(args.warmup if not host else 1):
+            step(host, idx_d, tgt_d)
+        if world > 1:
+            torch.distributed.barrier()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        n_steps = args.steps if not host else max(1, min(args.steps, 3))
+        with ClockSampler(device.index) as sampler:
+            e0.record()
+            for _ in range(n_steps):
+                loss = step(host, idx_d, tgt_d)
+            e1.record()
+            if world > 1:
+                torch.distributed.barrier()
+            torch.cuda.synchronize()
+        times[host] = max_over_ranks(e0.elapsed_time(e1) / n_steps, world, device)
+        if not host:
+            clocks, last_loss = sampler.summary(), float(loss.detach())
+    if not math.isfinite(last_loss):
+        raise RuntimeError("the training loss is not finite")
+    tokens = w["batch"] * w["seq"]
+    attn_launches = 7 * w["layers"]
+    return {"metric": "decoder training step tokens/s (24L d1024 16x64, T=16384, bf16, selective attention)",
+            "value": whole_job_tokens_per_second(tokens, world, times[False]), "unit": "tokens/s", "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": times[False], "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": f"c5: decoder training step, {w['layers']} layers, d_model {w['heads'] * w['dim']}, "
+                                   f"{w['heads']} heads x {w['dim']}, GELU MLP x4, pre-LN, no position signal, vocab 50304, "
+                                   f"T={w['seq']}, {w['batch']} sequence(s) per GPU, AdamW, grad clip 1.0",
+                       "parameters": params, "parallelism": f"dp{world}", "loss": last_loss,
+                       "l2": "activations and weights far exceed the 126 MB L2"},
+            "e2e": {"value": whole_job_tokens_per_second(tokens, world, times[True]), "unit": "tokens/s",
+                    "ms_per_step": times[True], "h2d_bytes_per_step": 2 * tokens * 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": attn_launches * args.steps, "clocks": clocks}
+
+
 def cpu_baseline(seconds: float = 12.0) -> dict:
     """The CPU oracle (a port of the reference's paper listing and its backward algebra) on the
     reference's own CPU-sized case: B=2, H=4, T=1024, D=64, fp32, seed 0."""
@@ -398,6 +472,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--seq", type=int, default=None, help="override T (profiling on a small case)")
     ap.add_argument("--batch", type=int, default=None, help="override B (profiling on a small case)")
+    ap.add_argument("--layers", type=int, default=None, help="override the layer count of the c5 decoder")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
@@ -406,6 +481,8 @@ def main():
         w["seq"] = args.seq
     if args.batch:
         w["batch"] = args.batch
+    if args.layers and "layers" in w:
+        w["layers"] = args.layers
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -425,9 +502,10 @@ def main():
         torch.distributed.init_process_group("nccl", device_id=device)
     if args.warmup < 3:
         args.warmup = 3
-    line = run_decode(args, w, rank, world, device) if args.workload == "decode" else run_ours(args, w, rank, world, device)
+    runner = {"decode": run_decode, "c5": run_decoder}.get(args.workload, run_ours)
+    line = runner(args, w, rank, world, device)
     if rank == 0:
-        if world == 1 and not args.no_cpu_baseline and args.workload != "decode":
+        if world == 1 and not args.no_cpu_baseline and args.workload not in ("decode", "c5"):
             line["cpu_baseline"] = cpu_baseline()
         print(json.dumps(line), flush=True)
     if world > 1:
