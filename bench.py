@@ -214,10 +214,29 @@ def run_ours(args, w, rank, world, device):
     h2d = sum(t.numel() * t.element_size() for t in (pinned_in if w["backward"] else pinned_in[:3]))
     d2h = sum(t.numel() * t.element_size() for t in pinned_out)
 
-    def e2e_step():
-        qd, kd, vd = (t.to(device, non_blocking=True) for t in pinned_in[:3])
+    # Every step copies its own inputs in and its own results out; the copies of neighbouring steps run on
+    # their own streams, so step i's compute overlaps step i+1's upload and step i-1's download, as a serving
+    # or training loop that feeds the operator from host memory would arrange it.
+    s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
+    s_comp = torch.cuda.current_stream(device)
+    n_in = 4 if w["backward"] else 3
+    dev_in = [[torch.empty_like(t, device=device) for t in pinned_in[:n_in]] for _ in range(2)]
+    uploaded = [torch.cuda.Event() for _ in range(2)]
+    consumed = [torch.cuda.Event() for _ in range(2)]
+    downloaded = torch.cuda.Event()
+
+    def e2e_step(i: int):
+        slot = i & 1
+        with torch.cuda.stream(s_in):
+            if i >= 2:
+                s_in.wait_event(consumed[slot])            # the compute of step i - 2 has read this slot
+            for dst, src in zip(dev_in[slot], pinned_in):
+                dst.copy_(src, non_blocking=True)
+            uploaded[slot].record(s_in)
+        s_comp.wait_event(uploaded[slot])
+        qd, kd, vd = (t.detach() for t in dev_in[slot][:3])
         if w["backward"]:
-            dd = pinned_in[3].to(device, non_blocking=True).float()
+            dd = dev_in[slot][3].float()
             qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
             out = kernels.selective_attention(qd, kd, vd)
             out.backward(dd)
@@ -225,18 +244,26 @@ def run_ours(args, w, rank, world, device):
         else:
             with torch.no_grad():
                 results = (kernels.selective_attention_forward(qd, kd, vd).to(torch.bfloat16),)
-        for dst, src in zip(pinned_out, results):
-            dst.copy_(src, non_blocking=True)
+        consumed[slot].record(s_comp)
+        done = torch.cuda.Event()
+        done.record(s_comp)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            for dst, src in zip(pinned_out, results):
+                src.record_stream(s_out)
+                dst.copy_(src, non_blocking=True)
+            downloaded.record(s_out)
 
-    e2e_steps = max(1, min(args.steps, 5))
-    for _ in range(min(args.warmup, 2)):
-        e2e_step()
+    e2e_steps = max(2, min(args.steps, 6))
+    for i in range(2):
+        e2e_step(i)
     barrier()
     s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
-    s0.record()
-    for _ in range(e2e_steps):
-        e2e_step()
-    s1.record()
+    s0.record(s_in)
+    for i in range(e2e_steps):
+        e2e_step(i)
+    s_comp.wait_event(downloaded)
+    s1.record(s_comp)
     barrier()
     e2e_ms = max_over_ranks(s0.elapsed_time(s1) / e2e_steps, world, device)
 
