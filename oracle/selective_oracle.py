@@ -155,7 +155,8 @@ def tail_rows(q, k, v, tail: int, exempt: int = 1, chunk: int = 1024, dtype=torc
     """Outputs of the last ``tail`` queries and the per-key totals, without a (T, T) tensor."""
     b, h, seq, dim = q.shape
     s = 1.0 / math.sqrt(dim)
-    keys = torch.arange(seq)
+    dev = q.device                      # runs where its inputs live (dense torch ops either way)
+    keys = torch.arange(seq, device=dev)
     q0, k0 = q[:, 0].to(dtype), k[:, 0].to(dtype)
 
     def sel(rows):
@@ -164,10 +165,10 @@ def tail_rows(q, k, v, tail: int, exempt: int = 1, chunk: int = 1024, dtype=torc
         return torch.relu(l0) * ok
 
     start = seq - tail
-    earlier = torch.zeros(b, seq, dtype=dtype)
+    earlier = torch.zeros(b, seq, dtype=dtype, device=dev)
     for a in range(0, start, chunk):
-        earlier += sel(torch.arange(a, min(a + chunk, start))).sum(dim=1)
-    rows = torch.arange(start, seq)
+        earlier += sel(torch.arange(a, min(a + chunk, start), device=dev)).sum(dim=1)
+    rows = torch.arange(start, seq, device=dev)
     st = sel(rows)
     history = earlier[:, None, :] + torch.cumsum(st, dim=1) - st
     z = (q[:, :, rows].to(dtype) @ k.to(dtype).transpose(-2, -1)) * s - history[:, None]

@@ -28,8 +28,16 @@ def test_forward_tail_rows_and_totals_at_benchmark_lengths(seq, tail):
     out, aux = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda(), return_aux=True)
     torch.cuda.synchronize()
     assert _lib.device_status() == 0
-    rows, want, total = oracle.tail_rows(q.float(), k.float(), v.float(), tail=tail, chunk=4096)
-    got = out[:, :, rows].cpu()
+    dev = "cuda" if seq > 100_000 else "cpu"               # the oracle's dense torch ops; on the device when long
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        rows, want, total = oracle.tail_rows(q.float().to(dev), k.float().to(dev), v.float().to(dev), tail=tail,
+                                             chunk=4096)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    rows, want, total = rows.cpu(), want.cpu(), total.cpu()
+    got = out[:, :, rows.cuda()].cpu()
     assert torch.isfinite(out).all()
     assert _rel(got, want) < 2e-2 and (got - want).abs().max() < 3e-2
     torch.testing.assert_close(aux["selected_total"].cpu(), total, atol=2e-2, rtol=2e-3)
@@ -68,3 +76,27 @@ def test_backward_is_linear_in_the_cotangent_at_16k():
     for name, a, b, both in zip(("dq", "dk", "dv"), *grads):
         assert torch.isfinite(both).all()
         assert _rel(a + b, both) < 2e-2, (name, _rel(a + b, both))
+
+
+def test_forward_past_the_int32_offset_limit():
+    """T = 270,000 (the reference's own long-sequence check, tests/test_selective_kernels.py:333-345): the carry
+    of the CUDA-core engine is (1, 8438, 270000) fp32 = 9.1 GB, whose element offsets pass 2^31.  fp32 inputs,
+    exact products, head_dim 16; last 1000 rows and the per-key totals against the chunked oracle."""
+    seq = 270_000
+    if torch.cuda.get_device_properties(0).total_memory < 24 * 2**30:
+        pytest.skip("needs a 24 GB GPU")
+    g = torch.Generator("cpu").manual_seed(31)
+    q, k, v = (torch.randn(1, 2, seq, 16, generator=g).cuda() for _ in range(3))
+    got, aux = kernels.selective_attention_forward(q, k, v, dot_precision="ieee", return_aux=True)
+    torch.cuda.synchronize()
+    assert aux["carry"].numel() > 2**31
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:                                                     # the oracle's dense torch ops, on the device for speed
+        rows, want, total = oracle.tail_rows(q, k, v, tail=1000, chunk=8192)
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    torch.testing.assert_close(got[:, :, rows], want, atol=2e-4, rtol=2e-4)
+    torch.testing.assert_close(aux["selected_total"], total, atol=1e-2, rtol=1e-3)
+    del got, aux
+    torch.cuda.empty_cache()
