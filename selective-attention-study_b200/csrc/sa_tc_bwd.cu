@@ -229,7 +229,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar_kv, bar_ld[2], bar_a, bar_b, bar_dq, bar_half, bar_early;
+  __shared__ uint64_t bar_kv, bar_ld[2], bar_a, bar_b, bar_dq, bar_half[2], bar_early;
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(16) float lse_s[kTile];
   __shared__ __align__(16) float dbar_s[kTile];
@@ -244,7 +244,11 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     mbar_init(&bar_a, 1);
     mbar_init(&bar_b, 1);
     mbar_init(&bar_dq, 1);
-    mbar_init(&bar_half, kComputeThreads / 32);
+    // bar_half: one per half, each used once per tile, so the waiter can never see one complete two phases between
+    // two of its polls.  bar_early needs no such split: each arrival needs scores that are issued after the
+    // previous arrival was observed.
+    mbar_init(&bar_half[0], kComputeThreads / 32);
+    mbar_init(&bar_half[1], kComputeThreads / 32);
     mbar_init(&bar_early, 1);
     mbar_init_fence();
   }
@@ -328,17 +332,17 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       tc_fence_after_sync();
       issue_scores(0, 1);
 
-      uint32_t half_phase = 0, early_phase = 0;
+      uint32_t early_phase = 0;
       for (int it = 0; it < n_iter; ++it) {
         // half 1: P^T and dz are ready and the score columns are free while the g pass still runs
+        const uint32_t ph = it & 1;
         mbar_wait(&bar_early, early_phase, status, 402);
         early_phase ^= 1;
         tc_fence_after_sync();
         issue_dv(it, 1, it == 0);                             // reads P^T before the next scores overwrite it
         issue_scores(it, 0);
         issue_dk_only(it, 1, it == 0);
-        mbar_wait(&bar_half, half_phase, status, 403);       // half 1: g written
-        half_phase ^= 1;
+        mbar_wait(&bar_half[1], ph, status, 403);            // half 1: g written
         tc_fence_after_sync();
         issue_dk0_only(it, 1, it == 0);
         // half 0
@@ -351,8 +355,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         for (int ks = 0; ks < 8; ++ks)                        // dQ = dz K: A M-major, K = key index
           mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
         mma_commit(&bar_dq);                                  // dQ done => every MMA reading the dz tiles is done
-        mbar_wait(&bar_half, half_phase, status, 407);       // half 0: g written
-        half_phase ^= 1;
+        mbar_wait(&bar_half[0], ph, status, 407);            // half 0: g written
         tc_fence_after_sync();
         issue_dk0_only(it, 0, false);
 #pragma unroll
@@ -440,7 +443,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         else process_half<false>(ctx, sel_state, dz_state SA_MARKS_PASS);
         fence_async_smem();                                    // g tile half -> visible to the MMAs
         __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_half);
+        if (lane == 0) mbar_arrive(&bar_half[hf]);
         SA_MARK(marks, 7)
       }
 
