@@ -4,6 +4,8 @@
 //   fold/cast dq = cast(dq_acc + [head 0] dq0)            (reference: kernels.py:662-666)
 //   decode    one cached decode step                       (reference: src/selective_attention/mixers.py:115-130)
 #include "sa_common.cuh"
+#include "sa_tc_host.cuh"
+#include "sa_tc_ptx.cuh"
 
 namespace sa {
 namespace {
@@ -89,23 +91,27 @@ __global__ void __launch_bounds__(256) fold_cast_kernel(const float* __restrict_
 
 // ---- decode -----------------------------------------------------------------------------------------
 constexpr int kDecThreads = 128;
-constexpr int kDecSplitMin = 512;             // keys per CTA: a multiple of 512, chosen per call so that the grid
-constexpr int kDecSplitMax = 4096;            //   has a few waves of CTAs and the combine pass stays short
+constexpr int kDecSplitMin = 512;             // keys per CTA: a multiple of 512, at least 512
+constexpr int kDecCtasPerSm = 3;              // attend CTAs resident per SM (64 KB of stages each)
 
-// Keys per CTA for `t` cached keys and `rows` = batch * heads query rows.
+// Keys per CTA for `t` cached keys and `rows` = batch * heads query rows: the grid is about one full wave of
+// resident CTAs, so no SM is left with a straggler and the combine pass stays short.
 static int decode_split_keys(int t, int rows) {
-  const int target_splits = (148 * 8 + rows - 1) / rows;            // about eight CTAs per SM in total
+  int target_splits = 148 * kDecCtasPerSm / rows;
+  if (target_splits < 1) target_splits = 1;
   int keys = (t + target_splits - 1) / target_splits;
   keys = (keys + kDecSplitMin - 1) / kDecSplitMin * kDecSplitMin;
   if (keys < kDecSplitMin) keys = kDecSplitMin;
-  if (keys > kDecSplitMax) keys = kDecSplitMax;
   return keys;
 }
 
+// Writes the new key and value into the cache and clears the tickets the attend kernel counts CTAs with.
 template <typename T>
 __global__ void append_kernel(const T* __restrict__ k1, const T* __restrict__ v1, T* __restrict__ kc,
-                              T* __restrict__ vc, int rows, int capacity, int length, int D) {
+                              T* __restrict__ vc, int rows, int capacity, int length, int D,
+                              unsigned int* __restrict__ tickets, int n_tickets) {
   int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx < n_tickets) tickets[idx] = 0u;
   if (idx >= rows * D) return;
   int n = idx / D, d = idx - n * D;
   int64_t dst = ((int64_t)n * capacity + length) * D + d;
@@ -128,137 +134,34 @@ __device__ __forceinline__ void load8(const T* p, float (&x)[8]) {
   }
 }
 
-// grid (splits, batch * heads).  A group of D / 8 lanes owns one key per step; every thread keeps kUnroll
-// 16-byte loads in flight so that a CTA streams its 512 keys of K, then of V, at memory speed.
-template <typename T, int D>
-__global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
-    const T* __restrict__ q1, const T* __restrict__ kc, const T* __restrict__ vc, const float* __restrict__ selected,
-    float* __restrict__ partial, float* __restrict__ sel_new, int heads, int groups, int t, int capacity,
-    int exempt, float scale, int split_keys) {
-  constexpr int kLanes = D / 8;                       // lanes per key
-  constexpr int kKeysPerStep = kDecThreads / kLanes;  // keys the CTA covers per step
-  constexpr int kUnroll = 4;
-  __shared__ float zs[kDecSplitMax];
-  __shared__ float red[kDecThreads];
-  __shared__ float accs[kKeysPerStep][D];
-
-  const int n = blockIdx.y, split = blockIdx.x;
-  const int b = n / heads, h = n - b * heads;
-  const int per = heads / groups, g = h / per;
-  const bool selector = (h - g * per) == 0;
-  const int c0 = split * split_keys, c1 = min(t, c0 + split_keys);
-  const int grp = threadIdx.x / kLanes, lane = threadIdx.x % kLanes;
-
-  float qv[8];
-  load8<T>(q1 + (int64_t)n * D + lane * 8, qv);
-  const T* kb = kc + (int64_t)n * capacity * D;
-  const T* vb = vc + (int64_t)n * capacity * D;
-  const float* selb = selected + ((int64_t)b * groups + g) * capacity;
-  float* selnb = sel_new + ((int64_t)b * groups + g) * t;
-
-  float local_max = -INFINITY;
-  for (int base = c0; base < c1; base += kKeysPerStep * kUnroll) {   // uniform trip count: the shuffles need whole warps
-    float dot[kUnroll];
-    float kx[kUnroll][8];
-    const bool full = base + kKeysPerStep * kUnroll <= c1;       // CTA-uniform: loads without per-key guards
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int j = base + u * kKeysPerStep + grp;
-      if (full || j < c1) {
-        load8<T>(kb + (int64_t)j * D + lane * 8, kx[u]);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) kx[u][e] = 0.f;
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      dot[u] = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) dot[u] = fmaf(qv[e], kx[u][e], dot[u]);
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-#pragma unroll
-      for (int s = kLanes / 2; s > 0; s >>= 1) dot[u] += __shfl_xor_sync(0xffffffffu, dot[u], s);
-      const int j = base + u * kKeysPerStep + grp;
-      if (j < c1) {
-        const float raw = dot[u] * scale;
-        const float z = (raw - selb[j]) * kLog2e;
-        if (lane == 0) {
-          zs[j - c0] = z;
-          if (selector) selnb[j] = (j >= exempt && j != t - 1 && raw > 0.f) ? raw : 0.f;
-        }
-        local_max = fmaxf(local_max, z);
-      }
-    }
-  }
-  red[threadIdx.x] = local_max;
-  __syncthreads();
-  for (int s = kDecThreads / 2; s > 0; s >>= 1) {
-    if (threadIdx.x < s) red[threadIdx.x] = fmaxf(red[threadIdx.x], red[threadIdx.x + s]);
-    __syncthreads();
-  }
-  const float m = red[0];
-  __syncthreads();
-
-  float acc[8];
-#pragma unroll
-  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-  float den = 0.f;
-  for (int base = c0; base < c1; base += kKeysPerStep * kUnroll) {
-    float vx[kUnroll][8], w[kUnroll];
-    const bool full = base + kKeysPerStep * kUnroll <= c1;
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int j = base + u * kKeysPerStep + grp;
-      if (full || j < c1) {
-        load8<T>(vb + (int64_t)j * D + lane * 8, vx[u]);
-        w[u] = exp2f(zs[j - c0] - m);
-      } else {
-        w[u] = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) vx[u][e] = 0.f;
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      den += w[u];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = fmaf(w[u], vx[u][e], acc[e]);
-    }
-  }
-#pragma unroll
-  for (int e = 0; e < 8; ++e) accs[grp][lane * 8 + e] = acc[e];
-  red[threadIdx.x] = (lane == 0) ? den : 0.f;
-  __syncthreads();
-  for (int s = kDecThreads / 2; s > 0; s >>= 1) {
-    if (threadIdx.x < s) red[threadIdx.x] += red[threadIdx.x + s];
-    __syncthreads();
-  }
-  float* prow = partial + ((int64_t)n * gridDim.x + split) * (D + 2);
-  for (int d = threadIdx.x; d < D; d += kDecThreads) {
-    float sum = 0.f;
-    for (int gg = 0; gg < kKeysPerStep; ++gg) sum += accs[gg][d];
-    prow[d] = sum;
-  }
-  if (threadIdx.x == 0) {
-    prow[D] = m;
-    prow[D + 1] = red[0];
-  }
+// 16-byte load of 8 (bf16 / fp16) or two 16-byte loads of 8 fp32 elements from shared memory, converted to fp32.
+template <typename T>
+__device__ __forceinline__ void load8_shared(const uint8_t* p, float (&x)[8]) {
+  load8<T>(reinterpret_cast<const T*>(p), x);
 }
 
-// grid (batch * heads), 128 threads: merges the per-split partial softmaxes.  The global maximum is found
-// first so that the weighted sums over splits have no serial dependence: warp w folds splits w, w + 4, ...
-// (lane l owns output columns l, l + 32, ...), then the four warps are added through shared memory.
-__global__ void __launch_bounds__(128) decode_combine_kernel(const float* __restrict__ partial, float* __restrict__ y,
-                                                             int splits, int D) {
-  __shared__ float part[4][128 + 1];
-  __shared__ float red[128];
-  const int n = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const float* prow = partial + (int64_t)n * splits * (D + 2);
+// Untiled bulk copy global -> shared memory, completion counted in bytes on an mbarrier.  Both addresses and the
+// size are multiples of 16 bytes.
+__device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(
+                   tc::smem_u32(smem_dst)),
+               "l"(gmem_src), "r"(bytes), "r"(tc::smem_u32(bar))
+               : "memory");
+}
+
+constexpr int kDecStages = 4;                   // stages of 8 KB of K + 8 KB of V
+constexpr int kDecStageBytes = 8192;            // per tensor
+constexpr size_t kDecSmemBytes = (size_t)kDecStages * 2 * kDecStageBytes + 128;
+
+// Merges the per-split partial softmaxes of one query row; called by all 128 threads of a CTA.  The global
+// maximum is found first so that the weighted sums over splits have no serial dependence: warp w folds splits
+// w, w + 4, ... (lane l owns output columns l, l + 32, ...), then the four warps are added through shared memory.
+// The partials were written by other CTAs: they are read past the L1 cache.
+__device__ __forceinline__ void decode_combine_row(const float* prow, float* yrow, int splits, int D,
+                                                   float (*part)[128 + 1], float* red) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   float m = -INFINITY;
-  for (int s = threadIdx.x; s < splits; s += 128) m = fmaxf(m, prow[(int64_t)s * (D + 2) + D]);
+  for (int s = threadIdx.x; s < splits; s += 128) m = fmaxf(m, __ldcg(prow + (int64_t)s * (D + 2) + D));
   red[threadIdx.x] = m;
   __syncthreads();
   for (int st = 64; st > 0; st >>= 1) {
@@ -270,12 +173,12 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const float* __rest
 #pragma unroll 4
   for (int s = warp; s < splits; s += 4) {
     const float* p = prow + (int64_t)s * (D + 2);
-    const float c = exp2f(p[D] - m);
-    den = fmaf(p[D + 1], c, den);
+    const float c = exp2f(__ldcg(p + D) - m);
+    den = fmaf(__ldcg(p + D + 1), c, den);
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       const int d = lane + 32 * u;
-      if (d < D) num[u] = fmaf(p[d], c, num[u]);
+      if (d < D) num[u] = fmaf(__ldcg(p + d), c, num[u]);
     }
   }
 #pragma unroll
@@ -289,16 +192,191 @@ __global__ void __launch_bounds__(128) decode_combine_kernel(const float* __rest
   if (d < D) {
     const float nn = part[0][d] + part[1][d] + part[2][d] + part[3][d];
     const float dd = part[0][128] + part[1][128] + part[2][128] + part[3][128];
-    y[(int64_t)n * D + d] = nn / dd;
+    yrow[d] = nn / dd;
   }
 }
 
-__global__ void decode_update_kernel(float* __restrict__ selected, const float* __restrict__ sel_new, int rows, int t,
-                                     int capacity) {
-  int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= (int64_t)rows * t) return;
-  int r = (int)(idx / t), j = (int)(idx - (int64_t)r * t);
-  selected[(int64_t)r * capacity + j] += sel_new[idx];
+// grid (splits, batch * heads).  One thread streams the CTA's keys of K and V through a ring of shared-memory
+// stages with bulk copies, kDecStages - 1 stages (48 KB) ahead of the arithmetic, so the bytes in flight do not
+// depend on how the arithmetic is scheduled.  A group of D / 8 lanes owns every (128 / lanes)-th key of a stage
+// and keeps its own running maximum, denominator and weighted sum (one pass, rescaled when its maximum grows);
+// the groups are merged at the end.
+template <typename T, int D>
+__global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
+    const T* __restrict__ q1, const T* __restrict__ kc, const T* __restrict__ vc, float* selected,
+    float* __restrict__ partial, float* __restrict__ sel_new, int heads, int groups, int t, int capacity,
+    int exempt, float scale, int split_keys, unsigned int* status, float* __restrict__ y, unsigned int* __restrict__ row_tickets, unsigned int* __restrict__ split_tickets) {
+  constexpr int kLanes = D / 8;                                   // lanes per key
+  constexpr int kGroups = kDecThreads / kLanes;                   // keys the CTA covers per step
+  constexpr int kRowBytes = D * (int)sizeof(T);
+  constexpr int kStageKeys = kDecStageBytes / kRowBytes;
+  constexpr int kPer = kStageKeys / kGroups;                      // keys per group per stage (4, fp32: 2)
+  static_assert(kPer >= 1 && kPer * kGroups == kStageKeys, "stage layout");
+  extern __shared__ uint8_t dec_smem_raw[];
+  uint8_t* ring = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(dec_smem_raw) + 127) & ~uintptr_t(127));
+  __shared__ uint64_t full[kDecStages];
+  __shared__ float red[kDecThreads];
+  __shared__ float gmax[kGroups];
+  __shared__ float accs[kGroups][D];
+  __shared__ float part[4][128 + 1];
+  __shared__ unsigned int ticket_s[2];
+
+  const int n = blockIdx.y, split = blockIdx.x;
+  const int b = n / heads, h = n - b * heads;
+  const int per = heads / groups, g = h / per;
+  const bool selector = (h - g * per) == 0;
+  const int c0 = split * split_keys, c1 = min(t, c0 + split_keys);
+  const int n_stages = (c1 - c0 + kStageKeys - 1) / kStageKeys;
+  const int grp = threadIdx.x / kLanes, lane = threadIdx.x % kLanes;
+  const uint8_t* kb = reinterpret_cast<const uint8_t*>(kc + (int64_t)n * capacity * D);
+  const uint8_t* vb = reinterpret_cast<const uint8_t*>(vc + (int64_t)n * capacity * D);
+
+  auto issue = [&](int st) {                                      // thread 0 only
+    const int j0 = c0 + st * kStageKeys;
+    const uint32_t bytes = (uint32_t)(min(kStageKeys, c1 - j0) * kRowBytes);
+    uint8_t* dst = ring + (size_t)(st % kDecStages) * 2 * kDecStageBytes;
+    uint64_t* bar = &full[st % kDecStages];
+    tc::mbar_expect_tx(bar, 2 * bytes);
+    bulk_load(dst, kb + (int64_t)j0 * kRowBytes, bytes, bar);
+    bulk_load(dst + kDecStageBytes, vb + (int64_t)j0 * kRowBytes, bytes, bar);
+  };
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < kDecStages; ++st) tc::mbar_init(&full[st], 1);
+    tc::mbar_init_fence();
+    for (int st = 0; st < min(kDecStages - 1, n_stages); ++st) issue(st);
+  }
+
+  float qv[8];
+  load8<T>(q1 + (int64_t)n * D + lane * 8, qv);
+  const float* selb = selected + ((int64_t)b * groups + g) * capacity;
+  float* selnb = sel_new + ((int64_t)b * groups + g) * t;
+  __syncthreads();                                                // barriers initialised before anyone waits
+
+  float m = -INFINITY, den = 0.f, acc[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int st = 0; st < n_stages; ++st) {
+    const int j0 = c0 + st * kStageKeys;
+    float sv[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {                              // the history sums arrive while the stage is awaited
+      const int j = j0 + u * kGroups + grp;
+      sv[u] = (j < c1) ? selb[j] : 0.f;
+    }
+    // the slot that stage st + kDecStages - 1 uses was read in iteration st - 1; every thread is past it
+    if (threadIdx.x == 0 && st + kDecStages - 1 < n_stages) issue(st + kDecStages - 1);
+    tc::mbar_wait(&full[st % kDecStages], (st / kDecStages) & 1, status, 600);
+    const uint8_t* ks = ring + (size_t)(st % kDecStages) * 2 * kDecStageBytes;
+    const uint8_t* vs = ks + kDecStageBytes;
+
+    float z[kPer];
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      float kx[8];
+      load8_shared<T>(ks + (u * kGroups + grp) * kRowBytes + lane * 8 * (int)sizeof(T), kx);
+      float dot = 0.f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) dot = fmaf(qv[e], kx[e], dot);
+      z[u] = dot;
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+#pragma unroll
+      for (int sft = kLanes / 2; sft > 0; sft >>= 1) z[u] += __shfl_xor_sync(0xffffffffu, z[u], sft);
+    }
+    float mx = m;
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      const int j = j0 + u * kGroups + grp;
+      const float raw = z[u] * scale;
+      if (j < c1) {
+        if (selector && lane == 0) selnb[j] = (j >= exempt && j != t - 1 && raw > 0.f) ? raw : 0.f;
+        z[u] = (raw - sv[u]) * kLog2e;
+      } else {
+        z[u] = -INFINITY;                                         // past the end: the stage holds no data there
+      }
+      mx = fmaxf(mx, z[u]);
+    }
+    if (mx > m) {                                                 // the group's maximum grew: rescale its sums
+      const float c = exp2f(m - mx);                              // m = -inf on the first keys: c = 0
+      den *= c;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= c;
+      m = mx;
+    }
+#pragma unroll
+    for (int u = 0; u < kPer; ++u) {
+      if (z[u] != -INFINITY) {
+        const float w = exp2f(z[u] - m);
+        float vx[8];
+        load8_shared<T>(vs + (u * kGroups + grp) * kRowBytes + lane * 8 * (int)sizeof(T), vx);
+        den += w;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) acc[e] = fmaf(w, vx[e], acc[e]);
+      }
+    }
+    __syncthreads();                                              // stage read by everyone: its slot may be refilled
+  }
+
+  // merge the groups: common maximum, then rescaled sums
+  if (lane == 0) gmax[grp] = m;
+  __syncthreads();
+  float cta_max = -INFINITY;
+#pragma unroll 4
+  for (int gg = 0; gg < kGroups; ++gg) cta_max = fmaxf(cta_max, gmax[gg]);
+  const float c = (m == -INFINITY) ? 0.f : exp2f(m - cta_max);   // a group that saw no key contributes nothing
+#pragma unroll
+  for (int e = 0; e < 8; ++e) accs[grp][lane * 8 + e] = acc[e] * c;
+  red[threadIdx.x] = (lane == 0) ? den * c : 0.f;
+  __syncthreads();
+  for (int sft = kDecThreads / 2; sft > 0; sft >>= 1) {
+    if (threadIdx.x < sft) red[threadIdx.x] += red[threadIdx.x + sft];
+    __syncthreads();
+  }
+  float* prow = partial + ((int64_t)n * gridDim.x + split) * (D + 2);
+  for (int d = threadIdx.x; d < D; d += kDecThreads) {
+    float sum = 0.f;
+    for (int gg = 0; gg < kGroups; ++gg) sum += accs[gg][d];
+    prow[d] = sum;
+  }
+  if (threadIdx.x == 0) {
+    prow[D] = cta_max;
+    prow[D + 1] = red[0];
+  }
+
+  // The last CTA of a query row merges the row's partials into y; the last of the `per` heads that share a
+  // history vector to finish a key range adds the new selection of that range to it (every reader is done).
+  __threadfence();                                                // partials and sel_new visible before the ticket
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    ticket_s[0] = atomicAdd(&row_tickets[n], 1u);
+    ticket_s[1] = atomicAdd(&split_tickets[((int64_t)b * groups + g) * gridDim.x + split], 1u);
+  }
+  __syncthreads();
+  const bool last_of_row = ticket_s[0] == gridDim.x - 1;
+  const bool last_of_range = ticket_s[1] == (unsigned)per - 1;
+  if (!last_of_row && !last_of_range) return;
+  __threadfence();
+  if (last_of_range) {
+    float* sel_rw = selected + ((int64_t)b * groups + g) * capacity;
+    constexpr int kBatch = 8;                                     // independent loads in flight per thread
+    for (int base = c0 + threadIdx.x; base < c1; base += kDecThreads * kBatch) {
+      float old_v[kBatch], new_v[kBatch];
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int j = base + u * kDecThreads;
+        old_v[u] = (j < c1) ? __ldcg(sel_rw + j) : 0.f;
+        new_v[u] = (j < c1) ? __ldcg(selnb + j) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < kBatch; ++u) {
+        const int j = base + u * kDecThreads;
+        if (j < c1) sel_rw[j] = old_v[u] + new_v[u];
+      }
+    }
+  }
+  if (last_of_row)
+    decode_combine_row(partial + (int64_t)n * gridDim.x * (D + 2), y + (int64_t)n * D, gridDim.x, D, part, red);
 }
 
 template <typename T>
@@ -309,20 +387,31 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
   const int split_keys = decode_split_keys(t, rows);
   const int splits = (t + split_keys - 1) / split_keys;
   float* partial = ws;
-  float* sel_new = ws + (size_t)rows * splits * (D + 2);
-  append_kernel<T><<<(rows * D + 255) / 256, 256, 0, s>>>(static_cast<const T*>(k1), static_cast<const T*>(v1),
-                                                         static_cast<T*>(kc), static_cast<T*>(vc), rows, capacity,
-                                                         length, D);
+  float* sel_new = partial + (size_t)rows * splits * (D + 2);
+  unsigned int* row_tickets = reinterpret_cast<unsigned int*>(sel_new + (size_t)batch * groups * t);
+  unsigned int* split_tickets = row_tickets + rows;
+  const int n_tickets = rows + batch * groups * splits;
+  const int append_threads = rows * D > n_tickets ? rows * D : n_tickets;
+  ProfileScope prof(SA_KERNEL_DECODE, s);   // the whole step: append, then attend with its merge and update
+  append_kernel<T><<<(append_threads + 255) / 256, 256, 0, s>>>(
+      static_cast<const T*>(k1), static_cast<const T*>(v1), static_cast<T*>(kc), static_cast<T*>(vc), rows, capacity,
+      length, D, row_tickets, n_tickets);
   SA_CUDA_CHECK(cudaGetLastError());
   dim3 grid(splits, rows);
-  ProfileScope prof(SA_KERNEL_DECODE, s);   // the whole step: append, attend, combine, update
   const float scale = 1.0f / sqrtf((float)D);
   const T* q = static_cast<const T*>(q1);
   const T* kk = static_cast<const T*>(kc);
   const T* vv = static_cast<const T*>(vc);
-#define SA_DECODE_LAUNCH(DIM)                                                                                   \
-  decode_attend_kernel<T, DIM><<<grid, kDecThreads, 0, s>>>(q, kk, vv, selected, partial, sel_new, heads, groups, \
-                                                            t, capacity, exempt, scale, split_keys)
+  unsigned int* status = nullptr;
+  if (int st = tc::status_word(&status)) return st;
+#define SA_DECODE_LAUNCH(DIM)                                                                                      \
+  do {                                                                                                             \
+    SA_CUDA_CHECK(cudaFuncSetAttribute(decode_attend_kernel<T, DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
+                                       (int)kDecSmemBytes));                                                       \
+    decode_attend_kernel<T, DIM><<<grid, kDecThreads, kDecSmemBytes, s>>>(                                         \
+        q, kk, vv, selected, partial, sel_new, heads, groups, t, capacity, exempt, scale, split_keys, status,      \
+        y, row_tickets, split_tickets);                                                                           \
+  } while (0)
   switch (D) {
     case 16: SA_DECODE_LAUNCH(16); break;
     case 32: SA_DECODE_LAUNCH(32); break;
@@ -331,11 +420,6 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
     default: return SA_ERR_UNSUPPORTED;
   }
 #undef SA_DECODE_LAUNCH
-  SA_CUDA_CHECK(cudaGetLastError());
-  decode_combine_kernel<<<rows, 128, 0, s>>>(partial, y, splits, D);
-  SA_CUDA_CHECK(cudaGetLastError());
-  const int64_t upd = (int64_t)batch * groups * t;
-  decode_update_kernel<<<(unsigned)((upd + 255) / 256), 256, 0, s>>>(selected, sel_new, batch * groups, t, capacity);
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;
 }
@@ -377,7 +461,8 @@ int launch_fold_cast(const float* acc, const float* acc0, void* dst, int dtype, 
 size_t decode_workspace_floats(int batch, int heads, int groups, int length, int head_dim) {
   const int t = length + 1;
   const size_t splits = (size_t)(t + kDecSplitMin - 1) / kDecSplitMin;       // upper bound: the smallest split size
-  return (size_t)batch * heads * splits * (head_dim + 2) + (size_t)batch * groups * t;
+  return (size_t)batch * heads * splits * (head_dim + 2) + (size_t)batch * groups * t   // partials, new selection
+         + (size_t)batch * heads + (size_t)batch * groups * splits;                       // tickets
 }
 
 int decode_step(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim, int exempt,
