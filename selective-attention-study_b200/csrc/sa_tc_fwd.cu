@@ -161,7 +161,7 @@ __global__ void __launch_bounds__(256) scan_kernel(float* __restrict__ carry, fl
 template <int D>
 struct FwdSmem {
   static constexpr int DK = D / 64;
-  static constexpr int q = 0;
+  static constexpr int q = 0;                         // landing tiles of Q, then (D = 64: with q0) the triangular ones
   static constexpr int q0 = q + DK * kRowTile;
   static constexpr int selp = q0 + DK * kRowTile;     // [128][64]: selection (B operand), then P (A operand)
   static constexpr int k = selp + kRowTile;           // DK tiles [64][64]
@@ -172,6 +172,10 @@ struct FwdSmem {
 
 constexpr int kFwdThreads = 256;      // two warpgroups: each owns 32 of a step's 64 key columns and half of D
 
+// One 128-query tile of one head.  Key steps of 64 run from the diagonal back to key 0: the keys nearest the query
+// carry the least history, so the running maximum settles within the first steps and the output accumulator,
+// which stays in TMEM for the whole loop, is rescaled only while the maximum still moves.  Per step the tensor
+// pipe gets two batches: (P V of the previous step, L0 and S of this one) and the triangular running-sum MMA.
 template <int D>
 __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
     forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -181,11 +185,10 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
   using L = FwdSmem<D>;
   constexpr int DK = D / 64;
   constexpr int DH = D / 2;                                   // output columns per warpgroup
-  // TMEM columns.  The stationary A operands live in TMEM as bf16 pairs (Q, Q0: D / 2 columns each; the
-  // strictly-lower-triangular ones matrix: 64 columns), so the per-step MMAs fetch only B from shared memory.
+  // TMEM columns: S and L0 (fp32, 64 each), the output accumulator (D), and the stationary A operands Q and Q0 as
+  // bf16 pairs (D / 2 columns each), so the per-step logit MMAs fetch only B from shared memory.
   constexpr uint32_t kTmemCols = (D == 64) ? 256 : 512;
-  constexpr uint32_t kColS = 0, kColL = 64, kColPV = (D == 64) ? 64 : 128;
-  constexpr uint32_t kColTri = (D == 64) ? 128 : 256, kColQ = kColTri + 64, kColQ0 = kColQ + D / 2;
+  constexpr uint32_t kColS = 0, kColL = 64, kColO = 128, kColQ = kColO + D, kColQ0 = kColQ + D / 2;
 
   const int nrows = gridDim.x / ntiles;                       // batch * heads
   const int mi = ntiles - 1 - (int)(blockIdx.x / nrows);      // heaviest query tiles first
@@ -235,18 +238,8 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
       tma_load_4d(smem + L::q + s * kRowTile, &map_q, &bar_q, s * 64, i0, h, b);
       tma_load_4d(smem + L::q0 + s * kRowTile, &map_q, &bar_q, s * 64, i0, 0, b);
     }
-    load_k(0);
-    load_v(0);
-  }
-  // strictly-lower-triangular ones: TRI[i][r] = 1 for r < i; thread (row, wg) writes K columns 64 wg .. 64 wg + 63
-  {
-    uint32_t w[32];
-#pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      const int r = wg * 64 + 2 * e;
-      w[e] = pack_bf16(r < row ? 1.f : 0.f, (r + 1) < row ? 1.f : 0.f);
-    }
-    tmem_st32(lane_base + kColTri + wg * 32, w);
+    load_k(steps - 1);
+    load_v(steps - 1);
   }
   // Q and Q0 rows from the TMA landing tiles (128-byte swizzle) into TMEM; warpgroup wg moves D / 2 of the D columns
   mbar_wait(&bar_q, 0, status, 300);
@@ -268,6 +261,23 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
     }
   }
   tmem_st_wait();
+  __syncthreads();                                             // the landing tiles have been read by everyone
+  // strictly-lower-triangular ones TRI[i][r] = 1 for r < i, a K-major A operand of two [128][64] tiles laid over the
+  // landing area; thread (row, wg) writes row `row` of tile wg (running-sum index r = 64 wg .. 64 wg + 63)
+  {
+    uint8_t* tri = smem + L::q + wg * kRowTile;
+#pragma unroll
+    for (int c = 0; c < 8; ++c) {
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = wg * 64 + c * 8 + 2 * e;
+        w[e] = pack_bf16(r < row ? 1.f : 0.f, (r + 1) < row ? 1.f : 0.f);
+      }
+      *reinterpret_cast<uint4*>(tri + swz_off(row, c)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+  }
+  fence_async_smem();
   tc_fence_before_sync();
   __syncthreads();
   tc_fence_after_sync();
@@ -278,36 +288,42 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
   const float c1 = scale * kLog2e;
   const float* carry_row = carry + ((int64_t)b * (ntiles + 1) + mi) * seq;
 
+  // L0 = Q0 K0^T and S = Q K^T of the step whose K tiles are landing
+  auto issue_logits = [&](int it) {
+    mbar_wait(&bar_k, it & 1, status, 301);
+    tc_fence_after_sync();
+    for (int ks = 0; ks < 4 * DK; ++ks)
+      mma_ts(tmem + kColL, tmem + kColQ0 + ks * 8,
+             smem_desc(sa + L::k0 + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
+    for (int ks = 0; ks < 4 * DK; ++ks)
+      mma_ts(tmem + kColS, tmem + kColQ + ks * 8,
+             smem_desc(sa + L::k + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
+  };
+  if (tid == 0) {
+    issue_logits(0);
+    mma_commit(&bar_mma);
+  }
+
   const int i = i0 + row;
   const int cw = wg * 32;                                     // this warpgroup's key columns within a step
   float run_max = -INFINITY, run_den = 0.f;                   // run_den: this warpgroup's share of the denominator
-  float acc[DH];
-#pragma unroll
-  for (int d = 0; d < DH; ++d) acc[d] = 0.f;
   uint32_t mma_phase = 0;
 
-  for (int t = 0; t < steps; ++t) {
+  for (int it = 0; it < steps; ++it) {
+    const int t = steps - 1 - it;
     const int j0 = t * kKeys;
-    // ---- A: S = Q K^T, L0 = Q0 K0^T ------------------------------------------------------------------
-    if (tid == 0) {
-      mbar_wait(&bar_k, t & 1, status, 301);
-      tc_fence_after_sync();
-      for (int ks = 0; ks < 4 * DK; ++ks)
-        mma_ts(tmem + kColL, tmem + kColQ0 + ks * 8,
-               smem_desc(sa + L::k0 + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
-      for (int ks = 0; ks < 4 * DK; ++ks)
-        mma_ts(tmem + kColS, tmem + kColQ + ks * 8,
-               smem_desc(sa + L::k + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
-      mma_commit(&bar_mma);
-    }
     if (tid < kKeys) {
       const int j = j0 + tid;
-      carry_s[t & 1][tid] = (j < seq) ? carry_row[j] * kLog2e : 0.f;
+      carry_s[it & 1][tid] = (j < seq) ? carry_row[j] * kLog2e : 0.f;
     }
+    // ---- A: the batch (P V of the previous step, L0, S) has completed ---------------------------------------
     mbar_wait(&bar_mma, mma_phase, status, 302);
     mma_phase ^= 1;
     tc_fence_after_sync();
-    if (tid == 0 && t + 1 < steps) load_k(t + 1);     // K and K0 tiles are free once both products are done
+    if (tid == 0) {
+      if (t > 0) load_k(t - 1);                        // K and K0 tiles are free once both products are done
+      if (it > 0) load_v(t);                           // and so is V, read last by the previous step's P V
+    }
 
     // ---- B: selection relu(L0) under the mask -> bf16, row = query, this warpgroup's 32 keys ----------------
     {
@@ -340,7 +356,8 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
     if (tid == 0) {
       tc_fence_after_sync();
       for (int ks = 0; ks < 8; ++ks)
-        mma_ts(tmem + kColS, tmem + kColTri + ks * 8, smem_desc(sa + L::selp + ks * 2048, kRowTile, 1024), idesc_tri, 1);
+        mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+               smem_desc(sa + L::selp + ks * 2048, kRowTile, 1024), idesc_tri, 1);
       mma_commit(&bar_mma);
     }
     mbar_wait(&bar_mma, mma_phase, status, 303);
@@ -353,7 +370,7 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
       uint32_t r[32];
       tmem_ld32(lane_base + kColS + cw, r);
       tmem_ld_wait();
-      const float* cs = carry_s[t & 1] + cw;
+      const float* cs = carry_s[it & 1] + cw;
       float tile_max = -INFINITY;
       if (j0 + kKeys - 1 > i0) {                               // a step that crosses the diagonal
 #pragma unroll
@@ -374,12 +391,15 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
     __syncthreads();
     tc_fence_after_sync();
     const float new_max = fmaxf(run_max, fmaxf(rmax_s[0][row], rmax_s[1][row]));
-    const float alpha = ex2(run_max - new_max);
+    // a row of the tile's upper half has no key at or below the diagonal in the first step: its maximum is still
+    // -inf there, and the reference point 0 keeps every term an exact zero instead of inf - inf
+    const float ref = (new_max == -INFINITY) ? 0.f : new_max;
+    const float alpha = ex2(run_max - ref);
     run_max = new_max;
     float rowsum = 0.f;
 #pragma unroll
     for (int e = 0; e < 32; ++e) {
-      z[e] = ex2(z[e] - new_max);
+      z[e] = ex2(z[e] - ref);
       rowsum += z[e];
     }
 #pragma unroll
@@ -389,49 +409,56 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
       *reinterpret_cast<uint4*>(smem + L::selp + swz_off(row, wg * 4 + c)) = w;
     }
     run_den = run_den * alpha + rowsum;
-    if (__any_sync(0xffffffffu, alpha != 1.f)) {              // the running maximum rarely moves once F has grown
+    if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {    // the accumulator (complete since A) follows the maximum
 #pragma unroll
-      for (int d = 0; d < DH; ++d) acc[d] *= alpha;
+      for (int c0 = 0; c0 < DH; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld32(lane_base + kColO + wg * DH + c0, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+        tmem_st32(lane_base + kColO + wg * DH + c0, r);
+      }
+      tmem_st_wait();
     }
     fence_async_smem();
     tc_fence_before_sync();
     __syncthreads();
 
-    // ---- E: P V ---------------------------------------------------------------------------------------------
+    // ---- E: O += P V, then the logits of the next step, as one batch -----------------------------------------
     if (tid == 0) {
-      mbar_wait(&bar_v, t & 1, status, 304);
+      mbar_wait(&bar_v, it & 1, status, 304);
       tc_fence_after_sync();
       for (int ks = 0; ks < 4; ++ks)
-        mma_ss(tmem + kColPV, smem_desc(sa + L::selp + ks * 32, 16, 1024),
-               smem_desc(sa + L::v + ks * 2048, kKeyTile, 1024), idesc_pv, ks > 0);
+        mma_ss(tmem + kColO, smem_desc(sa + L::selp + ks * 32, 16, 1024),
+               smem_desc(sa + L::v + ks * 2048, kKeyTile, 1024), idesc_pv, (it > 0 || ks > 0) ? 1u : 0u);
+      if (it + 1 < steps) issue_logits(it + 1);
       mma_commit(&bar_mma);
     }
-    mbar_wait(&bar_mma, mma_phase, status, 305);
-    mma_phase ^= 1;
-    tc_fence_after_sync();
-    if (tid == 0 && t + 1 < steps) load_v(t + 1);
-#pragma unroll
-    for (int c0 = 0; c0 < DH; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(lane_base + kColPV + wg * DH + c0, r);
-      tmem_ld_wait();
-#pragma unroll
-      for (int e = 0; e < 32; ++e) acc[c0 + e] += __uint_as_float(r[e]);
-    }
-    tc_fence_before_sync();
-    __syncthreads();
   }
+  mbar_wait(&bar_mma, mma_phase, status, 305);                // the last P V
+  tc_fence_after_sync();
 
   // the two warpgroups hold disjoint shares of each row's denominator
   rmax_s[wg][row] = run_den;
   __syncthreads();
   const float den = rmax_s[0][row] + rmax_s[1][row];
-  if (i < seq) {
+  {
     const float inv = 1.f / den;
     float4* orow = reinterpret_cast<float4*>(out + ((int64_t)n * seq + i) * D + wg * DH);
 #pragma unroll
-    for (int d = 0; d < DH; d += 4) orow[d >> 2] = make_float4(acc[d] * inv, acc[d + 1] * inv, acc[d + 2] * inv, acc[d + 3] * inv);
-    if (wg == 0) lse2[(int64_t)n * seq + i] = run_max + log2f(den);
+    for (int c0 = 0; c0 < DH; c0 += 32) {
+      uint32_t r[32];
+      tmem_ld32(lane_base + kColO + wg * DH + c0, r);
+      tmem_ld_wait();
+      if (i < seq) {
+#pragma unroll
+        for (int d = 0; d < 32; d += 4)
+          orow[(c0 + d) >> 2] = make_float4(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv,
+                                            __uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv);
+      }
+    }
+    if (i < seq && wg == 0) lse2[(int64_t)n * seq + i] = run_max + log2f(den);
   }
   tc_fence_before_sync();
   __syncthreads();
