@@ -6,11 +6,12 @@
 //                   COLSUM[b][query tile][key].
 //   scan_kernel     exclusive prefix of COLSUM across query tiles, in place (-> CARRY), plus one extra
 //                   row holding the grand total.  One thread per key column; bandwidth-bound.
-//   forward_kernel  flash-style forward for one 128-query tile of one head over 64-key tiles:
-//                   S = Q K^T and L0 = Q0 K0^T by MMA; relu(L0) under the selection mask is written to
-//                   shared memory as bf16 and the in-tile exclusive running sum over queries is one more
-//                   MMA, (-strictly-lower-triangular ones) x selection, accumulated into S; then online
-//                   softmax in the log2 domain with the cross-tile carry subtracted per key, P V by MMA.
+//   forward_kernel  flash-style forward for one 128-query tile of one head over 64-key steps, taken from the
+//                   diagonal back to key 0: S = Q K^T and L0 = Q0 K0^T by MMA (Q, Q0 in TMEM); relu(L0) under
+//                   the selection mask is written to shared memory as bf16 and the in-tile exclusive running
+//                   sum over queries is one more MMA, (-strictly-lower-triangular ones) x selection,
+//                   accumulated into S; then online softmax in the log2 domain with the cross-tile carry
+//                   subtracted per key, and O += P V in TMEM.
 //
 // Reference for the arithmetic: src/selective_attention/kernels.py:100-194 (selection, carry, forward).
 #include "sa_tc_host.cuh"
