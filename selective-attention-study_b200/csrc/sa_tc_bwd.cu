@@ -158,10 +158,16 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   tmem_ld16(c.lane_base + kColST + colw, r);
   tmem_ld_wait();
 #pragma unroll
-  for (int e = 0; e < 16; ++e) {
-    const float t2 = fmaf(c.c1, ls[e], -(cb + c.lse_s[col0 + e]));
-    p[e] = ex2(fmaf(__uint_as_float(r[e]), c.c1, t2));
-    if (DIAG && (c.row > col0 + e)) p[e] = 0.f;       // key after the query
+  for (int e4 = 0; e4 < 16; e4 += 4) {                  // row statistics: one 16-byte broadcast load per 4 queries
+    const float4 st4 = *reinterpret_cast<const float4*>(c.lse_s + col0 + e4);
+    const float st[4] = {st4.x, st4.y, st4.z, st4.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int e = e4 + k;
+      const float t2 = fmaf(c.c1, ls[e], -(cb + st[k]));
+      p[e] = ex2(fmaf(__uint_as_float(r[e]), c.c1, t2));
+      if (DIAG && (c.row > col0 + e)) p[e] = 0.f;       // key after the query
+    }
   }
   {                                                     // P^T as bf16 pairs into the (consumed) L0^T columns
     uint32_t w8[8];
@@ -173,7 +179,13 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   tmem_ld16(c.lane_base + kColDPT + colw, r);
   tmem_ld_wait();
 #pragma unroll
-  for (int e = 0; e < 16; ++e) p[e] = p[e] * (__uint_as_float(r[e]) - c.dbar_s[col0 + e]);     // dz
+  for (int e4 = 0; e4 < 16; e4 += 4) {
+    const float4 st4 = *reinterpret_cast<const float4*>(c.dbar_s + col0 + e4);
+    p[e4] = p[e4] * (__uint_as_float(r[e4]) - st4.x);                                 // dz
+    p[e4 + 1] = p[e4 + 1] * (__uint_as_float(r[e4 + 1]) - st4.y);
+    p[e4 + 2] = p[e4 + 2] * (__uint_as_float(r[e4 + 2]) - st4.z);
+    p[e4 + 3] = p[e4 + 3] * (__uint_as_float(r[e4 + 3]) - st4.w);
+  }
   put8(c.smem + L::dz, c.row, col0, p);
   put8(c.smem + L::dz, c.row, col0 + 8, p + 8);
 
@@ -349,12 +361,12 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         mbar_wait(&bar_early, early_phase, status, 406);
         early_phase ^= 1;
         tc_fence_after_sync();
-        issue_dv(it, 0, false);
-        issue_dk_only(it, 0, false);
 #pragma unroll
         for (int ks = 0; ks < 8; ++ks)                        // dQ = dz K: A M-major, K = key index
           mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
-        mma_commit(&bar_dq);                                  // dQ done => every MMA reading the dz tiles is done
+        issue_dk_only(it, 0, false);
+        mma_commit(&bar_dq);                                  // dQ done and every MMA reading the dz tiles is done:
+        issue_dv(it, 0, false);                               //   its read-out overlaps the MMAs from here on
         mbar_wait(&bar_half[0], ph, status, 407);            // half 0: g written
         tc_fence_after_sync();
         issue_dk0_only(it, 0, false);
