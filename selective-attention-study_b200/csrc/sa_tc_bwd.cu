@@ -19,6 +19,11 @@
 //                dK += dz^T Q;  dK0 += g^T Q0
 //     per tile : dQ = dz K;  dQ0 = g K0  (dz, g read from shared memory M-major) -> scaled, staged in
 //                shared memory and added to the fp32 global accumulators with TMA reduce-add.
+//
+// SELF variant (one head per selector, i.e. the per-head form reshaped to (B H, 1, T, D)): the selection logits
+// are the head's own logits, so L0^T is S^T, and since Q0 = Q and K0 = K the two gradient paths add before the
+// MMAs: dK += (dz + g)^T Q and dQ = (dz + g) K.  40 MMAs per query tile instead of 64, no Q0 / K0 tiles, one
+// read-out per tile.
 // Reference for the arithmetic: src/selective_attention/kernels.py:196-268.
 #include "sa_tc_host.cuh"
 #include "sa_tc_ptx.cuh"
@@ -112,7 +117,7 @@ struct HalfCtx {
 // its key row.  The two running sums run from the last query to the first; a chunk computes them
 // locally (two independent chains of 8) and picks up the totals of the chunks to its right, and the
 // carried state, through shared memory.
-template <bool DIAG>
+template <bool DIAG, bool SELF>
 __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state, float& dz_state SA_MARKS_ARG) {
   using L = BwdSmem;
   const int colw = c.wg * kChunk;
@@ -120,7 +125,7 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   uint32_t r[16];
   float negon[16], ls[16], p[16], lx[16];
 
-  tmem_ld16(c.lane_base + kColL0T + colw, r);
+  tmem_ld16(c.lane_base + (SELF ? kColST : kColL0T) + colw, r);
   tmem_ld_wait();
 #pragma unroll
   for (int e = 0; e < 16; ++e) {
@@ -186,8 +191,10 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
     p[e4 + 2] = p[e4 + 2] * (__uint_as_float(r[e4 + 2]) - st4.z);
     p[e4 + 3] = p[e4 + 3] * (__uint_as_float(r[e4 + 3]) - st4.w);
   }
-  put8(c.smem + L::dz, c.row, col0, p);
-  put8(c.smem + L::dz, c.row, col0 + 8, p + 8);
+  if (!SELF) {
+    put8(c.smem + L::dz, c.row, col0, p);
+    put8(c.smem + L::dz, c.row, col0 + 8, p + 8);
+  }
 
   lx[15] = 0.f;                                          // exclusive suffix sums of dz, two chains
   lx[7] = 0.f;
@@ -217,13 +224,21 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   }
   const float base = dz_state + later;
   dz_state += all;
+  if (SELF) {
 #pragma unroll
-  for (int e = 0; e < 16; ++e) lx[e] = negon[e] * (base + lx[e]);                                  // g
-  put8(c.smem + L::g, c.row, col0, lx);
-  put8(c.smem + L::g, c.row, col0 + 8, lx + 8);
+    for (int e = 0; e < 16; ++e) lx[e] = fmaf(negon[e], base + lx[e], p[e]);                       // dz + g
+    put8(c.smem + L::dz, c.row, col0, lx);
+    put8(c.smem + L::dz, c.row, col0 + 8, lx + 8);
+  } else {
+#pragma unroll
+    for (int e = 0; e < 16; ++e) lx[e] = negon[e] * (base + lx[e]);                                // g
+    put8(c.smem + L::g, c.row, col0, lx);
+    put8(c.smem + L::g, c.row, col0 + 8, lx + 8);
+  }
   SA_MARK(marks, 6)
 }
 
+template <bool SELF>
 __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -280,9 +295,9 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       auto load_stage = [&](int it) {
         const int mi = ntiles - 1 - it;
         uint8_t* st = smem + L::stage + (it & 1) * 3 * kRowTile;
-        mbar_expect_tx(&bar_ld[it & 1], 3 * kRowTile);
+        mbar_expect_tx(&bar_ld[it & 1], (SELF ? 2 : 3) * kRowTile);
         tma_load_4d(st, &map_q, &bar_ld[it & 1], 0, mi * kTile, h, b);
-        tma_load_4d(st + kRowTile, &map_q, &bar_ld[it & 1], 0, mi * kTile, 0, b);
+        if (!SELF) tma_load_4d(st + kRowTile, &map_q, &bar_ld[it & 1], 0, mi * kTile, 0, b);
         tma_load_4d(st + 2 * kRowTile, &map_do, &bar_ld[it & 1], 0, mi * kTile, n, 0);
       };
       // Operand descriptors are built once; an MMA's descriptor is a base plus a byte offset / 16, so the
@@ -298,9 +313,11 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       // S^T, dP^T, L0^T of one 64-query half
       auto issue_scores = [&](int it, int hf) {
         const uint32_t st = (it & 1) * 3 * kRowTile + hf * 8192;                   // rows 64 hf .. 64 hf + 63
+        if (!SELF) {
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColL0T, at(kK0, ks * 32), at(kStage, st + kRowTile + ks * 32), idesc_t, ks > 0);
+          for (int ks = 0; ks < 4; ++ks)
+            mma_ss(tmem + kColL0T, at(kK0, ks * 32), at(kStage, st + kRowTile + ks * 32), idesc_t, ks > 0);
+        }
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
           mma_ss(tmem + kColST, at(kK, ks * 32), at(kStage, st + ks * 32), idesc_t, ks > 0);
@@ -333,10 +350,10 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
                  (first && ks == 0) ? 0u : 1u);
       };
 
-      mbar_expect_tx(&bar_kv, 3 * kRowTile);
+      mbar_expect_tx(&bar_kv, (SELF ? 2 : 3) * kRowTile);
       tma_load_4d(smem + L::k, &map_k, &bar_kv, 0, nj * kTile, h, b);
       tma_load_4d(smem + L::v, &map_v, &bar_kv, 0, nj * kTile, h, b);
-      tma_load_4d(smem + L::k0, &map_k, &bar_kv, 0, nj * kTile, 0, b);
+      if (!SELF) tma_load_4d(smem + L::k0, &map_k, &bar_kv, 0, nj * kTile, 0, b);
       load_stage(0);
       if (n_iter > 1) load_stage(1);
       mbar_wait(&bar_kv, 0, status, 400);
@@ -353,31 +370,49 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         tc_fence_after_sync();
         issue_dv(it, 1, it == 0);                             // reads P^T before the next scores overwrite it
         issue_scores(it, 0);
-        issue_dk_only(it, 1, it == 0);
-        mbar_wait(&bar_half[1], ph, status, 403);            // half 1: g written
+        if (!SELF) issue_dk_only(it, 1, it == 0);
+        mbar_wait(&bar_half[1], ph, status, 403);            // half 1: g (SELF: dz + g) written
         tc_fence_after_sync();
-        issue_dk0_only(it, 1, it == 0);
+        if (SELF) issue_dk_only(it, 1, it == 0);
+        else issue_dk0_only(it, 1, it == 0);
         // half 0
         mbar_wait(&bar_early, early_phase, status, 406);
         early_phase ^= 1;
         tc_fence_after_sync();
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)                        // dQ = dz K: A M-major, K = key index
-          mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
-        issue_dk_only(it, 0, false);
-        mma_commit(&bar_dq);                                  // dQ done and every MMA reading the dz tiles is done:
-        issue_dv(it, 0, false);                               //   its read-out overlaps the MMAs from here on
-        mbar_wait(&bar_half[0], ph, status, 407);            // half 0: g written
-        tc_fence_after_sync();
-        issue_dk0_only(it, 0, false);
-#pragma unroll
-        for (int ks = 0; ks < 8; ++ks)                        // dQ0 = g K0
-          mma_ss(tmem + kColDQ0, at(mG, ks * 2048), at(mK0, ks * 2048), idesc_dq, ks > 0);
-        mma_commit(&bar_b);
-        if (it + 1 < n_iter) {
-          mbar_wait(&bar_ld[(it + 1) & 1], ((it + 1) >> 1) & 1, status, 404);
+        if (SELF) {
+          issue_dv(it, 0, false);
+          if (it + 1 < n_iter) {                              // nothing else can run until the g pass ends
+            mbar_wait(&bar_ld[(it + 1) & 1], ((it + 1) >> 1) & 1, status, 404);
+            tc_fence_after_sync();
+            issue_scores(it + 1, 1);
+          }
+          mbar_wait(&bar_half[0], ph, status, 407);          // half 0: dz + g written
           tc_fence_after_sync();
-          issue_scores(it + 1, 1);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)                      // dQ = (dz + g) K: A M-major, K = key index
+            mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
+          issue_dk_only(it, 0, false);
+          mma_commit(&bar_dq);
+          mma_commit(&bar_b);
+        } else {
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)                      // dQ = dz K: A M-major, K = key index
+            mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
+          issue_dk_only(it, 0, false);
+          mma_commit(&bar_dq);                                // dQ done and every MMA reading the dz tiles is done:
+          issue_dv(it, 0, false);                             //   its read-out overlaps the MMAs from here on
+          mbar_wait(&bar_half[0], ph, status, 407);          // half 0: g written
+          tc_fence_after_sync();
+          issue_dk0_only(it, 0, false);
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)                      // dQ0 = g K0
+            mma_ss(tmem + kColDQ0, at(mG, ks * 2048), at(mK0, ks * 2048), idesc_dq, ks > 0);
+          mma_commit(&bar_b);
+          if (it + 1 < n_iter) {
+            mbar_wait(&bar_ld[(it + 1) & 1], ((it + 1) >> 1) & 1, status, 404);
+            tc_fence_after_sync();
+            issue_scores(it + 1, 1);
+          }
         }
         mbar_wait(&bar_b, it & 1, status, 405);               // every MMA reading stage (it & 1) has completed
         if (it + 2 < n_iter) load_stage(it + 2);
@@ -451,8 +486,8 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         SA_MARK(marks, 1)
         ctx.hf = hf;
         ctx.drain_reduce = (hf == 1) && (it > 0);
-        if (diag) process_half<true>(ctx, sel_state, dz_state SA_MARKS_PASS);
-        else process_half<false>(ctx, sel_state, dz_state SA_MARKS_PASS);
+        if (diag) process_half<true, SELF>(ctx, sel_state, dz_state SA_MARKS_PASS);
+        else process_half<false, SELF>(ctx, sel_state, dz_state SA_MARKS_PASS);
         fence_async_smem();                                    // g tile half -> visible to the MMAs
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_half[hf]);
@@ -486,6 +521,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         bulk_commit();
       }
       SA_MARK(marks, 10)
+      if (SELF) continue;                                      // dQ already carries the selection path
       mbar_wait(&bar_b, it & 1, status, 411);
       tc_fence_after_sync();
       SA_MARK(marks, 11)
@@ -511,7 +547,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       uint32_t rv[16], rk[16], r0[16];
       tmem_ld16(lane_base + kColDV + c0, rv);
       tmem_ld16(lane_base + kColDK + c0, rk);
-      tmem_ld16(lane_base + kColDK0 + c0, r0);
+      if (!SELF) tmem_ld16(lane_base + kColDK0 + c0, r0);
       tmem_ld_wait();
       if (j < seq) {
 #pragma unroll
@@ -527,10 +563,11 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
           *reinterpret_cast<float4*>(dk_row + e) =
               make_float4(__uint_as_float(rk[e]) * scale, __uint_as_float(rk[e + 1]) * scale,
                           __uint_as_float(rk[e + 2]) * scale, __uint_as_float(rk[e + 3]) * scale);
-          asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dk0_row + e),
-                       "f"(__uint_as_float(r0[e]) * scale), "f"(__uint_as_float(r0[e + 1]) * scale),
-                       "f"(__uint_as_float(r0[e + 2]) * scale), "f"(__uint_as_float(r0[e + 3]) * scale)
-                       : "memory");
+          if (!SELF)
+            asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dk0_row + e),
+                         "f"(__uint_as_float(r0[e]) * scale), "f"(__uint_as_float(r0[e + 1]) * scale),
+                         "f"(__uint_as_float(r0[e + 2]) * scale), "f"(__uint_as_float(r0[e + 3]) * scale)
+                         : "memory");
         }
       }
     }
@@ -577,12 +614,21 @@ int backward(const Problem& p, const float* lse2, const float* carry, const floa
   st = status_word(&status);
   if (st != SA_OK) return st;
   const int smem = BwdSmem::total + 1024;
-  SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  // One head per selector (the per-head form): the selection logits are the head's own, and the kernel merges the
+  // two gradient paths before the MMAs.
+  const bool self = (p.heads == 1);
+  if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  else SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   {
     ProfileScope prof(SA_KERNEL_TC_BACKWARD, s);
-    backward_kernel<<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
-        map_q, map_k, map_v, map_do, map_dq, map_dq0, lse2, carry, dbar, dk_acc, dk0, static_cast<__nv_bfloat16*>(dv),
-        p.heads, p.seq, ntiles, p.exempt, p.scale, status);
+    if (self)
+      backward_kernel<true><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
+          map_q, map_k, map_v, map_do, map_dq, map_dq0, lse2, carry, dbar, dk_acc, dk0,
+          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status);
+    else
+      backward_kernel<false><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
+          map_q, map_k, map_v, map_do, map_dq, map_dq0, lse2, carry, dbar, dk_acc, dk0,
+          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status);
   }
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;

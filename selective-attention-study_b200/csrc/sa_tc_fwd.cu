@@ -177,7 +177,8 @@ constexpr int kFwdThreads = 256;      // two warpgroups: each owns 32 of a step'
 // carry the least history, so the running maximum settles within the first steps and the output accumulator,
 // which stays in TMEM for the whole loop, is rescaled only while the maximum still moves.  Per step the tensor
 // pipe gets two batches: (P V of the previous step, L0 and S of this one) and the triangular running-sum MMA.
-template <int D>
+// SELF: one head per selector (the per-head form), so L0 is S itself and the Q0 / K0 tiles and their MMA are left out.
+template <int D, bool SELF>
 __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
     forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                    const __grid_constant__ CUtensorMap map_v, const float* __restrict__ carry,
@@ -223,10 +224,10 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
   const uint32_t sa = smem_u32(smem);
 
   auto load_k = [&](int t) {
-    mbar_expect_tx(&bar_k, 2 * DK * kKeyTile);
+    mbar_expect_tx(&bar_k, (SELF ? 1 : 2) * DK * kKeyTile);
     for (int s = 0; s < DK; ++s) {
       tma_load_4d(smem + L::k + s * kKeyTile, &map_k, &bar_k, s * 64, t * kKeys, h, b);
-      tma_load_4d(smem + L::k0 + s * kKeyTile, &map_k, &bar_k, s * 64, t * kKeys, 0, b);
+      if (!SELF) tma_load_4d(smem + L::k0 + s * kKeyTile, &map_k, &bar_k, s * 64, t * kKeys, 0, b);
     }
   };
   auto load_v = [&](int t) {
@@ -234,10 +235,10 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
     for (int s = 0; s < DK; ++s) tma_load_4d(smem + L::v + s * kKeyTile, &map_v, &bar_v, s * 64, t * kKeys, h, b);
   };
   if (tid == 0) {
-    mbar_expect_tx(&bar_q, 2 * DK * kRowTile);
+    mbar_expect_tx(&bar_q, (SELF ? 1 : 2) * DK * kRowTile);
     for (int s = 0; s < DK; ++s) {
       tma_load_4d(smem + L::q + s * kRowTile, &map_q, &bar_q, s * 64, i0, h, b);
-      tma_load_4d(smem + L::q0 + s * kRowTile, &map_q, &bar_q, s * 64, i0, 0, b);
+      if (!SELF) tma_load_4d(smem + L::q0 + s * kRowTile, &map_q, &bar_q, s * 64, i0, 0, b);
     }
     load_k(steps - 1);
     load_v(steps - 1);
@@ -247,7 +248,7 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
   {
     constexpr int kChunks = D / 16;                            // 16-byte chunks per thread and matrix
 #pragma unroll
-    for (int m = 0; m < 2; ++m) {
+    for (int m = 0; m < (SELF ? 1 : 2); ++m) {
       const uint8_t* src = smem + (m == 0 ? L::q : L::q0);
       uint32_t w[kChunks * 4];
 #pragma unroll
@@ -293,9 +294,11 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
   auto issue_logits = [&](int it) {
     mbar_wait(&bar_k, it & 1, status, 301);
     tc_fence_after_sync();
-    for (int ks = 0; ks < 4 * DK; ++ks)
-      mma_ts(tmem + kColL, tmem + kColQ0 + ks * 8,
-             smem_desc(sa + L::k0 + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
+    if (!SELF) {
+      for (int ks = 0; ks < 4 * DK; ++ks)
+        mma_ts(tmem + kColL, tmem + kColQ0 + ks * 8,
+               smem_desc(sa + L::k0 + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
+    }
     for (int ks = 0; ks < 4 * DK; ++ks)
       mma_ts(tmem + kColS, tmem + kColQ + ks * 8,
              smem_desc(sa + L::k + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
@@ -329,7 +332,7 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
     // ---- B: selection relu(L0) under the mask -> bf16, row = query, this warpgroup's 32 keys ----------------
     {
       uint32_t r[32];
-      tmem_ld32(lane_base + kColL + cw, r);
+      tmem_ld32(lane_base + (SELF ? kColS : kColL) + cw, r);
       tmem_ld_wait();
       float s[32];
       if ((j0 + kKeys > i0) || (j0 < exempt)) {
@@ -499,12 +502,18 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   SA_CUDA_CHECK(cudaGetLastError());
 
   const int fwd_smem = FwdSmem<D>::total + 1024;
-  SA_CUDA_CHECK(cudaFuncSetAttribute(forward_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem));
   const unsigned grid = (unsigned)ntiles * p.batch * p.heads;
+  const bool self = (p.heads == 1);            // one head per selector: the selection logits are the head's own
+  if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(forward_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem));
+  else SA_CUDA_CHECK(cudaFuncSetAttribute(forward_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem));
   {
     ProfileScope prof(SA_KERNEL_TC_FORWARD, s);
-    forward_kernel<D><<<grid, kFwdThreads, fwd_smem, s>>>(map_q, map_k, map_v, carry, out, lse2, p.heads, p.seq, ntiles,
-                                                  p.exempt, p.scale, status);
+    if (self)
+      forward_kernel<D, true><<<grid, kFwdThreads, fwd_smem, s>>>(map_q, map_k, map_v, carry, out, lse2, p.heads, p.seq,
+                                                                   ntiles, p.exempt, p.scale, status);
+    else
+      forward_kernel<D, false><<<grid, kFwdThreads, fwd_smem, s>>>(map_q, map_k, map_v, carry, out, lse2, p.heads, p.seq,
+                                                                    ntiles, p.exempt, p.scale, status);
   }
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;

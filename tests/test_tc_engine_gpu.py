@@ -100,9 +100,10 @@ def test_backward_selection_gradient_only_through_history():
         assert _rel(a, b) < 2e-2
 
 
+@pytest.mark.parametrize("heads", [1, 2])                  # one head per selector runs the merged-gradient kernel
 @pytest.mark.parametrize("exempt", [3, 70, 200])
-def test_backward_exempt_prefix(exempt):
-    q, k, v, w = _inputs(1, 2, 333, 64, seed=exempt)
+def test_backward_exempt_prefix(exempt, heads):
+    q, k, v, w = _inputs(1, heads, 333, 64, seed=exempt)
     got = _fwd_bwd(q, k, v, w, exempt=exempt)
     want = oracle.attention_grads(q.float(), k.float(), v.float(), w.float(), exempt=exempt)
     for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
