@@ -142,7 +142,9 @@ int sa_backward(const sa_problem* p, const void* q, const void* k, const void* v
                 void* dq, void* dk, void* dv,
                 void* workspace, size_t workspace_bytes, void* stream);
 
-/* Bytes of scratch sa_decode_step needs. */
+/* Bytes of scratch sa_decode_step needs: per-split partial sums, the step's new selection values and the
+ * tickets with which the last CTA of a row / key range is found.  Contents undefined on entry and exit; two
+ * steps in flight at once (different streams) need separate workspaces. */
 size_t sa_decode_workspace_bytes(int batch, int heads, int groups, int length, int head_dim);
 
 /* One cached decode step.  Replaces the PyTorch ops of SelectiveAttention.step_cache
@@ -153,7 +155,9 @@ size_t sa_decode_workspace_bytes(int batch, int heads, int groups, int length, i
  *   q1, k1, v1       (batch, heads, head_dim) contiguous, element type dtype: the new token
  *   length           number of cached tokens BEFORE this step; k1/v1 are written at index `length`
  *   y                (batch, heads, head_dim) fp32
- * Heads are split in `groups` contiguous runs; the first head of a run is its selector. */
+ *   k_cache, v_cache 16-byte aligned (they are streamed with bulk copies)
+ * Heads are split in `groups` contiguous runs; the first head of a run is its selector.  The bounded waits of
+ * the copy pipeline report into the word sa_device_status reads. */
 int sa_decode_step(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim,
                    int exempt, const void* q1, const void* k1, const void* v1,
                    void* k_cache, void* v_cache, float* selected, float* y,
@@ -177,8 +181,8 @@ enum sa_kernel {
 int sa_profile_enable(int kernel_id);
 int sa_profile_collect(float* ms_host, int capacity);
 
-/* Reads (synchronously) the status word the bounded device-side waits of the tensor-core engine
- * report into; 0 means no wait ever ran out on the current device.  clear != 0 resets it.
+/* Reads (synchronously) the status word the bounded device-side waits of the tensor-core engine and of the
+ * decode step report into; 0 means no wait ever ran out on the current device.  clear != 0 resets it.
  * No counterpart in the reference (Triton kernels have no such waits). */
 int sa_device_status(unsigned int* value_host, int clear);
 

@@ -308,7 +308,9 @@ int sa_decode_step(int dtype, int batch, int heads, int groups, int length, int 
   if (!dim_ok(head_dim)) return SA_ERR_UNSUPPORTED;
   if (length >= capacity) return SA_ERR_BAD_ARGUMENT;
   if (!q1 || !k1 || !v1 || !k_cache || !v_cache || !selected || !y || !workspace) return SA_ERR_BAD_ARGUMENT;
-  if ((int64_t)batch * heads > 65535) return SA_ERR_UNSUPPORTED;
+  if ((int64_t)batch * heads * ((length + 512) / 512) > 0x7fffffffLL) return SA_ERR_TOO_LARGE;   // 1-D grid
+  for (const void* ptr : {q1, k1, v1, (const void*)k_cache, (const void*)v_cache})            // 16-byte loads, bulk copies
+    if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return SA_ERR_ALIGNMENT;
   if (workspace_bytes < sa_decode_workspace_bytes(batch, heads, groups, length, head_dim)) return SA_ERR_WORKSPACE;
   return decode_step(dtype, batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, k_cache, v_cache,
                      selected, y, static_cast<float*>(workspace), static_cast<cudaStream_t>(stream));

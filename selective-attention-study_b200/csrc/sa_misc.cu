@@ -196,7 +196,7 @@ __device__ __forceinline__ void decode_combine_row(const float* prow, float* yro
   }
 }
 
-// grid (splits, batch * heads).  One thread streams the CTA's keys of K and V through a ring of shared-memory
+// grid = batch * heads * splits CTAs (a row's splits are neighbours).  One thread streams the CTA's keys of K and V through a ring of shared-memory
 // stages with bulk copies, kDecStages - 1 stages (48 KB) ahead of the arithmetic, so the bytes in flight do not
 // depend on how the arithmetic is scheduled.  A group of D / 8 lanes owns every (128 / lanes)-th key of a stage
 // and keeps its own running maximum, denominator and weighted sum (one pass, rescaled when its maximum grows);
@@ -205,7 +205,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
     const T* __restrict__ q1, const T* __restrict__ kc, const T* __restrict__ vc, float* selected,
     float* __restrict__ partial, float* __restrict__ sel_new, int heads, int groups, int t, int capacity,
-    int exempt, float scale, int split_keys, unsigned int* status, float* __restrict__ y, unsigned int* __restrict__ row_tickets, unsigned int* __restrict__ split_tickets) {
+    int exempt, float scale, int split_keys, unsigned int* status, float* __restrict__ y, unsigned int* __restrict__ row_tickets, unsigned int* __restrict__ split_tickets, int splits) {
   constexpr int kLanes = D / 8;                                   // lanes per key
   constexpr int kGroups = kDecThreads / kLanes;                   // keys the CTA covers per step
   constexpr int kRowBytes = D * (int)sizeof(T);
@@ -221,7 +221,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
   __shared__ float part[4][128 + 1];
   __shared__ unsigned int ticket_s[2];
 
-  const int n = blockIdx.y, split = blockIdx.x;
+  const int n = (int)(blockIdx.x / (unsigned)splits), split = (int)(blockIdx.x % (unsigned)splits);
   const int b = n / heads, h = n - b * heads;
   const int per = heads / groups, g = h / per;
   const bool selector = (h - g * per) == 0;
@@ -333,7 +333,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
     if (threadIdx.x < sft) red[threadIdx.x] += red[threadIdx.x + sft];
     __syncthreads();
   }
-  float* prow = partial + ((int64_t)n * gridDim.x + split) * (D + 2);
+  float* prow = partial + ((int64_t)n * splits + split) * (D + 2);
   for (int d = threadIdx.x; d < D; d += kDecThreads) {
     float sum = 0.f;
     for (int gg = 0; gg < kGroups; ++gg) sum += accs[gg][d];
@@ -350,10 +350,10 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
   __syncthreads();
   if (threadIdx.x == 0) {
     ticket_s[0] = atomicAdd(&row_tickets[n], 1u);
-    ticket_s[1] = atomicAdd(&split_tickets[((int64_t)b * groups + g) * gridDim.x + split], 1u);
+    ticket_s[1] = atomicAdd(&split_tickets[((int64_t)b * groups + g) * splits + split], 1u);
   }
   __syncthreads();
-  const bool last_of_row = ticket_s[0] == gridDim.x - 1;
+  const bool last_of_row = ticket_s[0] == (unsigned)splits - 1;
   const bool last_of_range = ticket_s[1] == (unsigned)per - 1;
   if (!last_of_row && !last_of_range) return;
   __threadfence();
@@ -376,7 +376,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
     }
   }
   if (last_of_row)
-    decode_combine_row(partial + (int64_t)n * gridDim.x * (D + 2), y + (int64_t)n * D, gridDim.x, D, part, red);
+    decode_combine_row(partial + (int64_t)n * splits * (D + 2), y + (int64_t)n * D, splits, D, part, red);
 }
 
 template <typename T>
@@ -397,7 +397,7 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
       static_cast<const T*>(k1), static_cast<const T*>(v1), static_cast<T*>(kc), static_cast<T*>(vc), rows, capacity,
       length, D, row_tickets, n_tickets);
   SA_CUDA_CHECK(cudaGetLastError());
-  dim3 grid(splits, rows);
+  const unsigned grid = (unsigned)rows * (unsigned)splits;
   const float scale = 1.0f / sqrtf((float)D);
   const T* q = static_cast<const T*>(q1);
   const T* kk = static_cast<const T*>(kc);
@@ -410,7 +410,7 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
                                        (int)kDecSmemBytes));                                                       \
     decode_attend_kernel<T, DIM><<<grid, kDecThreads, kDecSmemBytes, s>>>(                                         \
         q, kk, vv, selected, partial, sel_new, heads, groups, t, capacity, exempt, scale, split_keys, status,      \
-        y, row_tickets, split_tickets);                                                                           \
+        y, row_tickets, split_tickets, splits);                                                                   \
   } while (0)
   switch (D) {
     case 16: SA_DECODE_LAUNCH(16); break;

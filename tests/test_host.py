@@ -51,6 +51,7 @@ def test_argument_checks_reject_before_any_launch():
     need = lib.sa_backward_workspace_bytes(ctypes.byref(p))
     assert need >= 2 * 64 * 32 * 4 * 2
     assert lib.sa_decode_step(0, 1, 2, 1, 8, 8, 32, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1 << 20, None) == 1  # cache full
+    assert lib.sa_decode_step(0, 1, 2, 1, 7, 8, 32, 1, 16, 16, 16, 24, 16, 16, 16, 16, 1 << 20, None) == 3  # k_cache not 16-byte aligned
     # partial sums (rows x splits x (D + 2)), new selection (groups x t), tickets (rows + groups x splits)
     assert lib.sa_decode_workspace_bytes(1, 2, 1, 7, 32) == (2 * 1 * 34 + 8 + 2 + 1) * 4
 
