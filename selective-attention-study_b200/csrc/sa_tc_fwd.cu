@@ -469,6 +469,320 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
   if (warp == 0) tmem_dealloc(tmem, kTmemCols);
 }
 
+// ---------------------------------------------------------------------------------------------------
+// forward, head_dim 64: 128-key steps, one CTA per SM
+// ---------------------------------------------------------------------------------------------------
+// Same arithmetic as forward_kernel, arranged so that one CTA keeps the tensor pipe and four warpgroups busy without
+// a second resident CTA: a step covers 128 keys (N = 128 MMAs run at the full tensor rate and the per-step barriers
+// are paid half as often), L0 is double-buffered in TMEM so the selection pass of the next step never waits for an
+// MMA, and the selection and probability tiles have separate shared-memory buffers so P V of one step runs under
+// the selection pass of the next.  The only MMA completion the arithmetic waits for is the triangular running sum.
+struct WideSmem {
+  static constexpr int q = 0;                          // landing tiles of Q and Q0, then the triangular ones (2 tiles)
+  static constexpr int sel = q + 2 * kRowTile;         // [128 queries][128 keys] bf16 as two key tiles (B of the running sum)
+  static constexpr int p = sel + 2 * kRowTile;         // the same shape: P (A of P V)
+  static constexpr int k = p + 2 * kRowTile;           // 2 stages x [128 keys][64]
+  static constexpr int k0 = k + 2 * kRowTile;
+  static constexpr int v = k0 + 2 * kRowTile;
+  static constexpr int total = v + 2 * kRowTile;       // 192 KB
+};
+constexpr int kWideCompute = 512;                      // four warpgroups: 32 of a step's 128 key columns, 16 of the 64 d each
+constexpr int kWideThreads = kWideCompute + 32;        // + the control warp: one lane issues every TMA load and MMA
+constexpr int kWideBarrier = 1;                        // hardware barrier id of the arithmetic warps
+
+template <bool SELF>
+__global__ void __launch_bounds__(kWideThreads, 1)
+    forward_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v, const float* __restrict__ carry,
+                        float* __restrict__ out, float* __restrict__ lse2, int heads, int seq, int ntiles, int exempt,
+                        float scale, unsigned int* status) {
+  using L = WideSmem;
+  constexpr int D = 64, DH = 16, NC = 32;
+  constexpr uint32_t kColS = 0, kColL = 128 /* two buffers of 128 */, kColO = 384, kColQ = 448, kColQ0 = 480;
+
+  const int nrows = gridDim.x / ntiles;                       // batch * heads
+  const int mi = ntiles - 1 - (int)(blockIdx.x / nrows);      // heaviest query tiles first
+  const int n = blockIdx.x % nrows;
+  const int b = n / heads, h = n - b * heads;
+  const int i0 = mi * kTile;
+  const int steps = mi + 1;                                   // 128-key steps up to and including the diagonal tile
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  // bar_sel / bar_p: one arrival per arithmetic warp and step (selection tile written / P written, S read, O rescaled)
+  __shared__ uint64_t bar_q, bar_k[2], bar_k0[2], bar_v[2], bar_l0, bar_tri, bar_fin, bar_sel, bar_p, bar_setup;
+  __shared__ uint32_t tmem_base_s;
+  __shared__ __align__(16) float carry_s[2][kTile];
+  __shared__ float rmax_s[4][kTile];
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    mbar_init(&bar_q, 1);
+    for (int u = 0; u < 2; ++u) {
+      mbar_init(&bar_k[u], 1);
+      mbar_init(&bar_k0[u], 1);
+      mbar_init(&bar_v[u], 1);
+    }
+    mbar_init(&bar_l0, 1);
+    mbar_init(&bar_tri, 1);
+    mbar_init(&bar_fin, 1);
+    mbar_init(&bar_sel, kWideCompute / 32);
+    mbar_init(&bar_p, kWideCompute / 32);
+    mbar_init(&bar_setup, kWideCompute / 32);
+    mbar_init_fence();
+  }
+  if (warp == 0) tmem_alloc(&tmem_base_s, 512);
+  tc_fence_before_sync();
+  __syncthreads();
+  tc_fence_after_sync();
+  const uint32_t tmem = tmem_base_s;
+  const uint32_t sa = smem_u32(smem);
+
+  if (warp == kWideCompute / 32) {
+    // =============================== control warp: TMA loads and MMA issue ===============================
+    if (lane == 0) {
+      // step index `it` counts from the diagonal (it = 0) back to key 0; its keys start at 128 (steps - 1 - it)
+      auto load_k = [&](int it) {
+        mbar_expect_tx(&bar_k[it & 1], kRowTile);
+        tma_load_4d(smem + L::k + (it & 1) * kRowTile, &map_k, &bar_k[it & 1], 0, (steps - 1 - it) * kTile, h, b);
+      };
+      auto load_k0 = [&](int it) {
+        if (SELF) return;
+        mbar_expect_tx(&bar_k0[it & 1], kRowTile);
+        tma_load_4d(smem + L::k0 + (it & 1) * kRowTile, &map_k, &bar_k0[it & 1], 0, (steps - 1 - it) * kTile, 0, b);
+      };
+      auto load_v = [&](int it) {
+        mbar_expect_tx(&bar_v[it & 1], kRowTile);
+        tma_load_4d(smem + L::v + (it & 1) * kRowTile, &map_v, &bar_v[it & 1], 0, (steps - 1 - it) * kTile, h, b);
+      };
+      const uint32_t idesc_s = instr_desc_bf16(128, 128, false, false);
+      const uint32_t idesc_tri = instr_desc_bf16(128, 128, false, true, /*negate_a=*/true);
+      const uint32_t idesc_pv = instr_desc_bf16(128, D, false, true);
+      auto issue_l0 = [&](int it) {                            // L0 = Q0 K0^T into the L buffer of the step
+        if (SELF) return;
+        mbar_wait(&bar_k0[it & 1], (it >> 1) & 1, status, 311);
+        tc_fence_after_sync();
+        for (int ks = 0; ks < 4; ++ks)
+          mma_ts(tmem + kColL + (it & 1) * 128, tmem + kColQ0 + ks * 8,
+                 smem_desc(sa + L::k0 + (it & 1) * kRowTile + ks * 32, 16, 1024), idesc_s, ks > 0);
+      };
+      auto issue_s = [&](int it) {                             // S = Q K^T
+        mbar_wait(&bar_k[it & 1], (it >> 1) & 1, status, 312);
+        tc_fence_after_sync();
+        for (int ks = 0; ks < 4; ++ks)
+          mma_ts(tmem + kColS, tmem + kColQ + ks * 8, smem_desc(sa + L::k + (it & 1) * kRowTile + ks * 32, 16, 1024),
+                 idesc_s, ks > 0);
+      };
+
+      mbar_expect_tx(&bar_q, (SELF ? 1 : 2) * kRowTile);
+      tma_load_4d(smem + L::q, &map_q, &bar_q, 0, i0, h, b);
+      if (!SELF) tma_load_4d(smem + L::q + kRowTile, &map_q, &bar_q, 0, i0, 0, b);
+      load_k0(0);
+      load_k(0);
+      load_v(0);
+      if (steps > 1) {
+        load_k0(1);
+        load_k(1);
+      }
+      mbar_wait(&bar_setup, 0, status, 317);                   // Q, Q0 in TMEM and the triangular tile in place
+      tc_fence_after_sync();
+      issue_l0(0);
+      issue_s(0);
+      mma_commit(&bar_l0);                                     // SELF: the selection pass reads S, so this covers S
+      for (int it = 0; it < steps; ++it) {
+        mbar_wait(&bar_sel, it & 1, status, 318);
+        tc_fence_after_sync();
+        for (int ks = 0; ks < 8; ++ks)                         // S -= TRI x selection
+          mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+                 smem_desc(sa + L::sel + ks * 2048, kRowTile, 1024), idesc_tri, 1);
+        mma_commit(&bar_tri);
+        if (!SELF && it + 1 < steps) {                         // L0 of the next step into the other L buffer
+          issue_l0(it + 1);
+          mma_commit(&bar_l0);
+        }
+        mbar_wait(&bar_tri, it & 1, status, 319);              // every MMA issued before the running sum is done:
+        if (it + 2 < steps) {                                  //   this step's K, K0 and the previous step's V are free
+          load_k0(it + 2);
+          load_k(it + 2);
+        }
+        if (it + 1 < steps) load_v(it + 1);
+        mbar_wait(&bar_p, it & 1, status, 320);
+        tc_fence_after_sync();
+        mbar_wait(&bar_v[it & 1], (it >> 1) & 1, status, 315);
+        tc_fence_after_sync();
+        for (int ks = 0; ks < 8; ++ks)                         // O += P V
+          mma_ss(tmem + kColO, smem_desc(sa + L::p + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+                 smem_desc(sa + L::v + (it & 1) * kRowTile + ks * 2048, kRowTile, 1024), idesc_pv,
+                 (it > 0 || ks > 0) ? 1u : 0u);
+        if (it + 1 < steps) {
+          issue_s(it + 1);
+          if (SELF) mma_commit(&bar_l0);                       // the selection pass of the next step reads S
+        } else {
+          mma_commit(&bar_fin);
+        }
+      }
+    }
+    __syncwarp();
+  } else {
+    // ======================================= arithmetic warps ============================================
+    const int row = tid & 127, wg = tid >> 7;
+    const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
+    auto arrive = [&](uint64_t* bar) {                         // this warp's shared-memory and TMEM writes are done
+      fence_async_smem();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar);
+    };
+    // Q and Q0 rows from the landing tiles into TMEM as bf16 pairs; warpgroup wg moves 16 of the 64 columns
+    mbar_wait(&bar_q, 0, status, 310);
+#pragma unroll
+    for (int m = 0; m < (SELF ? 1 : 2); ++m) {
+      const uint8_t* src = smem + L::q + m * kRowTile;
+      uint32_t w[8];
+#pragma unroll
+      for (int c = 0; c < 2; ++c) {
+        const uint4 v4 = *reinterpret_cast<const uint4*>(src + swz_off(row, wg * 2 + c));
+        w[4 * c] = v4.x; w[4 * c + 1] = v4.y; w[4 * c + 2] = v4.z; w[4 * c + 3] = v4.w;
+      }
+      tmem_st8(lane_base + (m == 0 ? kColQ : kColQ0) + wg * 8, w);
+    }
+    tmem_st_wait();
+    named_barrier(kWideBarrier, kWideCompute);                 // the landing tiles have been read by everyone
+    // strictly-lower-triangular ones TRI[i][r] = 1 for r < i over the landing area: a K-major A operand of two
+    // [128][64] tiles; thread (row, wg) writes running-sum indices r = 32 wg .. 32 wg + 31 of its row
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int chunk = wg * 4 + c;
+      uint32_t w[4];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const int r = chunk * 8 + 2 * e;
+        w[e] = pack_bf16(r < row ? 1.f : 0.f, (r + 1) < row ? 1.f : 0.f);
+      }
+      *reinterpret_cast<uint4*>(smem + L::q + (chunk >> 3) * kRowTile + swz_off(row, chunk & 7)) =
+          make_uint4(w[0], w[1], w[2], w[3]);
+    }
+    arrive(&bar_setup);
+
+    const float c1 = scale * kLog2e;
+    const float* carry_row = carry + ((int64_t)b * (ntiles + 1) + mi) * seq;
+    const int i = i0 + row;
+    const int cw = wg * NC;                                    // this warpgroup's key columns within a step
+    float run_max = -INFINITY, run_den = 0.f;                  // run_den: this warpgroup's share of the denominator
+
+    for (int it = 0; it < steps; ++it) {
+      const int j0 = (steps - 1 - it) * kTile;
+      if (tid < kTile) {
+        const int j = j0 + tid;
+        carry_s[it & 1][tid] = (j < seq) ? carry_row[j] * kLog2e : 0.f;
+      }
+      // ---- selection relu(L0) under the mask -> bf16; L0 of this step was issued a step ago ------------------
+      mbar_wait(&bar_l0, it & 1, status, 313);
+      tc_fence_after_sync();
+      {
+        uint32_t r[NC];
+        tmem_ld32(lane_base + (SELF ? kColS : kColL + (it & 1) * 128) + cw, r);
+        tmem_ld_wait();
+        float s[NC];
+        if ((j0 + kTile > i0) || (j0 < exempt)) {
+#pragma unroll
+          for (int e = 0; e < NC; ++e) {
+            const int j = j0 + cw + e;
+            s[e] = (j < i && j >= exempt) ? fmaxf(__uint_as_float(r[e]), 0.f) : 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < NC; ++e) s[e] = fmaxf(__uint_as_float(r[e]), 0.f);
+        }
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 w = make_uint4(pack_bf16(s[c * 8 + 0], s[c * 8 + 1]), pack_bf16(s[c * 8 + 2], s[c * 8 + 3]),
+                               pack_bf16(s[c * 8 + 4], s[c * 8 + 5]), pack_bf16(s[c * 8 + 6], s[c * 8 + 7]));
+          *reinterpret_cast<uint4*>(smem + L::sel + (wg >> 1) * kRowTile + swz_off(row, (wg & 1) * 4 + c)) = w;
+        }
+      }
+      arrive(&bar_sel);
+
+      // ---- online softmax of z = (S * scale - carry) * log2(e), after S -= TRI x selection --------------------
+      mbar_wait(&bar_tri, it & 1, status, 314);                // also: P V of the previous step has completed
+      tc_fence_after_sync();
+      float z[NC];
+      {
+        uint32_t r[NC];
+        tmem_ld32(lane_base + kColS + cw, r);
+        tmem_ld_wait();
+        const float* cs = carry_s[it & 1] + cw;
+        float tile_max = -INFINITY;
+        if (it == 0) {                                         // the diagonal tile
+#pragma unroll
+          for (int e = 0; e < NC; ++e) {
+            z[e] = (j0 + cw + e > i) ? -INFINITY : fmaf(__uint_as_float(r[e]), c1, -cs[e]);
+            tile_max = fmaxf(tile_max, z[e]);
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < NC; ++e) {
+            z[e] = fmaf(__uint_as_float(r[e]), c1, -cs[e]);
+            tile_max = fmaxf(tile_max, z[e]);
+          }
+        }
+        rmax_s[wg][row] = tile_max;
+      }
+      named_barrier(kWideBarrier, kWideCompute);
+      // every row has its own key in the diagonal tile, so the maximum is finite from the first step on
+      const float new_max =
+          fmaxf(fmaxf(run_max, fmaxf(rmax_s[0][row], rmax_s[1][row])), fmaxf(rmax_s[2][row], rmax_s[3][row]));
+      const float alpha = ex2(run_max - new_max);
+      run_max = new_max;
+      float rowsum = 0.f;
+#pragma unroll
+      for (int e = 0; e < NC; ++e) {
+        z[e] = ex2(z[e] - new_max);
+        rowsum += z[e];
+      }
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        uint4 w = make_uint4(pack_bf16(z[c * 8 + 0], z[c * 8 + 1]), pack_bf16(z[c * 8 + 2], z[c * 8 + 3]),
+                             pack_bf16(z[c * 8 + 4], z[c * 8 + 5]), pack_bf16(z[c * 8 + 6], z[c * 8 + 7]));
+        *reinterpret_cast<uint4*>(smem + L::p + (wg >> 1) * kRowTile + swz_off(row, (wg & 1) * 4 + c)) = w;
+      }
+      run_den = run_den * alpha + rowsum;
+      if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {   // the accumulator follows the maximum while it moves
+        uint32_t r[DH];
+        tmem_ld16(lane_base + kColO + wg * DH, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < DH; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
+        tmem_st16(lane_base + kColO + wg * DH, r);
+        tmem_st_wait();
+      }
+      arrive(&bar_p);
+    }
+    mbar_wait(&bar_fin, 0, status, 316);                       // the last P V
+    tc_fence_after_sync();
+
+    named_barrier(kWideBarrier, kWideCompute);                 // everyone has read the last row maxima
+    rmax_s[wg][row] = run_den;                                 // the warpgroups hold disjoint shares of the denominator
+    named_barrier(kWideBarrier, kWideCompute);
+    const float den = (rmax_s[0][row] + rmax_s[1][row]) + (rmax_s[2][row] + rmax_s[3][row]);
+    const float inv = 1.f / den;
+    uint32_t r[DH];
+    tmem_ld16(lane_base + kColO + wg * DH, r);
+    tmem_ld_wait();
+    if (i < seq) {
+      float4* orow = reinterpret_cast<float4*>(out + ((int64_t)n * seq + i) * D + wg * DH);
+#pragma unroll
+      for (int d = 0; d < DH; d += 4)
+        orow[d >> 2] = make_float4(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv,
+                                   __uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv);
+      if (wg == 0) lse2[(int64_t)n * seq + i] = run_max + log2f(den);
+    }
+  }
+  tc_fence_before_sync();
+  __syncthreads();
+  if (warp == 0) tmem_dealloc(tmem, 512);
+}
+
 template <int D>
 int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float* total, cudaStream_t s) {
   const int ntiles = (p.seq + kTile - 1) / kTile;
@@ -501,9 +815,28 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   }
   SA_CUDA_CHECK(cudaGetLastError());
 
-  const int fwd_smem = FwdSmem<D>::total + 1024;
   const unsigned grid = (unsigned)ntiles * p.batch * p.heads;
   const bool self = (p.heads == 1);            // one head per selector: the selection logits are the head's own
+  if constexpr (D == 64) {
+    CUtensorMap map_v128;
+    st = make_map_16bit(&map_v128, p.v.ptr, D, p.seq, p.heads, p.batch, p.v.st, p.v.sh, p.v.sb, kTile);
+    if (st != SA_OK) return st;
+    const int wide_smem = WideSmem::total + 1024;
+    if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(forward_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
+    else SA_CUDA_CHECK(cudaFuncSetAttribute(forward_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
+    {
+      ProfileScope prof(SA_KERNEL_TC_FORWARD, s);
+      if (self)
+        forward_wide_kernel<true><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, carry, out, lse2, p.heads,
+                                                                         p.seq, ntiles, p.exempt, p.scale, status);
+      else
+        forward_wide_kernel<false><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, carry, out, lse2, p.heads,
+                                                                          p.seq, ntiles, p.exempt, p.scale, status);
+    }
+    SA_CUDA_CHECK(cudaGetLastError());
+    return SA_OK;
+  }
+  const int fwd_smem = FwdSmem<D>::total + 1024;
   if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(forward_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem));
   else SA_CUDA_CHECK(cudaFuncSetAttribute(forward_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem));
   {
