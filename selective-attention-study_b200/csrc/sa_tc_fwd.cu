@@ -474,9 +474,10 @@ __global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
 // ---------------------------------------------------------------------------------------------------
 // Same arithmetic as forward_kernel, arranged so that one CTA keeps the tensor pipe and four warpgroups busy without
 // a second resident CTA: a step covers 128 keys (N = 128 MMAs run at the full tensor rate and the per-step barriers
-// are paid half as often), L0 is double-buffered in TMEM so the selection pass of the next step never waits for an
-// MMA, and the selection and probability tiles have separate shared-memory buffers so P V of one step runs under
-// the selection pass of the next.  The only MMA completion the arithmetic waits for is the triangular running sum.
+// are paid half as often), a control warp issues every load and MMA, and the steps are software-pipelined: after
+// the logits and the row maximum of step t the arithmetic warps write the selection tile of step t + 1 (L0 is
+// double-buffered in TMEM), and only then do the exponentials of step t, so S and the triangular running sum of
+// step t + 1 run on the tensor pipe under the exponentials instead of being waited for.
 struct WideSmem {
   static constexpr int q = 0;                          // landing tiles of Q and Q0, then the triangular ones (2 tiles)
   static constexpr int sel = q + 2 * kRowTile;         // [128 queries][128 keys] bf16 as two key tiles (B of the running sum)
@@ -509,8 +510,10 @@ __global__ void __launch_bounds__(kWideThreads, 1)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // bar_sel / bar_p: one arrival per arithmetic warp and step (selection tile written / P written, S read, O rescaled)
-  __shared__ uint64_t bar_q, bar_k[2], bar_k0[2], bar_v[2], bar_l0, bar_tri, bar_fin, bar_sel, bar_p, bar_setup;
+  // Completion barriers (one MMA commit each): bar_l0[j & 1] L0 of step j; bar_tri S and running sum of a step;
+  // bar_pv P V of a step; bar_fin the last P V.  Arrival barriers (one arrival per arithmetic warp and step):
+  // bar_sel selection tile written and the previous step's logits read; bar_p P written and O rescaled.
+  __shared__ uint64_t bar_q, bar_k[2], bar_k0[2], bar_v[2], bar_l0[2], bar_tri, bar_pv, bar_fin, bar_sel, bar_p, bar_setup;
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(16) float carry_s[2][kTile];
   __shared__ float rmax_s[4][kTile];
@@ -522,9 +525,10 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       mbar_init(&bar_k[u], 1);
       mbar_init(&bar_k0[u], 1);
       mbar_init(&bar_v[u], 1);
+      mbar_init(&bar_l0[u], 1);
     }
-    mbar_init(&bar_l0, 1);
     mbar_init(&bar_tri, 1);
+    mbar_init(&bar_pv, 1);
     mbar_init(&bar_fin, 1);
     mbar_init(&bar_sel, kWideCompute / 32);
     mbar_init(&bar_p, kWideCompute / 32);
@@ -546,7 +550,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         mbar_expect_tx(&bar_k[it & 1], kRowTile);
         tma_load_4d(smem + L::k + (it & 1) * kRowTile, &map_k, &bar_k[it & 1], 0, (steps - 1 - it) * kTile, h, b);
       };
-      auto load_k0 = [&](int it) {
+      auto load_k0 = [&](int it) {                             // SELF: K0 is K
         if (SELF) return;
         mbar_expect_tx(&bar_k0[it & 1], kRowTile);
         tma_load_4d(smem + L::k0 + (it & 1) * kRowTile, &map_k, &bar_k0[it & 1], 0, (steps - 1 - it) * kTile, 0, b);
@@ -559,19 +563,33 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       const uint32_t idesc_tri = instr_desc_bf16(128, 128, false, true, /*negate_a=*/true);
       const uint32_t idesc_pv = instr_desc_bf16(128, D, false, true);
       auto issue_l0 = [&](int it) {                            // L0 = Q0 K0^T into the L buffer of the step
-        if (SELF) return;
-        mbar_wait(&bar_k0[it & 1], (it >> 1) & 1, status, 311);
+        mbar_wait(SELF ? &bar_k[it & 1] : &bar_k0[it & 1], (it >> 1) & 1, status, 311);
         tc_fence_after_sync();
+        const uint32_t tile = sa + (SELF ? L::k : L::k0) + (it & 1) * kRowTile;
         for (int ks = 0; ks < 4; ++ks)
-          mma_ts(tmem + kColL + (it & 1) * 128, tmem + kColQ0 + ks * 8,
-                 smem_desc(sa + L::k0 + (it & 1) * kRowTile + ks * 32, 16, 1024), idesc_s, ks > 0);
+          mma_ts(tmem + kColL + (it & 1) * 128, tmem + (SELF ? kColQ : kColQ0) + ks * 8, smem_desc(tile + ks * 32, 16, 1024),
+                 idesc_s, ks > 0);
+        mma_commit(&bar_l0[it & 1]);
       };
-      auto issue_s = [&](int it) {                             // S = Q K^T
+      auto issue_s_tri = [&](int it) {                         // S = Q K^T, then S -= TRI x selection
         mbar_wait(&bar_k[it & 1], (it >> 1) & 1, status, 312);
         tc_fence_after_sync();
         for (int ks = 0; ks < 4; ++ks)
           mma_ts(tmem + kColS, tmem + kColQ + ks * 8, smem_desc(sa + L::k + (it & 1) * kRowTile + ks * 32, 16, 1024),
                  idesc_s, ks > 0);
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+                 smem_desc(sa + L::sel + ks * 2048, kRowTile, 1024), idesc_tri, 1);
+        mma_commit(&bar_tri);
+      };
+      auto issue_pv = [&](int it, uint64_t* bar) {             // O += P V
+        mbar_wait(&bar_v[it & 1], (it >> 1) & 1, status, 315);
+        tc_fence_after_sync();
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem + kColO, smem_desc(sa + L::p + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+                 smem_desc(sa + L::v + (it & 1) * kRowTile + ks * 2048, kRowTile, 1024), idesc_pv,
+                 (it > 0 || ks > 0) ? 1u : 0u);
+        mma_commit(bar);
       };
 
       mbar_expect_tx(&bar_q, (SELF ? 1 : 2) * kRowTile);
@@ -583,51 +601,42 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       if (steps > 1) {
         load_k0(1);
         load_k(1);
+        load_v(1);
       }
       mbar_wait(&bar_setup, 0, status, 317);                   // Q, Q0 in TMEM and the triangular tile in place
       tc_fence_after_sync();
       issue_l0(0);
-      issue_s(0);
-      mma_commit(&bar_l0);                                     // SELF: the selection pass reads S, so this covers S
+      if (steps > 1) issue_l0(1);
       for (int it = 0; it < steps; ++it) {
-        mbar_wait(&bar_sel, it & 1, status, 318);
+        mbar_wait(&bar_sel, it & 1, status, 318);              // selection of step it written; logits of it - 1 read
         tc_fence_after_sync();
-        for (int ks = 0; ks < 8; ++ks)                         // S -= TRI x selection
-          mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
-                 smem_desc(sa + L::sel + ks * 2048, kRowTile, 1024), idesc_tri, 1);
-        mma_commit(&bar_tri);
-        if (!SELF && it + 1 < steps) {                         // L0 of the next step into the other L buffer
-          issue_l0(it + 1);
-          mma_commit(&bar_l0);
+        if (it + 2 < steps) load_k0(it + 2);                   // L0 of step it has been consumed
+        issue_s_tri(it);
+        if (it > 0) {
+          mbar_wait(&bar_p, (it - 1) & 1, status, 320);        // P of step it - 1 written, O rescaled
+          tc_fence_after_sync();
+          if (it >= 2) {                                       // before this barrier's next commit: P V of it - 2 done,
+            mbar_wait(&bar_pv, it & 1, status, 321);           //   so its V tile may be refilled
+            if (it < steps) load_v(it);
+          }
+          issue_pv(it - 1, &bar_pv);
         }
-        mbar_wait(&bar_tri, it & 1, status, 319);              // every MMA issued before the running sum is done:
-        if (it + 2 < steps) {                                  //   this step's K, K0 and the previous step's V are free
-          load_k0(it + 2);
+        mbar_wait(&bar_tri, it & 1, status, 319);              // S of step it done: its K tile is free
+        if (it + 2 < steps) {
           load_k(it + 2);
-        }
-        if (it + 1 < steps) load_v(it + 1);
-        mbar_wait(&bar_p, it & 1, status, 320);
-        tc_fence_after_sync();
-        mbar_wait(&bar_v[it & 1], (it >> 1) & 1, status, 315);
-        tc_fence_after_sync();
-        for (int ks = 0; ks < 8; ++ks)                         // O += P V
-          mma_ss(tmem + kColO, smem_desc(sa + L::p + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
-                 smem_desc(sa + L::v + (it & 1) * kRowTile + ks * 2048, kRowTile, 1024), idesc_pv,
-                 (it > 0 || ks > 0) ? 1u : 0u);
-        if (it + 1 < steps) {
-          issue_s(it + 1);
-          if (SELF) mma_commit(&bar_l0);                       // the selection pass of the next step reads S
-        } else {
-          mma_commit(&bar_fin);
+          issue_l0(it + 2);                                    // its L buffer was read by the selection pass of step it
         }
       }
+      mbar_wait(&bar_p, (steps - 1) & 1, status, 322);
+      tc_fence_after_sync();
+      issue_pv(steps - 1, &bar_fin);
     }
     __syncwarp();
   } else {
     // ======================================= arithmetic warps ============================================
     const int row = tid & 127, wg = tid >> 7;
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-    auto arrive = [&](uint64_t* bar) {                         // this warp's shared-memory and TMEM writes are done
+    auto arrive = [&](uint64_t* bar) {                         // this warp's shared-memory and TMEM accesses are done
       fence_async_smem();
       tc_fence_before_sync();
       __syncwarp();
@@ -668,43 +677,50 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     const float* carry_row = carry + ((int64_t)b * (ntiles + 1) + mi) * seq;
     const int i = i0 + row;
     const int cw = wg * NC;                                    // this warpgroup's key columns within a step
-    float run_max = -INFINITY, run_den = 0.f;                  // run_den: this warpgroup's share of the denominator
 
-    for (int it = 0; it < steps; ++it) {
+    // selection relu(L0) under the mask of step `it` -> bf16 tile, in two halves of 16 columns; also stages the
+    // step's carry (scaled) for the logits pass
+    auto selection = [&](int it) {
       const int j0 = (steps - 1 - it) * kTile;
       if (tid < kTile) {
         const int j = j0 + tid;
         carry_s[it & 1][tid] = (j < seq) ? carry_row[j] * kLog2e : 0.f;
       }
-      // ---- selection relu(L0) under the mask -> bf16; L0 of this step was issued a step ago ------------------
-      mbar_wait(&bar_l0, it & 1, status, 313);
+      mbar_wait(&bar_l0[it & 1], (it >> 1) & 1, status, 313);
       tc_fence_after_sync();
-      {
-        uint32_t r[NC];
-        tmem_ld32(lane_base + (SELF ? kColS : kColL + (it & 1) * 128) + cw, r);
-        tmem_ld_wait();
-        float s[NC];
-        if ((j0 + kTile > i0) || (j0 < exempt)) {
+      const bool masked = (j0 + kTile > i0) || (j0 < exempt);
 #pragma unroll
-          for (int e = 0; e < NC; ++e) {
-            const int j = j0 + cw + e;
+      for (int hc = 0; hc < 2; ++hc) {
+        uint32_t r[16];
+        tmem_ld16(lane_base + kColL + (it & 1) * 128 + cw + hc * 16, r);
+        tmem_ld_wait();
+        float s[16];
+        if (masked) {
+#pragma unroll
+          for (int e = 0; e < 16; ++e) {
+            const int j = j0 + cw + hc * 16 + e;
             s[e] = (j < i && j >= exempt) ? fmaxf(__uint_as_float(r[e]), 0.f) : 0.f;
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < NC; ++e) s[e] = fmaxf(__uint_as_float(r[e]), 0.f);
+          for (int e = 0; e < 16; ++e) s[e] = fmaxf(__uint_as_float(r[e]), 0.f);
         }
 #pragma unroll
-        for (int c = 0; c < 4; ++c) {
+        for (int c = 0; c < 2; ++c) {
           uint4 w = make_uint4(pack_bf16(s[c * 8 + 0], s[c * 8 + 1]), pack_bf16(s[c * 8 + 2], s[c * 8 + 3]),
                                pack_bf16(s[c * 8 + 4], s[c * 8 + 5]), pack_bf16(s[c * 8 + 6], s[c * 8 + 7]));
-          *reinterpret_cast<uint4*>(smem + L::sel + (wg >> 1) * kRowTile + swz_off(row, (wg & 1) * 4 + c)) = w;
+          *reinterpret_cast<uint4*>(smem + L::sel + (wg >> 1) * kRowTile + swz_off(row, (wg & 1) * 4 + hc * 2 + c)) = w;
         }
       }
       arrive(&bar_sel);
+    };
 
-      // ---- online softmax of z = (S * scale - carry) * log2(e), after S -= TRI x selection --------------------
-      mbar_wait(&bar_tri, it & 1, status, 314);                // also: P V of the previous step has completed
+    float run_max = -INFINITY, run_den = 0.f;                  // run_den: this warpgroup's share of the denominator
+    selection(0);
+    for (int it = 0; it < steps; ++it) {
+      const int j0 = (steps - 1 - it) * kTile;
+      // ---- logits z = (S * scale - carry) * log2(e) after S -= TRI x selection, and the row maximum -----------
+      mbar_wait(&bar_tri, it & 1, status, 314);
       tc_fence_after_sync();
       float z[NC];
       {
@@ -734,11 +750,21 @@ __global__ void __launch_bounds__(kWideThreads, 1)
           fmaxf(fmaxf(run_max, fmaxf(rmax_s[0][row], rmax_s[1][row])), fmaxf(rmax_s[2][row], rmax_s[3][row]));
       const float alpha = ex2(run_max - new_max);
       run_max = new_max;
+
+      // ---- the next step's selection tile first: its S and running sum then run under the exponentials --------
+      if (it + 1 < steps) selection(it + 1);
+
+      // ---- exponentials, P, and the accumulator rescale ---------------------------------------------------------
       float rowsum = 0.f;
 #pragma unroll
       for (int e = 0; e < NC; ++e) {
         z[e] = ex2(z[e] - new_max);
         rowsum += z[e];
+      }
+      run_den = run_den * alpha + rowsum;
+      if (it > 0) {
+        mbar_wait(&bar_pv, (it - 1) & 1, status, 323);         // P V of the previous step: P tile and O are free
+        tc_fence_after_sync();
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
@@ -746,7 +772,6 @@ __global__ void __launch_bounds__(kWideThreads, 1)
                              pack_bf16(z[c * 8 + 4], z[c * 8 + 5]), pack_bf16(z[c * 8 + 6], z[c * 8 + 7]));
         *reinterpret_cast<uint4*>(smem + L::p + (wg >> 1) * kRowTile + swz_off(row, (wg & 1) * 4 + c)) = w;
       }
-      run_den = run_den * alpha + rowsum;
       if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {   // the accumulator follows the maximum while it moves
         uint32_t r[DH];
         tmem_ld16(lane_base + kColO + wg * DH, r);
