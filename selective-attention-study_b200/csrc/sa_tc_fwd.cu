@@ -32,6 +32,14 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
+// A global load the compiler must issue where it is written (volatile asm keeps its place among the other
+// volatile asm statements), so a value fetched one step ahead is really in flight during that step.
+__device__ __forceinline__ float load_ahead(const float* p) {
+  float v;
+  asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
+  return v;
+}
+
 // ---------------------------------------------------------------------------------------------------
 // selection column sums
 // ---------------------------------------------------------------------------------------------------
@@ -678,14 +686,17 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     const int i = i0 + row;
     const int cw = wg * NC;                                    // this warpgroup's key columns within a step
 
+    // The carry of a step's keys is fetched from global memory a step before it is staged, so the load's latency
+    // is spent under the exponentials of the step before.
+    auto fetch_carry = [&](int it) {
+      const int j = (steps - 1 - it) * kTile + tid;
+      return (tid < kTile && it < steps && j < seq) ? load_ahead(carry_row + j) : 0.f;
+    };
     // selection relu(L0) under the mask of step `it` -> bf16 tile, in two halves of 16 columns; also stages the
     // step's carry (scaled) for the logits pass
-    auto selection = [&](int it) {
+    auto selection = [&](int it, float carry_value) {
       const int j0 = (steps - 1 - it) * kTile;
-      if (tid < kTile) {
-        const int j = j0 + tid;
-        carry_s[it & 1][tid] = (j < seq) ? carry_row[j] * kLog2e : 0.f;
-      }
+      if (tid < kTile) carry_s[it & 1][tid] = carry_value * kLog2e;
       mbar_wait(&bar_l0[it & 1], (it >> 1) & 1, status, 313);
       tc_fence_after_sync();
       const bool masked = (j0 + kTile > i0) || (j0 < exempt);
@@ -716,7 +727,8 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     };
 
     float run_max = -INFINITY, run_den = 0.f;                  // run_den: this warpgroup's share of the denominator
-    selection(0);
+    selection(0, fetch_carry(0));
+    float next_carry = fetch_carry(1);
     for (int it = 0; it < steps; ++it) {
       const int j0 = (steps - 1 - it) * kTile;
       // ---- logits z = (S * scale - carry) * log2(e) after S -= TRI x selection, and the row maximum -----------
@@ -752,7 +764,8 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       run_max = new_max;
 
       // ---- the next step's selection tile first: its S and running sum then run under the exponentials --------
-      if (it + 1 < steps) selection(it + 1);
+      if (it + 1 < steps) selection(it + 1, next_carry);
+      next_carry = fetch_carry(it + 2);
 
       // ---- exponentials, P, and the accumulator rescale ---------------------------------------------------------
       float rowsum = 0.f;
