@@ -11,7 +11,10 @@
 //                   the selection mask is written to shared memory as bf16 and the in-tile exclusive running
 //                   sum over queries is one more MMA, (-strictly-lower-triangular ones) x selection,
 //                   accumulated into S; then online softmax in the log2 domain with the cross-tile carry
-//                   subtracted per key, and O += P V in TMEM.
+//                   subtracted per key, and O += P V in TMEM.  Used for head_dim 128.
+//   forward_wide_kernel  the same arithmetic for head_dim 64 with 128-key steps, one CTA per SM: four
+//                   arithmetic warpgroups and a control warp that issues every load and MMA, steps
+//                   software-pipelined so the tensor pipe works under the exponentials.
 //
 // Reference for the arithmetic: src/selective_attention/kernels.py:100-194 (selection, carry, forward).
 #include "sa_tc_host.cuh"
