@@ -699,7 +699,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     // step's carry (scaled) for the logits pass
     auto selection = [&](int it, float carry_value) {
       const int j0 = (steps - 1 - it) * kTile;
-      if (tid < kTile) carry_s[it & 1][tid] = carry_value * kLog2e;
+      if (tid < kTile) carry_s[it & 1][tid] = -carry_value * kLog2e;   // negated: the logits pass adds it in an FMA
       mbar_wait(&bar_l0[it & 1], (it >> 1) & 1, status, 313);
       tc_fence_after_sync();
       const bool masked = (j0 + kTile > i0) || (j0 < exempt);
@@ -713,16 +713,16 @@ __global__ void __launch_bounds__(kWideThreads, 1)
 #pragma unroll
           for (int e = 0; e < 16; ++e) {
             const int j = j0 + cw + hc * 16 + e;
-            s[e] = (j < i && j >= exempt) ? fmaxf(__uint_as_float(r[e]), 0.f) : 0.f;
+            s[e] = (j < i && j >= exempt) ? __uint_as_float(r[e]) : 0.f;
           }
         } else {
 #pragma unroll
-          for (int e = 0; e < 16; ++e) s[e] = fmaxf(__uint_as_float(r[e]), 0.f);
+          for (int e = 0; e < 16; ++e) s[e] = __uint_as_float(r[e]);
         }
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          uint4 w = make_uint4(pack_bf16(s[c * 8 + 0], s[c * 8 + 1]), pack_bf16(s[c * 8 + 2], s[c * 8 + 3]),
-                               pack_bf16(s[c * 8 + 4], s[c * 8 + 5]), pack_bf16(s[c * 8 + 6], s[c * 8 + 7]));
+        for (int c = 0; c < 2; ++c) {                          // the relu rides on the bf16 conversion
+          uint4 w = make_uint4(pack_bf16_relu(s[c * 8 + 0], s[c * 8 + 1]), pack_bf16_relu(s[c * 8 + 2], s[c * 8 + 3]),
+                               pack_bf16_relu(s[c * 8 + 4], s[c * 8 + 5]), pack_bf16_relu(s[c * 8 + 6], s[c * 8 + 7]));
           *reinterpret_cast<uint4*>(smem + L::sel + (wg >> 1) * kRowTile + swz_off(row, (wg & 1) * 4 + hc * 2 + c)) = w;
         }
       }
@@ -737,25 +737,32 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       // ---- logits z = (S * scale - carry) * log2(e) after S -= TRI x selection, and the row maximum -----------
       mbar_wait(&bar_tri, it & 1, status, 314);
       tc_fence_after_sync();
-      float z[NC];
+      // Packed fp32x2 arithmetic (two results per issue slot) for the logits, the shift by the maximum and the row sum.
+      float2 z[NC / 2];
       {
         uint32_t r[NC];
         tmem_ld32(lane_base + kColS + cw, r);
         tmem_ld_wait();
-        const float* cs = carry_s[it & 1] + cw;
+        const float4* ncs = reinterpret_cast<const float4*>(carry_s[it & 1] + cw);   // -carry * log2(e), broadcast loads
+        const float2 cc = make_float2(c1, c1);
         float tile_max = -INFINITY;
-        if (it == 0) {                                         // the diagonal tile
 #pragma unroll
-          for (int e = 0; e < NC; ++e) {
-            z[e] = (j0 + cw + e > i) ? -INFINITY : fmaf(__uint_as_float(r[e]), c1, -cs[e]);
-            tile_max = fmaxf(tile_max, z[e]);
+        for (int e4 = 0; e4 < NC / 4; ++e4) {
+          const float4 nc = ncs[e4];
+          float2 a = __ffma2_rn(make_float2(__uint_as_float(r[4 * e4]), __uint_as_float(r[4 * e4 + 1])), cc,
+                                make_float2(nc.x, nc.y));
+          float2 b2 = __ffma2_rn(make_float2(__uint_as_float(r[4 * e4 + 2]), __uint_as_float(r[4 * e4 + 3])), cc,
+                                 make_float2(nc.z, nc.w));
+          if (it == 0) {                                       // the diagonal tile
+            const int jj = j0 + cw + 4 * e4;
+            if (jj > i) a.x = -INFINITY;
+            if (jj + 1 > i) a.y = -INFINITY;
+            if (jj + 2 > i) b2.x = -INFINITY;
+            if (jj + 3 > i) b2.y = -INFINITY;
           }
-        } else {
-#pragma unroll
-          for (int e = 0; e < NC; ++e) {
-            z[e] = fmaf(__uint_as_float(r[e]), c1, -cs[e]);
-            tile_max = fmaxf(tile_max, z[e]);
-          }
+          tile_max = fmaxf(fmaxf(tile_max, fmaxf(a.x, a.y)), fmaxf(b2.x, b2.y));
+          z[2 * e4] = a;
+          z[2 * e4 + 1] = b2;
         }
         rmax_s[wg][row] = tile_max;
       }
@@ -771,21 +778,23 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       next_carry = fetch_carry(it + 2);
 
       // ---- exponentials, P, and the accumulator rescale ---------------------------------------------------------
-      float rowsum = 0.f;
+      float2 rs = make_float2(0.f, 0.f);
+      const float2 nm = make_float2(-new_max, -new_max);
 #pragma unroll
-      for (int e = 0; e < NC; ++e) {
-        z[e] = ex2(z[e] - new_max);
-        rowsum += z[e];
+      for (int e = 0; e < NC / 2; ++e) {
+        const float2 x = __fadd2_rn(z[e], nm);
+        z[e] = make_float2(ex2(x.x), ex2(x.y));
+        rs = __fadd2_rn(rs, z[e]);
       }
-      run_den = run_den * alpha + rowsum;
+      run_den = run_den * alpha + (rs.x + rs.y);
       if (it > 0) {
         mbar_wait(&bar_pv, (it - 1) & 1, status, 323);         // P V of the previous step: P tile and O are free
         tc_fence_after_sync();
       }
 #pragma unroll
       for (int c = 0; c < 4; ++c) {
-        uint4 w = make_uint4(pack_bf16(z[c * 8 + 0], z[c * 8 + 1]), pack_bf16(z[c * 8 + 2], z[c * 8 + 3]),
-                             pack_bf16(z[c * 8 + 4], z[c * 8 + 5]), pack_bf16(z[c * 8 + 6], z[c * 8 + 7]));
+        uint4 w = make_uint4(pack_bf16(z[c * 4].x, z[c * 4].y), pack_bf16(z[c * 4 + 1].x, z[c * 4 + 1].y),
+                             pack_bf16(z[c * 4 + 2].x, z[c * 4 + 2].y), pack_bf16(z[c * 4 + 3].x, z[c * 4 + 3].y));
         *reinterpret_cast<uint4*>(smem + L::p + (wg >> 1) * kRowTile + swz_off(row, (wg & 1) * 4 + c)) = w;
       }
       if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {   // the accumulator follows the maximum while it moves
