@@ -105,8 +105,8 @@ struct HalfCtx {
   bool selectable;         // key >= exempt
   float cnl;               // log2(e) * selection received through the END of this query tile
   float c1;                // scale * log2(e)
-  const float* lse_s;
-  const float* dbar_s;
+  const float* lse_s;      // -lse2 of the tile's queries (padded queries: -inf)
+  const float* dbar_s;     // -dbar
   float (*sel_tot)[kTile];
   float (*dz_tot)[kTile];
   uint64_t* bar_early;     // arrived once per half when P^T and dz are in place and the score columns are free
@@ -162,16 +162,24 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
 
   tmem_ld16(c.lane_base + kColST + colw, r);
   tmem_ld_wait();
+  // Packed fp32x2 arithmetic (two results per issue slot) for the elementwise parts.
+  const float2 cc = make_float2(c.c1, c.c1);
+  const float2 ncb = make_float2(-cb, -cb);
 #pragma unroll
   for (int e4 = 0; e4 < 16; e4 += 4) {                  // row statistics: one 16-byte broadcast load per 4 queries
     const float4 st4 = *reinterpret_cast<const float4*>(c.lse_s + col0 + e4);
-    const float st[4] = {st4.x, st4.y, st4.z, st4.w};
+    const float2 st[2] = {make_float2(st4.x, st4.y), make_float2(st4.z, st4.w)};
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      const int e = e4 + k;
-      const float t2 = fmaf(c.c1, ls[e], -(cb + st[k]));
-      p[e] = ex2(fmaf(__uint_as_float(r[e]), c.c1, t2));
-      if (DIAG && (c.row > col0 + e)) p[e] = 0.f;       // key after the query
+    for (int k = 0; k < 2; ++k) {
+      const int e = e4 + 2 * k;
+      const float2 t2 = __ffma2_rn(cc, make_float2(ls[e], ls[e + 1]), __fadd2_rn(st[k], ncb));     // c1 ls - (cb + lse)
+      const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), cc, t2);
+      p[e] = ex2(x.x);
+      p[e + 1] = ex2(x.y);
+      if (DIAG) {                                       // key after the query
+        if (c.row > col0 + e) p[e] = 0.f;
+        if (c.row > col0 + e + 1) p[e + 1] = 0.f;
+      }
     }
   }
   {                                                     // P^T as bf16 pairs into the (consumed) L0^T columns
@@ -186,10 +194,13 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
 #pragma unroll
   for (int e4 = 0; e4 < 16; e4 += 4) {
     const float4 st4 = *reinterpret_cast<const float4*>(c.dbar_s + col0 + e4);
-    p[e4] = p[e4] * (__uint_as_float(r[e4]) - st4.x);                                 // dz
-    p[e4 + 1] = p[e4 + 1] * (__uint_as_float(r[e4 + 1]) - st4.y);
-    p[e4 + 2] = p[e4 + 2] * (__uint_as_float(r[e4 + 2]) - st4.z);
-    p[e4 + 3] = p[e4 + 3] * (__uint_as_float(r[e4 + 3]) - st4.w);
+    const float2 d0 = __fmul2_rn(make_float2(p[e4], p[e4 + 1]),                                   // dz = P (dP - dbar)
+                                 __fadd2_rn(make_float2(__uint_as_float(r[e4]), __uint_as_float(r[e4 + 1])),
+                                            make_float2(st4.x, st4.y)));
+    const float2 d1 = __fmul2_rn(make_float2(p[e4 + 2], p[e4 + 3]),
+                                 __fadd2_rn(make_float2(__uint_as_float(r[e4 + 2]), __uint_as_float(r[e4 + 3])),
+                                            make_float2(st4.z, st4.w)));
+    p[e4] = d0.x; p[e4 + 1] = d0.y; p[e4 + 2] = d1.x; p[e4 + 3] = d1.y;
   }
   if (!SELF) {
     put8(c.smem + L::dz, c.row, col0, p);
@@ -224,14 +235,22 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   }
   const float base = dz_state + later;
   dz_state += all;
+  const float2 bb = make_float2(base, base);
   if (SELF) {
 #pragma unroll
-    for (int e = 0; e < 16; ++e) lx[e] = fmaf(negon[e], base + lx[e], p[e]);                       // dz + g
+    for (int e = 0; e < 16; e += 2) {                                                              // dz + g
+      const float2 x = __ffma2_rn(make_float2(negon[e], negon[e + 1]), __fadd2_rn(make_float2(lx[e], lx[e + 1]), bb),
+                                  make_float2(p[e], p[e + 1]));
+      lx[e] = x.x; lx[e + 1] = x.y;
+    }
     put8(c.smem + L::dz, c.row, col0, lx);
     put8(c.smem + L::dz, c.row, col0 + 8, lx + 8);
   } else {
 #pragma unroll
-    for (int e = 0; e < 16; ++e) lx[e] = negon[e] * (base + lx[e]);                                // g
+    for (int e = 0; e < 16; e += 2) {                                                              // g
+      const float2 x = __fmul2_rn(make_float2(negon[e], negon[e + 1]), __fadd2_rn(make_float2(lx[e], lx[e + 1]), bb));
+      lx[e] = x.x; lx[e + 1] = x.y;
+    }
     put8(c.smem + L::g, c.row, col0, lx);
     put8(c.smem + L::g, c.row, col0 + 8, lx + 8);
   }
@@ -466,8 +485,8 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       const bool diag = (mi == nj);
       SA_MARK(marks, 12)
       if (tid < kTile) {
-        lse_s[tid] = next_lse;
-        dbar_s[tid] = next_dbar;
+        lse_s[tid] = -next_lse;                                // negated: both enter packed adds directly
+        dbar_s[tid] = -next_dbar;
       }
       ctx.cnl = next_carry * kLog2e;
       if (it + 1 < n_iter) {
