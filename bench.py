@@ -52,7 +52,7 @@ FALLBACK_BF16_TFLOPS = 1590.0      # earlier measurement on this pool (burst); u
 
 # dram__bytes_read.sum + dram__bytes_write.sum per launch of the backward kernel, from the ncu capture
 # summarised under profiles/ (captured on a smaller case and scaled by head-tiles; None = not captured).
-BACKWARD_DRAM_TRAFFIC_PER_HEAD_TILE = 1368.54e6 / 132096   # B=1 capture, profiles/backward_kernel_B1_H16_T16384_D64.md
+BACKWARD_DRAM_TRAFFIC_PER_HEAD_TILE = 1375.65e6 / 132096   # B=1 capture, profiles/backward_kernel_B1_H16_T16384_D64.md
 
 
 def pairs(seq: int) -> float:
