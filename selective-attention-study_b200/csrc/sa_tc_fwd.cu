@@ -6,15 +6,14 @@
 //                   COLSUM[b][query tile][key].
 //   scan_kernel     exclusive prefix of COLSUM across query tiles, in place (-> CARRY), plus one extra
 //                   row holding the grand total.  One thread per key column; bandwidth-bound.
-//   forward_kernel  flash-style forward for one 128-query tile of one head over 64-key steps, taken from the
-//                   diagonal back to key 0: S = Q K^T and L0 = Q0 K0^T by MMA (Q, Q0 in TMEM); relu(L0) under
+//   forward_wide_kernel  flash-style forward for one 128-query tile of one head over 128-key steps, taken from
+//                   the diagonal back to key 0: S = Q K^T and L0 = Q0 K0^T by MMA (Q, Q0 in TMEM); relu(L0) under
 //                   the selection mask is written to shared memory as bf16 and the in-tile exclusive running
 //                   sum over queries is one more MMA, (-strictly-lower-triangular ones) x selection,
 //                   accumulated into S; then online softmax in the log2 domain with the cross-tile carry
-//                   subtracted per key, and O += P V in TMEM.  Used for head_dim 128.
-//   forward_wide_kernel  the same arithmetic for head_dim 64 with 128-key steps, one CTA per SM: four
-//                   arithmetic warpgroups and a control warp that issues every load and MMA, steps
-//                   software-pipelined so the tensor pipe works under the exponentials.
+//                   subtracted per key, and O += P V in TMEM.  Four arithmetic warpgroups and a control warp
+//                   that issues every load and MMA; steps software-pipelined so the tensor pipe works under
+//                   the exponentials.  head_dim 64 and 128.
 //
 // Reference for the arithmetic: src/selective_attention/kernels.py:100-194 (selection, carry, forward).
 #include "sa_tc_host.cuh"
@@ -25,9 +24,7 @@ namespace tc {
 namespace {
 
 constexpr int kTile = 128;          // query rows per CTA; also the carry checkpoint spacing
-constexpr int kKeys = 64;           // keys per forward step
 constexpr int kRowTile = 16384;     // bytes of a [128][64] bf16 operand tile
-constexpr int kKeyTile = 8192;      // bytes of a [64][64] bf16 operand tile
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -170,347 +167,60 @@ __global__ void __launch_bounds__(256) scan_kernel(float* __restrict__ carry, fl
 // ---------------------------------------------------------------------------------------------------
 // forward
 // ---------------------------------------------------------------------------------------------------
-template <int D>
-struct FwdSmem {
-  static constexpr int DK = D / 64;
-  static constexpr int q = 0;                         // landing tiles of Q, then (D = 64: with q0) the triangular ones
-  static constexpr int q0 = q + DK * kRowTile;
-  static constexpr int selp = q0 + DK * kRowTile;     // [128][64]: selection (B operand), then P (A operand)
-  static constexpr int k = selp + kRowTile;           // DK tiles [64][64]
-  static constexpr int k0 = k + DK * kKeyTile;
-  static constexpr int v = k0 + DK * kKeyTile;        // DK tiles [64 keys][64]
-  static constexpr int total = v + DK * kKeyTile;
-};
-
-constexpr int kFwdThreads = 256;      // two warpgroups: each owns 32 of a step's 64 key columns and half of D
-
-// One 128-query tile of one head.  Key steps of 64 run from the diagonal back to key 0: the keys nearest the query
-// carry the least history, so the running maximum settles within the first steps and the output accumulator,
-// which stays in TMEM for the whole loop, is rescaled only while the maximum still moves.  Per step the tensor
-// pipe gets two batches: (P V of the previous step, L0 and S of this one) and the triangular running-sum MMA.
-// SELF: one head per selector (the per-head form), so L0 is S itself and the Q0 / K0 tiles and their MMA are left out.
-template <int D, bool SELF>
-__global__ void __launch_bounds__(kFwdThreads, (D == 64) ? 2 : 1)
-    forward_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                   const __grid_constant__ CUtensorMap map_v, const float* __restrict__ carry,
-                   float* __restrict__ out, float* __restrict__ lse2, int heads, int seq, int ntiles, int exempt,
-                   float scale, unsigned int* status) {
-  using L = FwdSmem<D>;
-  constexpr int DK = D / 64;
-  constexpr int DH = D / 2;                                   // output columns per warpgroup
-  // TMEM columns: S and L0 (fp32, 64 each), the output accumulator (D), and the stationary A operands Q and Q0 as
-  // bf16 pairs (D / 2 columns each), so the per-step logit MMAs fetch only B from shared memory.
-  constexpr uint32_t kTmemCols = (D == 64) ? 256 : 512;
-  constexpr uint32_t kColS = 0, kColL = 64, kColO = 128, kColQ = kColO + D, kColQ0 = kColQ + D / 2;
-
-  const int nrows = gridDim.x / ntiles;                       // batch * heads
-  const int mi = ntiles - 1 - (int)(blockIdx.x / nrows);      // heaviest query tiles first
-  const int n = blockIdx.x % nrows;
-  const int b = n / heads, h = n - b * heads;
-  const int i0 = mi * kTile;
-  const int steps = (min(i0 + kTile, seq) + kKeys - 1) / kKeys;
-
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar_q, bar_k, bar_v, bar_mma;
-  __shared__ uint32_t tmem_base_s;
-  __shared__ __align__(16) float carry_s[2][kKeys];
-  __shared__ float rmax_s[2][kTile];
-
-  const int tid = threadIdx.x, warp = tid >> 5;
-  const int row = tid & 127, wg = tid >> 7;
-  if (tid == 0) {
-    mbar_init(&bar_q, 1);
-    mbar_init(&bar_k, 1);
-    mbar_init(&bar_v, 1);
-    mbar_init(&bar_mma, 1);
-    mbar_init_fence();
-  }
-  if (warp == 0) tmem_alloc(&tmem_base_s, kTmemCols);
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-  const uint32_t tmem = tmem_base_s;
-  const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);
-  const uint32_t sa = smem_u32(smem);
-
-  auto load_k = [&](int t) {
-    mbar_expect_tx(&bar_k, (SELF ? 1 : 2) * DK * kKeyTile);
-    for (int s = 0; s < DK; ++s) {
-      tma_load_4d(smem + L::k + s * kKeyTile, &map_k, &bar_k, s * 64, t * kKeys, h, b);
-      if (!SELF) tma_load_4d(smem + L::k0 + s * kKeyTile, &map_k, &bar_k, s * 64, t * kKeys, 0, b);
-    }
-  };
-  auto load_v = [&](int t) {
-    mbar_expect_tx(&bar_v, DK * kKeyTile);
-    for (int s = 0; s < DK; ++s) tma_load_4d(smem + L::v + s * kKeyTile, &map_v, &bar_v, s * 64, t * kKeys, h, b);
-  };
-  if (tid == 0) {
-    mbar_expect_tx(&bar_q, (SELF ? 1 : 2) * DK * kRowTile);
-    for (int s = 0; s < DK; ++s) {
-      tma_load_4d(smem + L::q + s * kRowTile, &map_q, &bar_q, s * 64, i0, h, b);
-      if (!SELF) tma_load_4d(smem + L::q0 + s * kRowTile, &map_q, &bar_q, s * 64, i0, 0, b);
-    }
-    load_k(steps - 1);
-    load_v(steps - 1);
-  }
-  // Q and Q0 rows from the TMA landing tiles (128-byte swizzle) into TMEM; warpgroup wg moves D / 2 of the D columns
-  mbar_wait(&bar_q, 0, status, 300);
-  {
-    constexpr int kChunks = D / 16;                            // 16-byte chunks per thread and matrix
-#pragma unroll
-    for (int m = 0; m < (SELF ? 1 : 2); ++m) {
-      const uint8_t* src = smem + (m == 0 ? L::q : L::q0);
-      uint32_t w[kChunks * 4];
-#pragma unroll
-      for (int c = 0; c < kChunks; ++c) {
-        const int chunk = wg * kChunks + c;                   // chunk index along D (8 elements each)
-        const uint4 v4 = *reinterpret_cast<const uint4*>(src + (chunk >> 3) * kRowTile + swz_off(row, chunk & 7));
-        w[4 * c] = v4.x; w[4 * c + 1] = v4.y; w[4 * c + 2] = v4.z; w[4 * c + 3] = v4.w;
-      }
-      const uint32_t dst = lane_base + (m == 0 ? kColQ : kColQ0) + wg * (D / 4);
-      if constexpr (D == 64) tmem_st16(dst, w);
-      else tmem_st32(dst, w);
-    }
-  }
-  tmem_st_wait();
-  __syncthreads();                                             // the landing tiles have been read by everyone
-  // strictly-lower-triangular ones TRI[i][r] = 1 for r < i, a K-major A operand of two [128][64] tiles laid over the
-  // landing area; thread (row, wg) writes row `row` of tile wg (running-sum index r = 64 wg .. 64 wg + 63)
-  {
-    uint8_t* tri = smem + L::q + wg * kRowTile;
-#pragma unroll
-    for (int c = 0; c < 8; ++c) {
-      uint32_t w[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = wg * 64 + c * 8 + 2 * e;
-        w[e] = pack_bf16(r < row ? 1.f : 0.f, (r + 1) < row ? 1.f : 0.f);
-      }
-      *reinterpret_cast<uint4*>(tri + swz_off(row, c)) = make_uint4(w[0], w[1], w[2], w[3]);
-    }
-  }
-  fence_async_smem();
-  tc_fence_before_sync();
-  __syncthreads();
-  tc_fence_after_sync();
-
-  const uint32_t idesc_s = instr_desc_bf16(128, kKeys, false, false);
-  const uint32_t idesc_tri = instr_desc_bf16(128, kKeys, false, true, /*negate_a=*/true);
-  const uint32_t idesc_pv = instr_desc_bf16(128, D, false, true);
-  const float c1 = scale * kLog2e;
-  const float* carry_row = carry + ((int64_t)b * (ntiles + 1) + mi) * seq;
-
-  // L0 = Q0 K0^T and S = Q K^T of the step whose K tiles are landing
-  auto issue_logits = [&](int it) {
-    mbar_wait(&bar_k, it & 1, status, 301);
-    tc_fence_after_sync();
-    if (!SELF) {
-      for (int ks = 0; ks < 4 * DK; ++ks)
-        mma_ts(tmem + kColL, tmem + kColQ0 + ks * 8,
-               smem_desc(sa + L::k0 + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
-    }
-    for (int ks = 0; ks < 4 * DK; ++ks)
-      mma_ts(tmem + kColS, tmem + kColQ + ks * 8,
-             smem_desc(sa + L::k + (ks >> 2) * kKeyTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
-  };
-  if (tid == 0) {
-    issue_logits(0);
-    mma_commit(&bar_mma);
-  }
-
-  const int i = i0 + row;
-  const int cw = wg * 32;                                     // this warpgroup's key columns within a step
-  float run_max = -INFINITY, run_den = 0.f;                   // run_den: this warpgroup's share of the denominator
-  uint32_t mma_phase = 0;
-
-  for (int it = 0; it < steps; ++it) {
-    const int t = steps - 1 - it;
-    const int j0 = t * kKeys;
-    if (tid < kKeys) {
-      const int j = j0 + tid;
-      carry_s[it & 1][tid] = (j < seq) ? carry_row[j] * kLog2e : 0.f;
-    }
-    // ---- A: the batch (P V of the previous step, L0, S) has completed ---------------------------------------
-    mbar_wait(&bar_mma, mma_phase, status, 302);
-    mma_phase ^= 1;
-    tc_fence_after_sync();
-    if (tid == 0) {
-      if (t > 0) load_k(t - 1);                        // K and K0 tiles are free once both products are done
-      if (it > 0) load_v(t);                           // and so is V, read last by the previous step's P V
-    }
-
-    // ---- B: selection relu(L0) under the mask -> bf16, row = query, this warpgroup's 32 keys ----------------
-    {
-      uint32_t r[32];
-      tmem_ld32(lane_base + (SELF ? kColS : kColL) + cw, r);
-      tmem_ld_wait();
-      float s[32];
-      if ((j0 + kKeys > i0) || (j0 < exempt)) {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int j = j0 + cw + e;
-          s[e] = (j < i && j >= exempt) ? fmaxf(__uint_as_float(r[e]), 0.f) : 0.f;
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) s[e] = fmaxf(__uint_as_float(r[e]), 0.f);
-      }
-#pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 w = make_uint4(pack_bf16(s[c * 8 + 0], s[c * 8 + 1]), pack_bf16(s[c * 8 + 2], s[c * 8 + 3]),
-                             pack_bf16(s[c * 8 + 4], s[c * 8 + 5]), pack_bf16(s[c * 8 + 6], s[c * 8 + 7]));
-        *reinterpret_cast<uint4*>(smem + L::selp + swz_off(row, wg * 4 + c)) = w;
-      }
-    }
-    fence_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-
-    // ---- C: S -= TRI x selection (exclusive running sum over the tile's queries) --------------------------
-    if (tid == 0) {
-      tc_fence_after_sync();
-      for (int ks = 0; ks < 8; ++ks)
-        mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
-               smem_desc(sa + L::selp + ks * 2048, kRowTile, 1024), idesc_tri, 1);
-      mma_commit(&bar_mma);
-    }
-    mbar_wait(&bar_mma, mma_phase, status, 303);
-    mma_phase ^= 1;
-    tc_fence_after_sync();
-
-    // ---- D: online softmax of z = (S * scale - carry) * log2(e) -----------------------------------------------
-    float z[32];
-    {
-      uint32_t r[32];
-      tmem_ld32(lane_base + kColS + cw, r);
-      tmem_ld_wait();
-      const float* cs = carry_s[it & 1] + cw;
-      float tile_max = -INFINITY;
-      if (j0 + kKeys - 1 > i0) {                               // a step that crosses the diagonal
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          z[e] = (j0 + cw + e > i) ? -INFINITY : fmaf(__uint_as_float(r[e]), c1, -cs[e]);
-          tile_max = fmaxf(tile_max, z[e]);
-        }
-      } else {
-#pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          z[e] = fmaf(__uint_as_float(r[e]), c1, -cs[e]);
-          tile_max = fmaxf(tile_max, z[e]);
-        }
-      }
-      rmax_s[wg][row] = tile_max;
-    }
-    tc_fence_before_sync();
-    __syncthreads();
-    tc_fence_after_sync();
-    const float new_max = fmaxf(run_max, fmaxf(rmax_s[0][row], rmax_s[1][row]));
-    // a row of the tile's upper half has no key at or below the diagonal in the first step: its maximum is still
-    // -inf there, and the reference point 0 keeps every term an exact zero instead of inf - inf
-    const float ref = (new_max == -INFINITY) ? 0.f : new_max;
-    const float alpha = ex2(run_max - ref);
-    run_max = new_max;
-    float rowsum = 0.f;
-#pragma unroll
-    for (int e = 0; e < 32; ++e) {
-      z[e] = ex2(z[e] - ref);
-      rowsum += z[e];
-    }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      uint4 w = make_uint4(pack_bf16(z[c * 8 + 0], z[c * 8 + 1]), pack_bf16(z[c * 8 + 2], z[c * 8 + 3]),
-                           pack_bf16(z[c * 8 + 4], z[c * 8 + 5]), pack_bf16(z[c * 8 + 6], z[c * 8 + 7]));
-      *reinterpret_cast<uint4*>(smem + L::selp + swz_off(row, wg * 4 + c)) = w;
-    }
-    run_den = run_den * alpha + rowsum;
-    if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {    // the accumulator (complete since A) follows the maximum
-#pragma unroll
-      for (int c0 = 0; c0 < DH; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld32(lane_base + kColO + wg * DH + c0, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int e = 0; e < 32; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-        tmem_st32(lane_base + kColO + wg * DH + c0, r);
-      }
-      tmem_st_wait();
-    }
-    fence_async_smem();
-    tc_fence_before_sync();
-    __syncthreads();
-
-    // ---- E: O += P V, then the logits of the next step, as one batch -----------------------------------------
-    if (tid == 0) {
-      mbar_wait(&bar_v, it & 1, status, 304);
-      tc_fence_after_sync();
-      for (int ks = 0; ks < 4; ++ks)
-        mma_ss(tmem + kColO, smem_desc(sa + L::selp + ks * 32, 16, 1024),
-               smem_desc(sa + L::v + ks * 2048, kKeyTile, 1024), idesc_pv, (it > 0 || ks > 0) ? 1u : 0u);
-      if (it + 1 < steps) issue_logits(it + 1);
-      mma_commit(&bar_mma);
-    }
-  }
-  mbar_wait(&bar_mma, mma_phase, status, 305);                // the last P V
-  tc_fence_after_sync();
-
-  // the two warpgroups hold disjoint shares of each row's denominator
-  rmax_s[wg][row] = run_den;
-  __syncthreads();
-  const float den = rmax_s[0][row] + rmax_s[1][row];
-  {
-    const float inv = 1.f / den;
-    float4* orow = reinterpret_cast<float4*>(out + ((int64_t)n * seq + i) * D + wg * DH);
-#pragma unroll
-    for (int c0 = 0; c0 < DH; c0 += 32) {
-      uint32_t r[32];
-      tmem_ld32(lane_base + kColO + wg * DH + c0, r);
-      tmem_ld_wait();
-      if (i < seq) {
-#pragma unroll
-        for (int d = 0; d < 32; d += 4)
-          orow[(c0 + d) >> 2] = make_float4(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv,
-                                            __uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv);
-      }
-    }
-    if (i < seq && wg == 0) lse2[(int64_t)n * seq + i] = run_max + log2f(den);
-  }
-  tc_fence_before_sync();
-  __syncthreads();
-  if (warp == 0) tmem_dealloc(tmem, kTmemCols);
+template <int N>
+__device__ __forceinline__ void tmem_ld_n(uint32_t taddr, uint32_t (&r)[N]) {
+  if constexpr (N == 16) tmem_ld16(taddr, r);
+  else tmem_ld32(taddr, r);
+}
+template <int N>
+__device__ __forceinline__ void tmem_st_n(uint32_t taddr, const uint32_t (&r)[N]) {
+  if constexpr (N == 8) tmem_st8(taddr, r);
+  else if constexpr (N == 16) tmem_st16(taddr, r);
+  else tmem_st32(taddr, r);
 }
 
 // ---------------------------------------------------------------------------------------------------
-// forward, head_dim 64: 128-key steps, one CTA per SM
+// forward: 128-query tile x 128-key steps, one CTA per SM
 // ---------------------------------------------------------------------------------------------------
-// Same arithmetic as forward_kernel, arranged so that one CTA keeps the tensor pipe and four warpgroups busy without
-// a second resident CTA: a step covers 128 keys (N = 128 MMAs run at the full tensor rate and the per-step barriers
+// One 128-query tile of one head.  Key steps of 128 run from the diagonal back to key 0: the keys nearest the query
+// carry the least history, so the running maximum settles within the first steps and the output accumulator,
+// which stays in TMEM for the whole loop, is rescaled only while the maximum still moves.  One CTA keeps the tensor
+// pipe and four warpgroups busy without a second resident CTA: a step covers 128 keys (N = 128 MMAs run at the full tensor rate and the per-step barriers
 // are paid half as often), a control warp issues every load and MMA, and the steps are software-pipelined: after
-// the logits and the row maximum of step t the arithmetic warps write the selection tile of step t + 1 (L0 is
-// double-buffered in TMEM), and only then do the exponentials of step t, so S and the triangular running sum of
-// step t + 1 run on the tensor pipe under the exponentials instead of being waited for.
+// the logits and the row maximum of step t the arithmetic warps write the selection tile of step t + 1 (its L0 was
+// issued right behind the running sum of step t), and only then do the exponentials of step t, so S and the
+// triangular running sum of step t + 1 run on the tensor pipe under the exponentials instead of being waited for.
+// head_dim 64 keeps two stages of K, K0 and V in shared memory; head_dim 128 has room for one and refills a
+// tile as soon as the MMA that read it has completed.
+template <int D>
 struct WideSmem {
-  static constexpr int q = 0;                          // landing tiles of Q and Q0, then the triangular ones (2 tiles)
-  static constexpr int sel = q + 2 * kRowTile;         // [128 queries][128 keys] bf16 as two key tiles (B of the running sum)
+  static constexpr int DK = D / 64;
+  static constexpr int kStages = (D == 64) ? 2 : 1;
+  static constexpr int kTileBytes = DK * kRowTile;     // one [128 keys][D] operand
+  static constexpr int q = 0;                          // landing tiles of Q (and Q0 at head_dim 64), then the triangular ones
+  static constexpr int sel = q + 2 * kRowTile;         // [128 queries][128 keys] bf16 as two key tiles (B of the running sum);
+                                                       //   head_dim 128: first the landing tiles of Q0
   static constexpr int p = sel + 2 * kRowTile;         // the same shape: P (A of P V)
-  static constexpr int k = p + 2 * kRowTile;           // 2 stages x [128 keys][64]
-  static constexpr int k0 = k + 2 * kRowTile;
-  static constexpr int v = k0 + 2 * kRowTile;
-  static constexpr int total = v + 2 * kRowTile;       // 192 KB
+  static constexpr int k = p + 2 * kRowTile;
+  static constexpr int k0 = k + kStages * kTileBytes;
+  static constexpr int v = k0 + kStages * kTileBytes;
+  static constexpr int total = v + kStages * kTileBytes;   // 192 KB for both head dims
+  static constexpr int q0_landing = (D == 64) ? q + kRowTile : sel;
 };
-constexpr int kWideCompute = 512;                      // four warpgroups: 32 of a step's 128 key columns, 16 of the 64 d each
+constexpr int kWideCompute = 512;                      // four warpgroups: 32 of a step's 128 key columns, D / 4 of the d each
 constexpr int kWideThreads = kWideCompute + 32;        // + the control warp: one lane issues every TMA load and MMA
 constexpr int kWideBarrier = 1;                        // hardware barrier id of the arithmetic warps
 
-template <bool SELF>
+template <int D, bool SELF>
 __global__ void __launch_bounds__(kWideThreads, 1)
     forward_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const float* __restrict__ carry,
                         float* __restrict__ out, float* __restrict__ lse2, int heads, int seq, int ntiles, int exempt,
                         float scale, unsigned int* status) {
-  using L = WideSmem;
-  constexpr int D = 64, DH = 16, NC = 32;
-  constexpr uint32_t kColS = 0, kColL = 128 /* two buffers of 128 */, kColO = 384, kColQ = 448, kColQ0 = 480;
+  using L = WideSmem<D>;
+  constexpr int DK = D / 64, DH = D / 4, NC = 32, ST = L::kStages;
+  // TMEM columns: S and L0 (fp32, 128 each), the output accumulator (D), Q and Q0 as bf16 pairs (D / 2 each)
+  constexpr uint32_t kColS = 0, kColL = 128, kColO = 256, kColQ = kColO + D, kColQ0 = kColQ + D / 2;
 
   const int nrows = gridDim.x / ntiles;                       // batch * heads
   const int mi = ntiles - 1 - (int)(blockIdx.x / nrows);      // heaviest query tiles first
@@ -521,10 +231,10 @@ __global__ void __launch_bounds__(kWideThreads, 1)
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  // Completion barriers (one MMA commit each): bar_l0[j & 1] L0 of step j; bar_tri S and running sum of a step;
-  // bar_pv P V of a step; bar_fin the last P V.  Arrival barriers (one arrival per arithmetic warp and step):
-  // bar_sel selection tile written and the previous step's logits read; bar_p P written and O rescaled.
-  __shared__ uint64_t bar_q, bar_k[2], bar_k0[2], bar_v[2], bar_l0[2], bar_tri, bar_pv, bar_fin, bar_sel, bar_p, bar_setup;
+  // Completion barriers (one MMA commit each): bar_l0 L0 of a step; bar_tri S and running sum of a step; bar_pv
+  // P V of a step; bar_fin the last P V.  Arrival barriers (one arrival per arithmetic warp and step): bar_sel
+  // selection tile written and the previous step's logits read; bar_p P written and O rescaled.
+  __shared__ uint64_t bar_q, bar_k[2], bar_k0[2], bar_v[2], bar_l0, bar_tri, bar_pv, bar_fin, bar_sel, bar_p, bar_setup;
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(16) float carry_s[2][kTile];
   __shared__ float rmax_s[4][kTile];
@@ -536,8 +246,8 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       mbar_init(&bar_k[u], 1);
       mbar_init(&bar_k0[u], 1);
       mbar_init(&bar_v[u], 1);
-      mbar_init(&bar_l0[u], 1);
     }
+    mbar_init(&bar_l0, 1);
     mbar_init(&bar_tri, 1);
     mbar_init(&bar_pv, 1);
     mbar_init(&bar_fin, 1);
@@ -556,37 +266,37 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   if (warp == kWideCompute / 32) {
     // =============================== control warp: TMA loads and MMA issue ===============================
     if (lane == 0) {
-      // step index `it` counts from the diagonal (it = 0) back to key 0; its keys start at 128 (steps - 1 - it)
-      auto load_k = [&](int it) {
-        mbar_expect_tx(&bar_k[it & 1], kRowTile);
-        tma_load_4d(smem + L::k + (it & 1) * kRowTile, &map_k, &bar_k[it & 1], 0, (steps - 1 - it) * kTile, h, b);
+      // Step index `it` counts from the diagonal (it = 0) back to key 0; its keys start at 128 (steps - 1 - it).
+      // A tile of step it lives in stage slot(it); the j-th fill of a stage completes its barrier's phase j.
+      auto slot = [](int it) { return ST == 2 ? (it & 1) : 0; };
+      auto fill = [](int it) { return (uint32_t)((ST == 2 ? (it >> 1) : it) & 1); };
+      auto load_tile = [&](int off, const CUtensorMap* map, uint64_t* bars, int it, int head) {
+        uint64_t* bar = &bars[slot(it)];
+        mbar_expect_tx(bar, L::kTileBytes);
+        for (int s2 = 0; s2 < DK; ++s2)
+          tma_load_4d(smem + off + slot(it) * L::kTileBytes + s2 * kRowTile, map, bar, s2 * 64, (steps - 1 - it) * kTile, head, b);
       };
-      auto load_k0 = [&](int it) {                             // SELF: K0 is K
-        if (SELF) return;
-        mbar_expect_tx(&bar_k0[it & 1], kRowTile);
-        tma_load_4d(smem + L::k0 + (it & 1) * kRowTile, &map_k, &bar_k0[it & 1], 0, (steps - 1 - it) * kTile, 0, b);
-      };
-      auto load_v = [&](int it) {
-        mbar_expect_tx(&bar_v[it & 1], kRowTile);
-        tma_load_4d(smem + L::v + (it & 1) * kRowTile, &map_v, &bar_v[it & 1], 0, (steps - 1 - it) * kTile, h, b);
-      };
+      auto load_k = [&](int it) { load_tile(L::k, &map_k, bar_k, it, h); };
+      auto load_k0 = [&](int it) { if (!SELF) load_tile(L::k0, &map_k, bar_k0, it, 0); };   // SELF: K0 is K
+      auto load_v = [&](int it) { load_tile(L::v, &map_v, bar_v, it, h); };
       const uint32_t idesc_s = instr_desc_bf16(128, 128, false, false);
       const uint32_t idesc_tri = instr_desc_bf16(128, 128, false, true, /*negate_a=*/true);
       const uint32_t idesc_pv = instr_desc_bf16(128, D, false, true);
-      auto issue_l0 = [&](int it) {                            // L0 = Q0 K0^T into the L buffer of the step
-        mbar_wait(SELF ? &bar_k[it & 1] : &bar_k0[it & 1], (it >> 1) & 1, status, 311);
+      auto issue_l0 = [&](int it) {                            // L0 = Q0 K0^T
+        mbar_wait(SELF ? &bar_k[slot(it)] : &bar_k0[slot(it)], fill(it), status, 311);
         tc_fence_after_sync();
-        const uint32_t tile = sa + (SELF ? L::k : L::k0) + (it & 1) * kRowTile;
-        for (int ks = 0; ks < 4; ++ks)
-          mma_ts(tmem + kColL + (it & 1) * 128, tmem + (SELF ? kColQ : kColQ0) + ks * 8, smem_desc(tile + ks * 32, 16, 1024),
-                 idesc_s, ks > 0);
-        mma_commit(&bar_l0[it & 1]);
+        const uint32_t tile = sa + (SELF ? L::k : L::k0) + slot(it) * L::kTileBytes;
+        for (int ks = 0; ks < 4 * DK; ++ks)
+          mma_ts(tmem + kColL, tmem + (SELF ? kColQ : kColQ0) + ks * 8,
+                 smem_desc(tile + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024), idesc_s, ks > 0);
+        mma_commit(&bar_l0);
       };
       auto issue_s_tri = [&](int it) {                         // S = Q K^T, then S -= TRI x selection
-        mbar_wait(&bar_k[it & 1], (it >> 1) & 1, status, 312);
+        mbar_wait(&bar_k[slot(it)], fill(it), status, 312);
         tc_fence_after_sync();
-        for (int ks = 0; ks < 4; ++ks)
-          mma_ts(tmem + kColS, tmem + kColQ + ks * 8, smem_desc(sa + L::k + (it & 1) * kRowTile + ks * 32, 16, 1024),
+        const uint32_t tile = sa + L::k + slot(it) * L::kTileBytes;
+        for (int ks = 0; ks < 4 * DK; ++ks)
+          mma_ts(tmem + kColS, tmem + kColQ + ks * 8, smem_desc(tile + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
                  idesc_s, ks > 0);
         for (int ks = 0; ks < 8; ++ks)
           mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
@@ -594,22 +304,24 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         mma_commit(&bar_tri);
       };
       auto issue_pv = [&](int it, uint64_t* bar) {             // O += P V
-        mbar_wait(&bar_v[it & 1], (it >> 1) & 1, status, 315);
+        mbar_wait(&bar_v[slot(it)], fill(it), status, 315);
         tc_fence_after_sync();
         for (int ks = 0; ks < 8; ++ks)
           mma_ss(tmem + kColO, smem_desc(sa + L::p + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
-                 smem_desc(sa + L::v + (it & 1) * kRowTile + ks * 2048, kRowTile, 1024), idesc_pv,
+                 smem_desc(sa + L::v + slot(it) * L::kTileBytes + ks * 2048, kRowTile, 1024), idesc_pv,
                  (it > 0 || ks > 0) ? 1u : 0u);
         mma_commit(bar);
       };
 
-      mbar_expect_tx(&bar_q, (SELF ? 1 : 2) * kRowTile);
-      tma_load_4d(smem + L::q, &map_q, &bar_q, 0, i0, h, b);
-      if (!SELF) tma_load_4d(smem + L::q + kRowTile, &map_q, &bar_q, 0, i0, 0, b);
+      mbar_expect_tx(&bar_q, (SELF ? 1 : 2) * DK * kRowTile);
+      for (int s2 = 0; s2 < DK; ++s2) {
+        tma_load_4d(smem + L::q + s2 * kRowTile, &map_q, &bar_q, s2 * 64, i0, h, b);
+        if (!SELF) tma_load_4d(smem + L::q0_landing + s2 * kRowTile, &map_q, &bar_q, s2 * 64, i0, 0, b);
+      }
       load_k0(0);
       load_k(0);
       load_v(0);
-      if (steps > 1) {
+      if (ST == 2 && steps > 1) {
         load_k0(1);
         load_k(1);
         load_v(1);
@@ -617,25 +329,28 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       mbar_wait(&bar_setup, 0, status, 317);                   // Q, Q0 in TMEM and the triangular tile in place
       tc_fence_after_sync();
       issue_l0(0);
-      if (steps > 1) issue_l0(1);
       for (int it = 0; it < steps; ++it) {
-        mbar_wait(&bar_sel, it & 1, status, 318);              // selection of step it written; logits of it - 1 read
-        tc_fence_after_sync();
-        if (it + 2 < steps) load_k0(it + 2);                   // L0 of step it has been consumed
+        mbar_wait(&bar_sel, it & 1, status, 318);              // selection of step it written; logits of it - 1 read;
+        tc_fence_after_sync();                                 //   L0 of step it consumed: its K0 tile is free
+        if (it + ST < steps) load_k0(it + ST);
         issue_s_tri(it);
+        const bool l0_now = !(SELF && ST == 1);                // one-stage SELF: K of the next step is not loaded yet
+        if (l0_now && it + 1 < steps) issue_l0(it + 1);
         if (it > 0) {
           mbar_wait(&bar_p, (it - 1) & 1, status, 320);        // P of step it - 1 written, O rescaled
           tc_fence_after_sync();
-          if (it >= 2) {                                       // before this barrier's next commit: P V of it - 2 done,
+          if (ST == 2 && it >= 2) {                            // before this barrier's next commit: P V of it - 2 done,
             mbar_wait(&bar_pv, it & 1, status, 321);           //   so its V tile may be refilled
-            if (it < steps) load_v(it);
+            load_v(it);
           }
           issue_pv(it - 1, &bar_pv);
         }
         mbar_wait(&bar_tri, it & 1, status, 319);              // S of step it done: its K tile is free
-        if (it + 2 < steps) {
-          load_k(it + 2);
-          issue_l0(it + 2);                                    // its L buffer was read by the selection pass of step it
+        if (it + ST < steps) load_k(it + ST);
+        if (!l0_now && it + 1 < steps) issue_l0(it + 1);
+        if (ST == 1 && it > 0) {                               // the single V tile: refilled with V of step it (for the
+          mbar_wait(&bar_pv, (it - 1) & 1, status, 321);       //   P V issued in the next iteration) once P V of step
+          load_v(it);                                          //   it - 1 has completed
         }
       }
       mbar_wait(&bar_p, (steps - 1) & 1, status, 322);
@@ -653,18 +368,22 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       __syncwarp();
       if (lane == 0) mbar_arrive(bar);
     };
-    // Q and Q0 rows from the landing tiles into TMEM as bf16 pairs; warpgroup wg moves 16 of the 64 columns
+    // Q and Q0 rows from the landing tiles into TMEM as bf16 pairs; warpgroup wg moves D / 4 of the D columns
     mbar_wait(&bar_q, 0, status, 310);
+    {
+      constexpr int kChunks = D / 32;                          // 16-byte chunks per thread and matrix
 #pragma unroll
-    for (int m = 0; m < (SELF ? 1 : 2); ++m) {
-      const uint8_t* src = smem + L::q + m * kRowTile;
-      uint32_t w[8];
+      for (int m = 0; m < (SELF ? 1 : 2); ++m) {
+        const uint8_t* src = smem + (m == 0 ? L::q : L::q0_landing);
+        uint32_t w[kChunks * 4];
 #pragma unroll
-      for (int c = 0; c < 2; ++c) {
-        const uint4 v4 = *reinterpret_cast<const uint4*>(src + swz_off(row, wg * 2 + c));
-        w[4 * c] = v4.x; w[4 * c + 1] = v4.y; w[4 * c + 2] = v4.z; w[4 * c + 3] = v4.w;
+        for (int c = 0; c < kChunks; ++c) {
+          const int chunk = wg * kChunks + c;                  // chunk index along D (8 elements each)
+          const uint4 v4 = *reinterpret_cast<const uint4*>(src + (chunk >> 3) * kRowTile + swz_off(row, chunk & 7));
+          w[4 * c] = v4.x; w[4 * c + 1] = v4.y; w[4 * c + 2] = v4.z; w[4 * c + 3] = v4.w;
+        }
+        tmem_st_n<kChunks * 4>(lane_base + (m == 0 ? kColQ : kColQ0) + wg * (kChunks * 4), w);
       }
-      tmem_st8(lane_base + (m == 0 ? kColQ : kColQ0) + wg * 8, w);
     }
     tmem_st_wait();
     named_barrier(kWideBarrier, kWideCompute);                 // the landing tiles have been read by everyone
@@ -700,13 +419,13 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     auto selection = [&](int it, float carry_value) {
       const int j0 = (steps - 1 - it) * kTile;
       if (tid < kTile) carry_s[it & 1][tid] = -carry_value * kLog2e;   // negated: the logits pass adds it in an FMA
-      mbar_wait(&bar_l0[it & 1], (it >> 1) & 1, status, 313);
+      mbar_wait(&bar_l0, it & 1, status, 313);
       tc_fence_after_sync();
       const bool masked = (j0 + kTile > i0) || (j0 < exempt);
 #pragma unroll
       for (int hc = 0; hc < 2; ++hc) {
         uint32_t r[16];
-        tmem_ld16(lane_base + kColL + (it & 1) * 128 + cw + hc * 16, r);
+        tmem_ld16(lane_base + kColL + cw + hc * 16, r);
         tmem_ld_wait();
         float s[16];
         if (masked) {
@@ -799,11 +518,11 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       }
       if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {   // the accumulator follows the maximum while it moves
         uint32_t r[DH];
-        tmem_ld16(lane_base + kColO + wg * DH, r);
+        tmem_ld_n<DH>(lane_base + kColO + wg * DH, r);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < DH; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
-        tmem_st16(lane_base + kColO + wg * DH, r);
+        tmem_st_n<DH>(lane_base + kColO + wg * DH, r);
         tmem_st_wait();
       }
       arrive(&bar_p);
@@ -817,7 +536,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     const float den = (rmax_s[0][row] + rmax_s[1][row]) + (rmax_s[2][row] + rmax_s[3][row]);
     const float inv = 1.f / den;
     uint32_t r[DH];
-    tmem_ld16(lane_base + kColO + wg * DH, r);
+    tmem_ld_n<DH>(lane_base + kColO + wg * DH, r);
     tmem_ld_wait();
     if (i < seq) {
       float4* orow = reinterpret_cast<float4*>(out + ((int64_t)n * seq + i) * D + wg * DH);
@@ -836,14 +555,12 @@ __global__ void __launch_bounds__(kWideThreads, 1)
 template <int D>
 int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float* total, cudaStream_t s) {
   const int ntiles = (p.seq + kTile - 1) / kTile;
-  CUtensorMap map_q, map_k, map_k128, map_v;
+  CUtensorMap map_q, map_k128, map_v128;                 // boxes of 128 rows x 64 columns
   int st = make_map_16bit(&map_q, p.q.ptr, D, p.seq, p.heads, p.batch, p.q.st, p.q.sh, p.q.sb, kTile);
-  if (st != SA_OK) return st;
-  st = make_map_16bit(&map_k, p.k.ptr, D, p.seq, p.heads, p.batch, p.k.st, p.k.sh, p.k.sb, kKeys);
   if (st != SA_OK) return st;
   st = make_map_16bit(&map_k128, p.k.ptr, D, p.seq, p.heads, p.batch, p.k.st, p.k.sh, p.k.sb, kTile);
   if (st != SA_OK) return st;
-  st = make_map_16bit(&map_v, p.v.ptr, D, p.seq, p.heads, p.batch, p.v.st, p.v.sh, p.v.sb, kKeys);
+  st = make_map_16bit(&map_v128, p.v.ptr, D, p.seq, p.heads, p.batch, p.v.st, p.v.sh, p.v.sb, kTile);
   if (st != SA_OK) return st;
   unsigned int* status = nullptr;
   st = status_word(&status);
@@ -867,39 +584,22 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
 
   const unsigned grid = (unsigned)ntiles * p.batch * p.heads;
   const bool self = (p.heads == 1);            // one head per selector: the selection logits are the head's own
-  if constexpr (D == 64) {
-    CUtensorMap map_v128;
-    st = make_map_16bit(&map_v128, p.v.ptr, D, p.seq, p.heads, p.batch, p.v.st, p.v.sh, p.v.sb, kTile);
-    if (st != SA_OK) return st;
-    const int wide_smem = WideSmem::total + 1024;
-    if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(forward_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
-    else SA_CUDA_CHECK(cudaFuncSetAttribute(forward_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
+  {
+    const int wide_smem = WideSmem<D>::total + 1024;
+    if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(forward_wide_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
+    else SA_CUDA_CHECK(cudaFuncSetAttribute(forward_wide_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
     {
       ProfileScope prof(SA_KERNEL_TC_FORWARD, s);
       if (self)
-        forward_wide_kernel<true><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, carry, out, lse2, p.heads,
-                                                                         p.seq, ntiles, p.exempt, p.scale, status);
+        forward_wide_kernel<D, true><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, carry, out, lse2,
+                                                                            p.heads, p.seq, ntiles, p.exempt, p.scale, status);
       else
-        forward_wide_kernel<false><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, carry, out, lse2, p.heads,
-                                                                          p.seq, ntiles, p.exempt, p.scale, status);
+        forward_wide_kernel<D, false><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, carry, out, lse2,
+                                                                             p.heads, p.seq, ntiles, p.exempt, p.scale, status);
     }
     SA_CUDA_CHECK(cudaGetLastError());
     return SA_OK;
   }
-  const int fwd_smem = FwdSmem<D>::total + 1024;
-  if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(forward_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem));
-  else SA_CUDA_CHECK(cudaFuncSetAttribute(forward_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, fwd_smem));
-  {
-    ProfileScope prof(SA_KERNEL_TC_FORWARD, s);
-    if (self)
-      forward_kernel<D, true><<<grid, kFwdThreads, fwd_smem, s>>>(map_q, map_k, map_v, carry, out, lse2, p.heads, p.seq,
-                                                                   ntiles, p.exempt, p.scale, status);
-    else
-      forward_kernel<D, false><<<grid, kFwdThreads, fwd_smem, s>>>(map_q, map_k, map_v, carry, out, lse2, p.heads, p.seq,
-                                                                    ntiles, p.exempt, p.scale, status);
-  }
-  SA_CUDA_CHECK(cudaGetLastError());
-  return SA_OK;
 }
 
 }  // namespace
