@@ -47,6 +47,32 @@ def test_forward_matches_oracle(seq, dim, scale):
         torch.testing.assert_close(got_row[:, valid], want_row[:, valid], atol=1e-3, rtol=1e-3)
 
 
+@pytest.mark.parametrize("seq", [1, 130, 777])
+@pytest.mark.parametrize("dim", [64, 128])
+def test_forward_one_head_per_selector(seq, dim):
+    """heads == 1 (the per-head form) runs the kernels' own-logits instantiation, which at head_dim 128 also has its
+    own load schedule (one K tile in shared memory serves both the selection and the attention logits)."""
+    q, k, v, _ = _inputs(3, 1, seq, dim, seed=seq + dim + 1, scale=0.7)
+    out, aux = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda(), return_aux=True, exempt=2)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    want = oracle.attention(q.float(), k.float(), v.float(), exempt=2)
+    assert _rel(out.cpu(), want) < 2e-2, _rel(out.cpu(), want)
+    torch.testing.assert_close(aux["selected_total"].cpu(), oracle.selected_total(q.float(), k.float(), 2)[:, 0],
+                               atol=1e-3, rtol=1e-3)
+
+
+def test_forward_head_dim_128_strided_views_and_exempt():
+    b, t, h, d = 2, 300, 3, 128
+    g = torch.Generator("cpu").manual_seed(11)
+    packed = (0.5 * torch.randn(b, t, 3, h, d, generator=g)).bfloat16().cuda()   # fused QKV projection layout
+    q, k, v = (packed[:, :, i].transpose(1, 2) for i in range(3))
+    assert not q.is_contiguous()
+    out = kernels.selective_attention_forward(q, k, v, exempt=40)
+    want = oracle.attention(q.float().cpu(), k.float().cpu(), v.float().cpu(), exempt=40)
+    assert _rel(out.cpu(), want) < 2e-2
+
+
 @pytest.mark.parametrize("exempt", [3, 16, 70, 200])
 def test_forward_exempt_prefix(exempt):
     q, k, v, _ = _inputs(1, 2, 333, 64, seed=exempt)
