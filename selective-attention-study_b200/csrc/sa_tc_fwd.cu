@@ -221,6 +221,10 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   constexpr int DK = D / 64, DH = D / 4, NC = 32, ST = L::kStages;
   // TMEM columns: S and L0 (fp32, 128 each), the output accumulator (D), Q and Q0 as bf16 pairs (D / 2 each)
   constexpr uint32_t kColS = 0, kColL = 128, kColO = 256, kColQ = kColO + D, kColQ0 = kColQ + D / 2;
+  // head_dim 64 leaves 128 columns: the triangular matrix and P live there as bf16 pairs (64 columns each), so the
+  // running-sum and P V MMAs fetch only their B operands from shared memory.  head_dim 128 keeps both in shared memory.
+  constexpr bool kTmemAB = (D == 64);
+  constexpr uint32_t kColTri = 384, kColP = 448;
 
   const int nrows = gridDim.x / ntiles;                       // batch * heads
   const int mi = ntiles - 1 - (int)(blockIdx.x / nrows);      // heaviest query tiles first
@@ -298,18 +302,26 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         for (int ks = 0; ks < 4 * DK; ++ks)
           mma_ts(tmem + kColS, tmem + kColQ + ks * 8, smem_desc(tile + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
                  idesc_s, ks > 0);
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
-                 smem_desc(sa + L::sel + ks * 2048, kRowTile, 1024), idesc_tri, 1);
+        for (int ks = 0; ks < 8; ++ks) {
+          if (kTmemAB)
+            mma_ts(tmem + kColS, tmem + kColTri + ks * 8, smem_desc(sa + L::sel + ks * 2048, kRowTile, 1024), idesc_tri, 1);
+          else
+            mma_ss(tmem + kColS, smem_desc(sa + L::q + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
+                   smem_desc(sa + L::sel + ks * 2048, kRowTile, 1024), idesc_tri, 1);
+        }
         mma_commit(&bar_tri);
       };
       auto issue_pv = [&](int it, uint64_t* bar) {             // O += P V
         mbar_wait(&bar_v[slot(it)], fill(it), status, 315);
         tc_fence_after_sync();
-        for (int ks = 0; ks < 8; ++ks)
-          mma_ss(tmem + kColO, smem_desc(sa + L::p + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024),
-                 smem_desc(sa + L::v + slot(it) * L::kTileBytes + ks * 2048, kRowTile, 1024), idesc_pv,
-                 (it > 0 || ks > 0) ? 1u : 0u);
+        for (int ks = 0; ks < 8; ++ks) {
+          const uint64_t vdesc = smem_desc(sa + L::v + slot(it) * L::kTileBytes + ks * 2048, kRowTile, 1024);
+          if (kTmemAB)
+            mma_ts(tmem + kColO, tmem + kColP + ks * 8, vdesc, idesc_pv, (it > 0 || ks > 0) ? 1u : 0u);
+          else
+            mma_ss(tmem + kColO, smem_desc(sa + L::p + (ks >> 2) * kRowTile + (ks & 3) * 32, 16, 1024), vdesc, idesc_pv,
+                   (it > 0 || ks > 0) ? 1u : 0u);
+        }
         mma_commit(bar);
       };
 
@@ -389,17 +401,28 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     named_barrier(kWideBarrier, kWideCompute);                 // the landing tiles have been read by everyone
     // strictly-lower-triangular ones TRI[i][r] = 1 for r < i over the landing area: a K-major A operand of two
     // [128][64] tiles; thread (row, wg) writes running-sum indices r = 32 wg .. 32 wg + 31 of its row
+    if (kTmemAB) {                                             // 32 running-sum indices = 16 packed columns per thread
+      uint32_t w[16];
 #pragma unroll
-    for (int c = 0; c < 4; ++c) {
-      const int chunk = wg * 4 + c;
-      uint32_t w[4];
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int r = chunk * 8 + 2 * e;
+      for (int e = 0; e < 16; ++e) {
+        const int r = wg * 32 + 2 * e;
         w[e] = pack_bf16(r < row ? 1.f : 0.f, (r + 1) < row ? 1.f : 0.f);
       }
-      *reinterpret_cast<uint4*>(smem + L::q + (chunk >> 3) * kRowTile + swz_off(row, chunk & 7)) =
-          make_uint4(w[0], w[1], w[2], w[3]);
+      tmem_st16(lane_base + kColTri + wg * 16, w);
+      tmem_st_wait();
+    } else {
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        const int chunk = wg * 4 + c;
+        uint32_t w[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int r = chunk * 8 + 2 * e;
+          w[e] = pack_bf16(r < row ? 1.f : 0.f, (r + 1) < row ? 1.f : 0.f);
+        }
+        *reinterpret_cast<uint4*>(smem + L::q + (chunk >> 3) * kRowTile + swz_off(row, chunk & 7)) =
+            make_uint4(w[0], w[1], w[2], w[3]);
+      }
     }
     arrive(&bar_setup);
 
@@ -510,11 +533,18 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         mbar_wait(&bar_pv, (it - 1) & 1, status, 323);         // P V of the previous step: P tile and O are free
         tc_fence_after_sync();
       }
+      if (kTmemAB) {                                           // P as bf16 pairs: keys 32 wg .. at column 16 wg of P
+        uint32_t w[16];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        uint4 w = make_uint4(pack_bf16(z[c * 4].x, z[c * 4].y), pack_bf16(z[c * 4 + 1].x, z[c * 4 + 1].y),
-                             pack_bf16(z[c * 4 + 2].x, z[c * 4 + 2].y), pack_bf16(z[c * 4 + 3].x, z[c * 4 + 3].y));
-        *reinterpret_cast<uint4*>(smem + L::p + (wg >> 1) * kRowTile + swz_off(row, (wg & 1) * 4 + c)) = w;
+        for (int e = 0; e < 16; ++e) w[e] = pack_bf16(z[e].x, z[e].y);
+        tmem_st16(lane_base + kColP + wg * 16, w);
+      } else {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          uint4 w = make_uint4(pack_bf16(z[c * 4].x, z[c * 4].y), pack_bf16(z[c * 4 + 1].x, z[c * 4 + 1].y),
+                               pack_bf16(z[c * 4 + 2].x, z[c * 4 + 2].y), pack_bf16(z[c * 4 + 3].x, z[c * 4 + 3].y));
+          *reinterpret_cast<uint4*>(smem + L::p + (wg >> 1) * kRowTile + swz_off(row, (wg & 1) * 4 + c)) = w;
+        }
       }
       if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {   // the accumulator follows the maximum while it moves
         uint32_t r[DH];
@@ -523,8 +553,8 @@ __global__ void __launch_bounds__(kWideThreads, 1)
 #pragma unroll
         for (int e = 0; e < DH; ++e) r[e] = __float_as_uint(__uint_as_float(r[e]) * alpha);
         tmem_st_n<DH>(lane_base + kColO + wg * DH, r);
-        tmem_st_wait();
       }
+      tmem_st_wait();                                          // P (head_dim 64) and the rescaled accumulator are in TMEM
       arrive(&bar_p);
     }
     mbar_wait(&bar_fin, 0, status, 316);                       // the last P V
