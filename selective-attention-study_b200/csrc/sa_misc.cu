@@ -92,7 +92,7 @@ __global__ void __launch_bounds__(256) fold_cast_kernel(const float* __restrict_
 // ---- decode -----------------------------------------------------------------------------------------
 constexpr int kDecThreads = 128;
 constexpr int kDecSplitMin = 512;             // keys per CTA: a multiple of 512, at least 512
-constexpr int kDecCtasPerSm = 3;              // attend CTAs resident per SM (64 KB of stages each)
+constexpr int kDecCtasPerSm = 4;              // attend CTAs resident per SM (48 KB of stages each)
 
 // Keys per CTA for `t` cached keys and `rows` = batch * heads query rows: the grid is about one full wave of
 // resident CTAs, so no SM is left with a straggler and the combine pass stays short.
@@ -149,7 +149,7 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
                : "memory");
 }
 
-constexpr int kDecStages = 4;                   // stages of 8 KB of K + 8 KB of V
+constexpr int kDecStages = 3;                   // stages of 8 KB of K + 8 KB of V
 constexpr int kDecStageBytes = 8192;            // per tensor
 constexpr size_t kDecSmemBytes = (size_t)kDecStages * 2 * kDecStageBytes + 128;
 
@@ -197,7 +197,7 @@ __device__ __forceinline__ void decode_combine_row(const float* prow, float* yro
 }
 
 // grid = batch * heads * splits CTAs (a row's splits are neighbours).  One thread streams the CTA's keys of K and V through a ring of shared-memory
-// stages with bulk copies, kDecStages - 1 stages (48 KB) ahead of the arithmetic, so the bytes in flight do not
+// stages with bulk copies, kDecStages - 1 stages (32 KB) ahead of the arithmetic, so the bytes in flight do not
 // depend on how the arithmetic is scheduled.  A group of D / 8 lanes owns every (128 / lanes)-th key of a stage
 // and keeps its own running maximum, denominator and weighted sum (one pass, rescaled when its maximum grows);
 // the groups are merged at the end.
