@@ -85,31 +85,86 @@ def measured_peaks() -> tuple[float, str]:
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons while the timed region runs.  Read-only NVML queries from a thread
+    (a sample every few milliseconds, so even a short timed region of one rank among eight is covered); the
+    nvidia-smi polling route is the fall-back when NVML cannot be loaded."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
               "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    REASON_BITS = (("hw_slowdown", 0x8), ("sw_thermal_slowdown", 0x20), ("hw_thermal_slowdown", 0x40), ("sw_power_cap", 0x4))
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.thread = index, [], None, None
+        self.stop = threading.Event()
+        self.nvml = None
+        self.handle = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            try:
+                props = torch.cuda.get_device_properties(index)
+                bus = f"{props.pci_domain_id:08x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+                self.handle = pynvml.nvmlDeviceGetHandleByPciBusId(bus)
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.nvml = pynvml
+        except Exception:
+            self.nvml = None
+
+    def _sample_nvml(self):
+        n = self.nvml
+        sm = n.nvmlDeviceGetClockInfo(self.handle, n.NVML_CLOCK_SM)
+        mx = n.nvmlDeviceGetMaxClockInfo(self.handle, n.NVML_CLOCK_SM)
+        try:
+            bits = n.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+        except Exception:
+            bits = n.nvmlDeviceGetCurrentClocksThrottleReasons(self.handle)
+        flags = {name: ("Active" if bits & bit else "Not Active") for name, bit in self.REASON_BITS}
+        self.rows.append([str(sm), str(mx), flags["hw_slowdown"], flags["hw_thermal_slowdown"],
+                          flags["sw_thermal_slowdown"], flags["sw_power_cap"]])
+
+    def _poll_nvml(self):
+        while not self.stop.is_set():
+            try:
+                self._sample_nvml()
+            except Exception:
+                return
+            self.stop.wait(0.005)
+
+    def _read_smi(self):
+        for line in self.proc.stdout:
+            self.rows.append([x.strip() for x in line.split(",")])
 
     def __enter__(self):
+        if self.nvml is not None:
+            try:
+                self._sample_nvml()                            # one sample at the start of the region, always
+            except Exception:
+                self.nvml = None
+        if self.nvml is not None:
+            self.thread = threading.Thread(target=self._poll_nvml, daemon=True)
+            self.thread.start()
+            return self
         try:
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}",
                                           "--format=csv,noheader,nounits", "-lms", "100"], stdout=subprocess.PIPE,
                                          stderr=subprocess.DEVNULL, text=True)
-            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread = threading.Thread(target=self._read_smi, daemon=True)
             self.thread.start()
         except OSError:
             self.proc = None
         return self
 
-    def _read(self):
-        for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
-
     def __exit__(self, *exc):
-        if self.proc is not None:
+        if self.nvml is not None:
+            try:
+                self._sample_nvml()                            # and one at its end (the work is still draining)
+            except Exception:
+                pass
+            self.stop.set()
+            if self.thread is not None:
+                self.thread.join(timeout=2)
+        elif self.proc is not None:
             self.proc.terminate()
             self.thread.join(timeout=2)
 
@@ -460,6 +515,7 @@ def run_reference(args, w):
     per-head work is equal, so the full-sequence time is the sample's time x heads / 2."""
     import selective_oracle as oracle
 
+    torch.set_num_threads(os.cpu_count() or 1)       # torchrun sets OMP_NUM_THREADS=1; this arm runs on rank 0 alone
     heads_sample = min(2, w["heads"])
     seq = w["seq"]
     g = torch.Generator("cpu").manual_seed(0)
