@@ -9,7 +9,8 @@
  *
  * Conventions
  *   - every pointer is a DEVICE pointer unless its name ends in _host; the library never allocates
- *     device memory and never frees any: all outputs and scratch come from the caller;
+ *     device memory and never frees any: all outputs and scratch come from the caller (its only
+ *     allocation is one page of pinned host memory per device for the timeout flag, see sa_device_status);
  *   - q, k, v are (batch, heads, seq, head_dim) with arbitrary batch/head/token strides (in elements)
  *     and a contiguous innermost axis; head 0 of every sequence supplies the selection (the per-head
  *     variant reshapes every head into its own one-head sequence, as the reference does);
@@ -41,8 +42,8 @@ enum sa_dtype { SA_F32 = 0, SA_BF16 = 1, SA_F16 = 2 };
 
 /* SA_ENGINE_SIMT   : fp32 FFMA arithmetic on CUDA cores, exact ("ieee") products; any supported dtype,
  *                    head_dim 16/32/64/128, any seq >= 1; carry checkpoints every 32 queries.
- * SA_ENGINE_TCGEN05: bf16/fp16 operands on the tcgen05 tensor cores with fp32 TMEM accumulators, fed by
- *                    TMA; head_dim 64 or 128; carry checkpoints every 128 queries.                    */
+ * SA_ENGINE_TCGEN05: bf16 operands (dtype SA_BF16 only) on the tcgen05 tensor cores with fp32 TMEM
+ *                    accumulators, fed by TMA; head_dim 64 or 128; carry checkpoints every 128 queries. */
 enum sa_engine { SA_ENGINE_SIMT = 0, SA_ENGINE_TCGEN05 = 1 };
 
 enum sa_damp { SA_DAMP_NONE = 0, SA_DAMP_LINEAR = 1, SA_DAMP_SQRT = 2 };
@@ -62,6 +63,20 @@ typedef struct sa_problem {
   int64_t k_stride[3];
   int64_t v_stride[3];
 } sa_problem;
+
+/* A selector kept outside q / k: the rows whose logits make the selection when the heads of one sequence
+ * are split over several calls (or GPUs).  Each call then holds some heads of the sequence in q / k / v and a
+ * replica of the selection head's rows here; none of its own heads is treated as the selector.  The
+ * reference has no such split (its selector is always head 0 of the tensors it is given,
+ * src/selective_attention/kernels.py:123-124,160-161,216-217); this is how its operator shards by head. */
+typedef struct sa_selector {
+  int32_t struct_bytes;  /* sizeof(sa_selector), checked                                               */
+  int32_t reserved;      /* 0                                                                          */
+  const void* q0;        /* (batch, seq, head_dim), element type p->dtype, contiguous innermost axis   */
+  const void* k0;
+  int64_t q0_stride[2];  /* batch and token strides of q0 in elements                                  */
+  int64_t k0_stride[2];
+} sa_selector;
 
 /* Library / build identification. */
 int sa_abi_version(void);
@@ -97,6 +112,23 @@ int sa_carry_checkpoints(int engine, int seq);
 int sa_forward(const sa_problem* p, const void* q, const void* k, const void* v,
                float* out, float* lse2, float* carry, float* total, void* stream);
 
+/* Forward with the selector given separately (sel == NULL: identical to sa_forward).  `total` and `carry`
+ * are those of the selector, so calls that share a selector produce identical copies of them. */
+int sa_forward_selector(const sa_problem* p, const void* q, const void* k, const void* v,
+                        const sa_selector* sel,
+                        float* out, float* lse2, float* carry, float* total, void* stream);
+
+/* The selection pass alone on the CUDA-core engine (p->engine must be SA_ENGINE_SIMT; v strides are
+ * ignored): carry checkpoints every 32 queries, the layout of the reference's CARRY buffer, and the per-key
+ * totals.  Replaces _selective_carry (src/selective_attention/kernels.py:111-138).  Used to hand 32-row
+ * checkpoints to a consumer of the reference's aux["carry"] (scripts/investigate/history_probe.py:49-60) and
+ * to the CUDA-core backward after a tensor-core forward.
+ *   carry  (batch, ceil(seq / 32), seq) fp32; rows are written for keys at or before the block, the rest is
+ *          left untouched (zero-fill it for the reference's layout)
+ *   total  (batch, seq) fp32 */
+int sa_selection_carry(const sa_problem* p, const void* q, const void* k, const sa_selector* sel,
+                       float* carry, float* total, void* stream);
+
 /* Forward for callers that must not allocate.  It has no counterpart in the reference (whose forward
  * allocates its CARRY scratch with torch on every call, src/selective_attention/kernels.py:573-580).
  *
@@ -115,7 +147,8 @@ int sa_forward(const sa_problem* p, const void* q, const void* k, const void* v,
  *   - the first call on each device looks up the array's device address (cudaGetSymbolAddress, with
  *     that device current) and caches it; make that first call during set-up, before any stream
  *     capture begins;
- *   - it calls no cudaMalloc / cudaFree and no allocating library routine;
+ *   - it calls no cudaMalloc / cudaFree and no allocating library routine (it does not create the
+ *     timeout flag of sa_device_status either; it uses the flag if an earlier call made it);
  *   - all calls on a device share the one array and it keeps the previous call's contents.  Nothing in
  *     it has to start at zero (every checkpoint that is read is written first by the same call), but
  *     two calls whose kernels overlap on the GPU (different streams, or different host threads) race
@@ -141,6 +174,20 @@ int sa_backward(const sa_problem* p, const void* q, const void* k, const void* v
                 const void* d_out, int d_out_dtype,
                 void* dq, void* dk, void* dv,
                 void* workspace, size_t workspace_bytes, void* stream);
+
+/* Backward with the selector given separately (sel == NULL: identical to sa_backward).  With a selector,
+ * dq / dk hold only the heads' own gradients (nothing is folded into head 0) and the gradient that reaches
+ * the selector through the history term comes back UNFOLDED and in fp32:
+ *   dq0, dk0   (batch, seq, head_dim) fp32 contiguous, 16-byte aligned; zero-filled by the call, then
+ *              accumulated.  They are this call's partial sums: the caller adds the dq0 / dk0 of all calls
+ *              that share the selector (an all-reduce across GPUs) and adds the result to the gradient
+ *              of the selection head's q / k rows.  Replaces the fold of kernels.py:662-665 for a split. */
+int sa_backward_selector(const sa_problem* p, const void* q, const void* k, const void* v,
+                         const sa_selector* sel,
+                         const float* out, const float* lse2, const float* carry,
+                         const void* d_out, int d_out_dtype,
+                         void* dq, void* dk, void* dv, float* dq0, float* dk0,
+                         void* workspace, size_t workspace_bytes, void* stream);
 
 /* Bytes of scratch sa_decode_step needs: per-split partial sums, the step's new selection values and the
  * tickets with which the last CTA of a row / key range is found.  Contents undefined on entry and exit; two
@@ -181,10 +228,26 @@ enum sa_kernel {
 int sa_profile_enable(int kernel_id);
 int sa_profile_collect(float* ms_host, int capacity);
 
-/* Reads (synchronously) the status word the bounded device-side waits of the tensor-core engine and of the
- * decode step report into; 0 means no wait ever ran out on the current device.  clear != 0 resets it.
+/* Kernels of this library launched by this process so far (all devices, all threads).  Benchmarks report the
+ * difference across their timed region.  No counterpart in the reference. */
+unsigned long long sa_launch_count(void);
+
+/* Bounded device-side waits.  Every wait inside the tensor-core engine and the decode step gives up after a
+ * fixed number of clock ticks (~0.2 s), records (site << 8) | 1 in a per-device word, and its kernel returns;
+ * only the launch sequence that gave up is cut short.  The word is also mirrored into mapped host memory (one
+ * pinned page per device, created by the first entry-point call on the device), so from then on every
+ * sa_forward* / sa_backward* / sa_decode_step call on that device returns SA_ERR_DEVICE_TIMEOUT without
+ * launching anything until the word is cleared.
+ *   sa_device_status  reads the word (0 = no wait ever ran out on the current device); clear != 0 resets it.
+ *                     It copies with cudaMemcpy on the legacy default stream: synchronise streams created
+ *                     with cudaStreamNonBlocking before calling it.
  * No counterpart in the reference (Triton kernels have no such waits). */
 int sa_device_status(unsigned int* value_host, int clear);
+
+/* Makes one bounded wait run out on purpose: a single CTA waits on an mbarrier nobody arrives on, with a
+ * limit of limit_kcycles * 1024 clock ticks (1 .. 100000), reports site 900 and returns.  The kernel
+ * terminates by itself; nothing faults.  For testing the path above.  No counterpart in the reference. */
+int sa_selftest_wait_timeout(unsigned int limit_kcycles, void* stream);
 
 /* Known-answer test of the tcgen05 / TMA operand encodings the tensor-core engine uses.
  *   scratch  32 KiB of device memory, 1024-byte aligned

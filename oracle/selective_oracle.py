@@ -17,7 +17,9 @@ What each function follows (paths inside the reference project):
 ``attention_grads``        ``src/selective_attention/kernels.py:204-268, 621-666`` (the backward's algebra,
                            written densely: dV, dz, dK, dQ, the suffix sum U, the gated head-0 gradient)
 ``damped_attention``       ``src/selective_attention/kernels.py:179-182`` (evaluation-only damping of F)
-``tail_rows``              ``tests/test_selective_kernels.py:310-330``   (last rows of a long sequence)
+``window_rows``            ``tests/test_selective_kernels.py:310-330``   (a window of query rows of a long
+``tail_rows``              sequence: the selection of earlier queries summed in chunks; the tail is the
+                           reference's own form, the window generalises its start)
 ``decode_step``            ``src/selective_attention/mixers.py:115-130`` (one cached decode step)
 ``sequence_fwd_bwd``       the same algebra as ``attention`` / ``attention_grads`` for one sequence at a
                            length where (H, T, T) does not fit: F is built once, heads go in chunks
@@ -54,10 +56,10 @@ def selection_matrix(q0: torch.Tensor, k0: torch.Tensor, exempt: int = 1) -> tor
     exempt = _check_exempt(exempt)
     seq, dim = q0.shape[-2], q0.shape[-1]
     l0 = (q0 @ k0.transpose(-2, -1)) / math.sqrt(dim)
-    rows = torch.arange(seq)[:, None]
-    cols = torch.arange(seq)[None, :]
+    rows = torch.arange(seq, device=q0.device)[:, None]
+    cols = torch.arange(seq, device=q0.device)[None, :]
     allowed = (cols < rows) & (cols >= exempt)
-    return torch.where(allowed & (l0 > 0), l0, torch.zeros((), dtype=l0.dtype))
+    return torch.where(allowed & (l0 > 0), l0, torch.zeros((), dtype=l0.dtype, device=q0.device))
 
 
 def history_logits(q: torch.Tensor, k: torch.Tensor, exempt: int = 1, dtype=torch.float32):
@@ -151,35 +153,44 @@ def damped_attention(q, k, v, damp: str, train_len: int, exempt: int = 1, dtype=
     return z.softmax(dim=-1) @ v
 
 
-def tail_rows(q, k, v, tail: int, exempt: int = 1, chunk: int = 1024, dtype=torch.float32):
-    """Outputs of the last ``tail`` queries and the per-key totals, without a (T, T) tensor."""
+def window_rows(q, k, v, start: int, stop: int, exempt: int = 1, chunk: int = 1024, dtype=torch.float32):
+    """Outputs of the queries [start, stop) and the selection every key has received from the queries
+    before ``stop``, without a (T, T) tensor: the selection of the earlier queries is summed in chunks.
+    Runs where its inputs live (dense torch ops either way)."""
     b, h, seq, dim = q.shape
     s = 1.0 / math.sqrt(dim)
-    dev = q.device                      # runs where its inputs live (dense torch ops either way)
-    keys = torch.arange(seq, device=dev)
-    q0, k0 = q[:, 0].to(dtype), k[:, 0].to(dtype)
+    dev = q.device
+    keys = torch.arange(stop, device=dev)
+    q0, k0 = q[:, 0].to(dtype), k[:, 0, :stop].to(dtype)
 
     def sel(rows):
         l0 = (q0[:, rows] @ k0.transpose(-2, -1)) * s
         ok = (keys[None, :] < rows[:, None]) & (keys >= exempt)[None, :]
         return torch.relu(l0) * ok
 
-    start = seq - tail
-    earlier = torch.zeros(b, seq, dtype=dtype, device=dev)
+    earlier = torch.zeros(b, stop, dtype=dtype, device=dev)
     for a in range(0, start, chunk):
         earlier += sel(torch.arange(a, min(a + chunk, start), device=dev)).sum(dim=1)
-    rows = torch.arange(start, seq, device=dev)
+    rows = torch.arange(start, stop, device=dev)
     st = sel(rows)
     history = earlier[:, None, :] + torch.cumsum(st, dim=1) - st
-    z = (q[:, :, rows].to(dtype) @ k.to(dtype).transpose(-2, -1)) * s - history[:, None]
+    z = (q[:, :, rows].to(dtype) @ k[:, :, :stop].to(dtype).transpose(-2, -1)) * s - history[:, None]
     z = z.masked_fill(keys[None, None, None, :] > rows[None, None, :, None], float("-inf"))
-    return rows, z.softmax(dim=-1) @ v.to(dtype), earlier + st.sum(dim=1)
+    return rows, z.softmax(dim=-1) @ v[:, :, :stop].to(dtype), earlier + st.sum(dim=1)
+
+
+def tail_rows(q, k, v, tail: int, exempt: int = 1, chunk: int = 1024, dtype=torch.float32):
+    """Outputs of the last ``tail`` queries and the per-key totals, without a (T, T) tensor."""
+    seq = q.shape[2]
+    return window_rows(q, k, v, seq - tail, seq, exempt, chunk, dtype)
 
 
 def sequence_fwd_bwd(q, k, v, d_out, exempt: int = 1, head_chunk: int = 2, dtype=torch.float32):
     """(out, dq, dk, dv, total) for ONE sequence (H, T, D) with F (T, T) built once and the heads
-    processed ``head_chunk`` at a time, so peak memory is (head_chunk + 3) * T * T values."""
+    processed ``head_chunk`` at a time, so peak memory is (head_chunk + 3) * T * T values.  Runs where its
+    inputs live."""
     h, seq, dim = q.shape
+    dev = q.device
     s = 1.0 / math.sqrt(dim)
     q, k, v, d_out = (t.to(dtype) for t in (q, k, v, d_out))
     sel = selection_matrix(q[0], k[0], exempt)
@@ -187,10 +198,10 @@ def sequence_fwd_bwd(q, k, v, d_out, exempt: int = 1, head_chunk: int = 2, dtype
     total = sel.sum(dim=0)
     history = torch.cumsum(sel, dim=0) - sel
     del sel
-    upper = torch.ones(seq, seq, dtype=torch.bool).triu(1)
+    upper = torch.ones(seq, seq, dtype=torch.bool, device=dev).triu(1)
     out = torch.empty_like(q)
     dq, dk, dv = torch.empty_like(q), torch.empty_like(q), torch.empty_like(q)
-    dz_all = torch.zeros(seq, seq, dtype=dtype)
+    dz_all = torch.zeros(seq, seq, dtype=dtype, device=dev)
     for a in range(0, h, head_chunk):
         hs = slice(a, min(a + head_chunk, h))
         z = (q[hs] @ k[hs].transpose(-2, -1)) * s - history
@@ -206,7 +217,9 @@ def sequence_fwd_bwd(q, k, v, d_out, exempt: int = 1, head_chunk: int = 2, dtype
         dz_all += dz.sum(dim=0)
         del dz
     later = torch.flip(torch.cumsum(torch.flip(dz_all, [0]), dim=0), [0]) - dz_all
-    g = torch.where(gate, -later, torch.zeros((), dtype=dtype))
+    del dz_all
+    g = torch.where(gate, -later, torch.zeros((), dtype=dtype, device=dev))
+    del later
     dk[0] += s * (g.t() @ q[0])
     dq[0] += s * (g @ k[0])
     return out, dq, dk, dv, total

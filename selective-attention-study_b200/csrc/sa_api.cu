@@ -3,6 +3,7 @@
 // are in include/selective_attention_b200.h.
 #include <math.h>
 
+#include <atomic>
 #include <mutex>
 
 #include "sa_common.cuh"
@@ -12,6 +13,9 @@ namespace sa {
 
 static thread_local int g_last_cuda_error = 0;
 void set_last_cuda_error(int code) { g_last_cuda_error = code; }
+
+static std::atomic<unsigned long long> g_launches{0};
+void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
 
 // Event pairs recorded around the enabled kernel; created on demand, reused after sa_profile_collect.
 namespace {
@@ -44,7 +48,7 @@ bool dim_ok(int d) { return d == 16 || d == 32 || d == 64 || d == 128; }
 bool dtype_ok(int t) { return t == SA_F32 || t == SA_BF16 || t == SA_F16; }
 size_t dtype_bytes(int t) { return t == SA_F32 ? 4 : 2; }
 
-int to_problem(const sa_problem* in, const void* q, const void* k, const void* v, Problem* p) {
+int to_problem(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel, Problem* p) {
   if (in == nullptr || in->struct_bytes != (int32_t)sizeof(sa_problem)) return SA_ERR_BAD_ARGUMENT;
   if (!dtype_ok(in->dtype)) return SA_ERR_BAD_ARGUMENT;
   if (in->engine != SA_ENGINE_SIMT && in->engine != SA_ENGINE_TCGEN05) return SA_ERR_BAD_ARGUMENT;
@@ -52,7 +56,11 @@ int to_problem(const sa_problem* in, const void* q, const void* k, const void* v
   if (!dim_ok(in->head_dim)) return SA_ERR_UNSUPPORTED;
   if (in->damp < SA_DAMP_NONE || in->damp > SA_DAMP_SQRT) return SA_ERR_BAD_ARGUMENT;
   if (in->damp != SA_DAMP_NONE && in->train_len < 1) return SA_ERR_BAD_ARGUMENT;
-  if ((int64_t)in->batch * in->heads > 65535) return SA_ERR_UNSUPPORTED;   // grid.y
+  // the CUDA-core kernels put (batch, head) rows on grid.y; the tensor-core kernels use 1-D grids
+  if (in->engine == SA_ENGINE_SIMT && (int64_t)in->batch * in->heads > 65535) return SA_ERR_UNSUPPORTED;
+  if ((int64_t)in->batch * in->heads * ((in->seq + 127) / 128) > 0x7fffffffLL) return SA_ERR_UNSUPPORTED;
+  if (sel != nullptr && (sel->struct_bytes != (int32_t)sizeof(sa_selector) || !sel->q0 || !sel->k0))
+    return SA_ERR_BAD_ARGUMENT;
   p->batch = in->batch;
   p->heads = in->heads;
   p->seq = in->seq;
@@ -65,6 +73,14 @@ int to_problem(const sa_problem* in, const void* q, const void* k, const void* v
   p->q = Strided{q, in->q_stride[0], in->q_stride[1], in->q_stride[2]};
   p->k = Strided{k, in->k_stride[0], in->k_stride[1], in->k_stride[2]};
   p->v = Strided{v, in->v_stride[0], in->v_stride[1], in->v_stride[2]};
+  p->external_selector = (sel != nullptr);
+  if (sel != nullptr) {
+    p->q0 = Strided{sel->q0, sel->q0_stride[0], 0, sel->q0_stride[1]};
+    p->k0 = Strided{sel->k0, sel->k0_stride[0], 0, sel->k0_stride[1]};
+  } else {
+    p->q0 = Strided{q, in->q_stride[0], 0, in->q_stride[2]};          // head 0 of q / k
+    p->k0 = Strided{k, in->k_stride[0], 0, in->k_stride[2]};
+  }
   return SA_OK;
 }
 
@@ -96,7 +112,7 @@ using namespace sa;
 
 extern "C" {
 
-int sa_abi_version(void) { return 1; }
+int sa_abi_version(void) { return 2; }
 
 const char* sa_status_string(int status) {
   switch (status) {
@@ -144,17 +160,33 @@ int sa_carry_checkpoints(int engine, int seq) {
   return 0;
 }
 
-int sa_forward(const sa_problem* in, const void* q, const void* k, const void* v, float* out, float* lse2,
-               float* carry, float* total, void* stream) {
+int sa_forward_selector(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
+                        float* out, float* lse2, float* carry, float* total, void* stream) {
   Problem p;
-  int st = to_problem(in, q, k, v, &p);
+  int st = to_problem(in, q, k, v, sel, &p);
   if (st != SA_OK) return st;
   if (!q || !k || !v || !out || !lse2 || !carry || !total) return SA_ERR_BAD_ARGUMENT;
+  if (tc::timeout_pending()) return SA_ERR_DEVICE_TIMEOUT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (in->engine == SA_ENGINE_SIMT) return simt_forward(p, out, lse2, carry, total, s);
   st = tc_supported(p);
   if (st != SA_OK) return st;
   return tc_forward(p, out, lse2, carry, total, s);
+}
+
+int sa_selection_carry(const sa_problem* in, const void* q, const void* k, const sa_selector* sel, float* carry,
+                       float* total, void* stream) {
+  Problem p;
+  int st = to_problem(in, q, k, q, sel, &p);
+  if (st != SA_OK) return st;
+  if (!q || !k || !carry || !total) return SA_ERR_BAD_ARGUMENT;
+  if (in->engine != SA_ENGINE_SIMT) return SA_ERR_UNSUPPORTED;
+  return simt_carry(p, carry, total, static_cast<cudaStream_t>(stream));
+}
+
+int sa_forward(const sa_problem* in, const void* q, const void* k, const void* v, float* out, float* lse2,
+               float* carry, float* total, void* stream) {
+  return sa_forward_selector(in, q, k, v, nullptr, out, lse2, carry, total, stream);
 }
 
 // ---- forward with library-owned scratch (no allocation anywhere on the call path) ----------------------
@@ -188,9 +220,11 @@ size_t sa_static_scratch_floats(void) { return (size_t)SA_STATIC_SCRATCH_FLOATS;
 int sa_forward_static_scratch(const sa_problem* in, const void* q, const void* k, const void* v, float* out,
                               float* lse2, float* total, void* stream) {
   Problem p;
-  int st = to_problem(in, q, k, v, &p);
+  int st = to_problem(in, q, k, v, nullptr, &p);
   if (st != SA_OK) return st;
   if (!q || !k || !v || !out || !lse2 || !total) return SA_ERR_BAD_ARGUMENT;
+  if (tc::timeout_pending()) return SA_ERR_DEVICE_TIMEOUT;
+  tc::NoHostAllocScope no_alloc;   // the bounded waits then use the timeout flag only if an earlier call made it
   const size_t need = (size_t)p.batch * (size_t)sa_carry_checkpoints(in->engine, p.seq) * (size_t)p.seq;
   if (need > (size_t)SA_STATIC_SCRATCH_FLOATS) return SA_ERR_TOO_LARGE;
   if (in->engine == SA_ENGINE_TCGEN05) {
@@ -208,21 +242,26 @@ int sa_forward_static_scratch(const sa_problem* in, const void* q, const void* k
 
 size_t sa_backward_workspace_bytes(const sa_problem* in) {
   Problem p;
-  if (to_problem(in, nullptr, nullptr, nullptr, &p) != SA_OK) return 0;
+  if (to_problem(in, nullptr, nullptr, nullptr, nullptr, &p) != SA_OK) return 0;
   return carve(in).total;
 }
 
-int sa_backward(const sa_problem* in, const void* q, const void* k, const void* v, const float* out,
-                const float* lse2, const float* carry, const void* d_out, int d_out_dtype, void* dq, void* dk,
-                void* dv, void* workspace, size_t workspace_bytes, void* stream) {
+int sa_backward_selector(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
+                         const float* out, const float* lse2, const float* carry, const void* d_out, int d_out_dtype,
+                         void* dq, void* dk, void* dv, float* dq0_out, float* dk0_out, void* workspace,
+                         size_t workspace_bytes, void* stream) {
   Problem p;
-  int st = to_problem(in, q, k, v, &p);
+  int st = to_problem(in, q, k, v, sel, &p);
   if (st != SA_OK) return st;
   if (!q || !k || !v || !out || !lse2 || !carry || !d_out || !dq || !dk || !dv || !workspace) return SA_ERR_BAD_ARGUMENT;
+  if (sel != nullptr && (!dq0_out || !dk0_out)) return SA_ERR_BAD_ARGUMENT;
   if (!dtype_ok(d_out_dtype) || in->damp != SA_DAMP_NONE) return SA_ERR_BAD_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(workspace) & 255) != 0) return SA_ERR_ALIGNMENT;
+  if (sel != nullptr && ((reinterpret_cast<uintptr_t>(dq0_out) | reinterpret_cast<uintptr_t>(dk0_out)) & 15) != 0)
+    return SA_ERR_ALIGNMENT;
   const BackwardWorkspace w = carve(in);
   if (workspace_bytes < w.total) return SA_ERR_WORKSPACE;
+  if (tc::timeout_pending()) return SA_ERR_DEVICE_TIMEOUT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   char* base = static_cast<char*>(workspace);
   float* dq_acc = reinterpret_cast<float*>(base + w.dq_acc);
@@ -235,9 +274,18 @@ int sa_backward(const sa_problem* in, const void* q, const void* k, const void* 
   const size_t elems = (size_t)rows * p.head_dim;
   const size_t elems0 = (size_t)p.batch * per_head;
 
-  // dq_acc, dq0 and dk0 are accumulated with atomics and start at zero (the dq0/dk0 pair is contiguous).
+  // dq_acc, dq0 and dk0 are accumulated with atomics and start at zero (the workspace's dq0/dk0 pair is contiguous).
   SA_CUDA_CHECK(cudaMemsetAsync(dq_acc, 0, elems * 4, s));
-  SA_CUDA_CHECK(cudaMemsetAsync(dq0, 0, (w.dk0 - w.dq0) + elems0 * 4, s));
+  if (sel != nullptr) {            // the selector's gradients go to the caller, unfolded
+    dq0 = dq0_out;
+    dk0 = dk0_out;
+    SA_CUDA_CHECK(cudaMemsetAsync(dq0, 0, elems0 * 4, s));
+    SA_CUDA_CHECK(cudaMemsetAsync(dk0, 0, elems0 * 4, s));
+  } else {
+    SA_CUDA_CHECK(cudaMemsetAsync(dq0, 0, (w.dk0 - w.dq0) + elems0 * 4, s));
+  }
+  const float* fold_q = sel ? nullptr : dq0;
+  const float* fold_k = sel ? nullptr : dk0;
 
   if (in->engine == SA_ENGINE_SIMT) {
     const float* d_out_f32 = static_cast<const float*>(d_out);
@@ -250,9 +298,9 @@ int sa_backward(const sa_problem* in, const void* q, const void* k, const void* 
     if (st != SA_OK) return st;
     st = simt_backward(p, lse2, carry, dbar, d_out_f32, dq_acc, dk_acc, dq0, dk0, dv, s);
     if (st != SA_OK) return st;
-    st = launch_fold_cast(dk_acc, dk0, dk, p.dtype, p.batch, p.heads, per_head, s);
+    st = launch_fold_cast(dk_acc, fold_k, dk, p.dtype, p.batch, p.heads, per_head, s);
     if (st != SA_OK) return st;
-    return launch_fold_cast(dq_acc, dq0, dq, p.dtype, p.batch, p.heads, per_head, s);
+    return launch_fold_cast(dq_acc, fold_q, dq, p.dtype, p.batch, p.heads, per_head, s);
   }
   st = tc_backward_supported(p);
   if (st != SA_OK) return st;
@@ -261,10 +309,19 @@ int sa_backward(const sa_problem* in, const void* q, const void* k, const void* 
   if (st != SA_OK) return st;
   st = tc_backward(p, lse2, carry, dbar, d_out_lowp, dq_acc, dk_acc, dq0, dk0, dv, s);
   if (st != SA_OK) return st;
-  st = launch_fold_cast(dk_acc, dk0, dk, p.dtype, p.batch, p.heads, per_head, s);
+  st = launch_fold_cast(dk_acc, fold_k, dk, p.dtype, p.batch, p.heads, per_head, s);
   if (st != SA_OK) return st;
-  return launch_fold_cast(dq_acc, dq0, dq, p.dtype, p.batch, p.heads, per_head, s);
+  return launch_fold_cast(dq_acc, fold_q, dq, p.dtype, p.batch, p.heads, per_head, s);
 }
+
+int sa_backward(const sa_problem* in, const void* q, const void* k, const void* v, const float* out,
+                const float* lse2, const float* carry, const void* d_out, int d_out_dtype, void* dq, void* dk,
+                void* dv, void* workspace, size_t workspace_bytes, void* stream) {
+  return sa_backward_selector(in, q, k, v, nullptr, out, lse2, carry, d_out, d_out_dtype, dq, dk, dv, nullptr, nullptr,
+                              workspace, workspace_bytes, stream);
+}
+
+unsigned long long sa_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
 int sa_profile_enable(int kernel_id) {
   if (kernel_id < 0 || kernel_id > SA_KERNEL_DECODE) return SA_ERR_BAD_ARGUMENT;
@@ -287,6 +344,11 @@ int sa_profile_collect(float* ms_host, int capacity) {
 int sa_device_status(unsigned int* value_host, int clear) {
   if (!value_host) return SA_ERR_BAD_ARGUMENT;
   return tc::read_status(value_host, clear != 0);
+}
+
+int sa_selftest_wait_timeout(unsigned int limit_kcycles, void* stream) {
+  if (limit_kcycles < 1u || limit_kcycles > 100000u) return SA_ERR_BAD_ARGUMENT;   // at most ~0.05 s
+  return tc::selftest_wait_timeout(limit_kcycles, static_cast<cudaStream_t>(stream));
 }
 
 int sa_selftest_tcgen05(void* scratch, float* result, void* stream) {
@@ -312,6 +374,7 @@ int sa_decode_step(int dtype, int batch, int heads, int groups, int length, int 
   for (const void* ptr : {q1, k1, v1, (const void*)k_cache, (const void*)v_cache})            // 16-byte loads, bulk copies
     if ((reinterpret_cast<uintptr_t>(ptr) & 15) != 0) return SA_ERR_ALIGNMENT;
   if (workspace_bytes < sa_decode_workspace_bytes(batch, heads, groups, length, head_dim)) return SA_ERR_WORKSPACE;
+  if (tc::timeout_pending()) return SA_ERR_DEVICE_TIMEOUT;
   return decode_step(dtype, batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, k_cache, v_cache,
                      selected, y, static_cast<float*>(workspace), static_cast<cudaStream_t>(stream));
 }

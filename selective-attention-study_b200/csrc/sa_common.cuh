@@ -36,10 +36,16 @@ struct Problem {
   int dtype;
   float scale;          // 1 / sqrt(head_dim)
   Strided q, k, v;
+  // The selector: the (batch, seq, head_dim) rows whose logits make the selection.  By default head 0 of q / k
+  // (pointer and batch / token strides of q / k, head stride unused); with an external selector the caller's
+  // own tensors, and then no head of q / k is the selector: nothing is folded into head 0 by the backward.
+  Strided q0, k0;
+  bool external_selector;
 };
 
 // ---- engine entry points (host) -------------------------------------------------------------------
 int simt_forward(const Problem& p, float* out, float* lse2, float* carry, float* total, cudaStream_t s);
+int simt_carry(const Problem& p, float* carry, float* total, cudaStream_t s);
 int simt_backward(const Problem& p, const float* lse2, const float* carry, const float* dbar,
                   const float* d_out, float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv,
                   cudaStream_t s);
@@ -66,6 +72,7 @@ int decode_step(int dtype, int batch, int heads, int groups, int length, int cap
                 float* ws, cudaStream_t s);
 
 void set_last_cuda_error(int code);
+void count_launch();   // every kernel launch of the library calls this once (sa_launch_count)
 
 // ---- per-kernel timing hook (sa_profile_*) ------------------------------------------------------------
 // Kernel ids of include/selective_attention_b200.h (SA_KERNEL_*).  When a kernel id is enabled, the

@@ -47,10 +47,10 @@ int dbar_by_dim(const float* out, const void* d_out, int64_t rows, int head_dim,
   TLOW* l = static_cast<TLOW*>(low);
   ProfileScope prof(SA_KERNEL_DBAR, s);
   switch (head_dim) {
-    case 16: dbar_kernel<TDO, TLOW, 16, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
-    case 32: dbar_kernel<TDO, TLOW, 32, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
-    case 64: dbar_kernel<TDO, TLOW, 64, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
-    case 128: dbar_kernel<TDO, TLOW, 128, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
+    case 16: count_launch(), dbar_kernel<TDO, TLOW, 16, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
+    case 32: count_launch(), dbar_kernel<TDO, TLOW, 32, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
+    case 64: count_launch(), dbar_kernel<TDO, TLOW, 64, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
+    case 128: count_launch(), dbar_kernel<TDO, TLOW, 128, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
     default: return SA_ERR_UNSUPPORTED;
   }
   SA_CUDA_CHECK(cudaGetLastError());
@@ -205,7 +205,7 @@ template <typename T, int D>
 __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
     const T* __restrict__ q1, const T* __restrict__ kc, const T* __restrict__ vc, float* selected,
     float* __restrict__ partial, float* __restrict__ sel_new, int heads, int groups, int t, int capacity,
-    int exempt, float scale, int split_keys, unsigned int* status, float* __restrict__ y, unsigned int* __restrict__ row_tickets, unsigned int* __restrict__ split_tickets, int splits) {
+    int exempt, float scale, int split_keys, tc::WaitCtx status, float* __restrict__ y, unsigned int* __restrict__ row_tickets, unsigned int* __restrict__ split_tickets, int splits) {
   constexpr int kLanes = D / 8;                                   // lanes per key
   constexpr int kGroups = kDecThreads / kLanes;                   // keys the CTA covers per step
   constexpr int kRowBytes = D * (int)sizeof(T);
@@ -393,6 +393,7 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
   const int n_tickets = rows + batch * groups * splits;
   const int append_threads = rows * D > n_tickets ? rows * D : n_tickets;
   ProfileScope prof(SA_KERNEL_DECODE, s);   // the whole step: append, then attend with its merge and update
+  count_launch();
   append_kernel<T><<<(append_threads + 255) / 256, 256, 0, s>>>(
       static_cast<const T*>(k1), static_cast<const T*>(v1), static_cast<T*>(kc), static_cast<T*>(vc), rows, capacity,
       length, D, row_tickets, n_tickets);
@@ -402,12 +403,13 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
   const T* q = static_cast<const T*>(q1);
   const T* kk = static_cast<const T*>(kc);
   const T* vv = static_cast<const T*>(vc);
-  unsigned int* status = nullptr;
-  if (int st = tc::status_word(&status)) return st;
+  tc::WaitCtx status;
+  if (int st = tc::wait_ctx(&status)) return st;
 #define SA_DECODE_LAUNCH(DIM)                                                                                      \
   do {                                                                                                             \
     SA_CUDA_CHECK(cudaFuncSetAttribute(decode_attend_kernel<T, DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
                                        (int)kDecSmemBytes));                                                       \
+    count_launch();                                                                                                \
     decode_attend_kernel<T, DIM><<<grid, kDecThreads, kDecSmemBytes, s>>>(                                         \
         q, kk, vv, selected, partial, sel_new, heads, groups, t, capacity, exempt, scale, split_keys, status,      \
         y, row_tickets, split_tickets, splits);                                                                   \
@@ -442,13 +444,16 @@ int launch_fold_cast(const float* acc, const float* acc0, void* dst, int dtype, 
   const unsigned blocks = (unsigned)((total4 + 255) / 256);
   switch (dtype) {
     case SA_F32:
+      count_launch();
       fold_cast_kernel<float><<<blocks, 256, 0, s>>>(acc, acc0, static_cast<float*>(dst), heads, seq_times_dim, total4);
       break;
     case SA_BF16:
+      count_launch();
       fold_cast_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(acc, acc0, static_cast<__nv_bfloat16*>(dst), heads,
                                                              seq_times_dim, total4);
       break;
     case SA_F16:
+      count_launch();
       fold_cast_kernel<__half><<<blocks, 256, 0, s>>>(acc, acc0, static_cast<__half*>(dst), heads, seq_times_dim,
                                                       total4);
       break;

@@ -49,9 +49,9 @@ __global__ void __launch_bounds__(kThreads) carry_kernel(Problem p, float* __res
 
   const int b = blockIdx.y;
   const int j0 = blockIdx.x * kKF;
-  const T* q0 = row_ptr<T>(p.q, b, 0);
-  const T* k0 = row_ptr<T>(p.k, b, 0);
-  load_tile<T, D>(k0s, k0, p.k.st, j0, kKF, p.seq);
+  const T* q0 = row_ptr<T>(p.q0, b, 0);
+  const T* k0 = row_ptr<T>(p.k0, b, 0);
+  load_tile<T, D>(k0s, k0, p.k0.st, j0, kKF, p.seq);
 
   const int jl = threadIdx.x & 63;         // key within the block
   const int rg = threadIdx.x >> 6;         // row group: rows rg * 8 .. rg * 8 + 7
@@ -61,7 +61,7 @@ __global__ void __launch_bounds__(kThreads) carry_kernel(Problem p, float* __res
 
   for (int rb = j0 / kQ; rb < nblocks; ++rb) {
     __syncthreads();                       // previous iteration done with q0s / part
-    load_tile<T, D>(q0s, q0, p.q.st, rb * kQ, kQ, p.seq);
+    load_tile<T, D>(q0s, q0, p.q0.st, rb * kQ, kQ, p.seq);
     __syncthreads();
     float colsum = 0.f;
     const float* kr = k0s + jl * (D + 1);
@@ -111,11 +111,11 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(Problem p, const floa
   const T* qh = row_ptr<T>(p.q, b, h);
   const T* kh = row_ptr<T>(p.k, b, h);
   const T* vh = row_ptr<T>(p.v, b, h);
-  const T* q0 = row_ptr<T>(p.q, b, 0);
-  const T* k0 = row_ptr<T>(p.k, b, 0);
+  const T* q0 = row_ptr<T>(p.q0, b, 0);
+  const T* k0 = row_ptr<T>(p.k0, b, 0);
 
   load_tile<T, D>(qs, qh, p.q.st, m0, kQ, p.seq);
-  load_tile<T, D>(q0s, q0, p.q.st, m0, kQ, p.seq);
+  load_tile<T, D>(q0s, q0, p.q0.st, m0, kQ, p.seq);
 
   const int r = threadIdx.x >> 3;          // query row in the tile
   const int cg = threadIdx.x & 7;          // column group
@@ -134,7 +134,7 @@ __global__ void __launch_bounds__(kThreads) forward_kernel(Problem p, const floa
   for (int n0 = 0; n0 < last_key; n0 += kKF) {
     __syncthreads();
     load_tile<T, D>(ks, kh, p.k.st, n0, kKF, p.seq);
-    load_tile<T, D>(k0s, k0, p.k.st, n0, kKF, p.seq);
+    load_tile<T, D>(k0s, k0, p.k0.st, n0, kKF, p.seq);
     load_tile<T, D>(vs, vh, p.v.st, n0, kKF, p.seq);
     __syncthreads();
     float aff[8], sel[8];
@@ -244,13 +244,13 @@ __global__ void __launch_bounds__(kThreads) backward_kernel(
   const T* qh = row_ptr<T>(p.q, b, h);
   const T* kh = row_ptr<T>(p.k, b, h);
   const T* vh = row_ptr<T>(p.v, b, h);
-  const T* q0 = row_ptr<T>(p.q, b, 0);
-  const T* k0 = row_ptr<T>(p.k, b, 0);
+  const T* q0 = row_ptr<T>(p.q0, b, 0);
+  const T* k0 = row_ptr<T>(p.k0, b, 0);
   const TDO* doh = d_out + (int64_t)n * p.seq * D;
 
   load_tile<T, D>(ks, kh, p.k.st, j0, kKB, p.seq);
   load_tile<T, D>(vs, vh, p.v.st, j0, kKB, p.seq);
-  load_tile<T, D>(k0s, k0, p.k.st, j0, kKB, p.seq);
+  load_tile<T, D>(k0s, k0, p.k0.st, j0, kKB, p.seq);
 
   const int r = threadIdx.x >> 3;   // row index (query row in phase 1, key row / query row in phase 2)
   const int cg = threadIdx.x & 7;
@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(kThreads) backward_kernel(
     const int m0 = rb * kQ;
     __syncthreads();
     load_tile<T, D>(qs, qh, p.q.st, m0, kQ, p.seq);
-    load_tile<T, D>(q0s, q0, p.q.st, m0, kQ, p.seq);
+    load_tile<T, D>(q0s, q0, p.q0.st, m0, kQ, p.seq);
     for (int idx = threadIdx.x; idx < kQ * D; idx += kThreads) {
       int rr = idx / D, d = idx - rr * D;
       int t = m0 + rr;
@@ -411,10 +411,25 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   SA_CUDA_CHECK(cudaFuncSetAttribute(forward_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)forward_smem<D>()));
   dim3 gc((p.seq + kKF - 1) / kKF, p.batch);
+  count_launch();
   carry_kernel<T, D><<<gc, kThreads, carry_smem<D>(), s>>>(p, carry, total, nb);
   SA_CUDA_CHECK(cudaGetLastError());
   dim3 gf(nb, p.batch * p.heads);
+  count_launch();
   forward_kernel<T, D><<<gf, kThreads, forward_smem<D>(), s>>>(p, carry, out, lse2, nb);
+  SA_CUDA_CHECK(cudaGetLastError());
+  return SA_OK;
+}
+
+// The selection pass alone: carry checkpoints every 32 queries and the per-key totals.
+template <typename T, int D>
+int carry_impl(const Problem& p, float* carry, float* total, cudaStream_t s) {
+  const int nb = (p.seq + kQ - 1) / kQ;
+  SA_CUDA_CHECK(cudaFuncSetAttribute(carry_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     (int)carry_smem<D>()));
+  dim3 gc((p.seq + kKF - 1) / kKF, p.batch);
+  count_launch();
+  carry_kernel<T, D><<<gc, kThreads, carry_smem<D>(), s>>>(p, carry, total, nb);
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;
 }
@@ -426,6 +441,7 @@ int backward_impl(const Problem& p, const float* lse2, const float* carry, const
   SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<T, TDO, D>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                      (int)backward_smem<D>()));
   dim3 g((p.seq + kKB - 1) / kKB, p.batch * p.heads);
+  count_launch();
   backward_kernel<T, TDO, D><<<g, kThreads, backward_smem<D>(), s>>>(
       p, lse2, carry, dbar, static_cast<const TDO*>(d_out), dq_acc, dk_acc, dq0, dk0, static_cast<T*>(dv), nb);
   SA_CUDA_CHECK(cudaGetLastError());
@@ -439,6 +455,17 @@ int forward_by_dim(const Problem& p, float* out, float* lse2, float* carry, floa
     case 32: return forward_impl<T, 32>(p, out, lse2, carry, total, s);
     case 64: return forward_impl<T, 64>(p, out, lse2, carry, total, s);
     case 128: return forward_impl<T, 128>(p, out, lse2, carry, total, s);
+  }
+  return SA_ERR_UNSUPPORTED;
+}
+
+template <typename T>
+int carry_by_dim(const Problem& p, float* carry, float* total, cudaStream_t s) {
+  switch (p.head_dim) {
+    case 16: return carry_impl<T, 16>(p, carry, total, s);
+    case 32: return carry_impl<T, 32>(p, carry, total, s);
+    case 64: return carry_impl<T, 64>(p, carry, total, s);
+    case 128: return carry_impl<T, 128>(p, carry, total, s);
   }
   return SA_ERR_UNSUPPORTED;
 }

@@ -75,27 +75,6 @@ __device__ __forceinline__ void put8(uint8_t* base, int row, int c0, const float
   *reinterpret_cast<uint4*>(base + (c0 >> 6) * kRowTile + swz_off(row, (c0 & 63) >> 3)) = w;
 }
 
-#ifdef SA_BWD_TIMING
-__device__ unsigned long long g_bwd_timing[16];
-struct Marks {
-  unsigned long long acc[16];
-  long long last;
-  bool on;
-};
-#define SA_MARK(m, k)                                     \
-  if ((m).on) {                                           \
-    long long _now = clock64();                           \
-    (m).acc[k] += (unsigned long long)(_now - (m).last);  \
-    (m).last = _now;                                      \
-  }
-#define SA_MARKS_ARG , Marks& marks
-#define SA_MARKS_PASS , marks
-#else
-#define SA_MARK(m, k)
-#define SA_MARKS_ARG
-#define SA_MARKS_PASS
-#endif
-
 struct HalfCtx {
   uint8_t* smem;
   uint32_t lane_base;
@@ -118,7 +97,7 @@ struct HalfCtx {
 // locally (two independent chains of 8) and picks up the totals of the chunks to its right, and the
 // carried state, through shared memory.
 template <bool DIAG, bool SELF>
-__device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state, float& dz_state SA_MARKS_ARG) {
+__device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state, float& dz_state) {
   using L = BwdSmem;
   const int colw = c.wg * kChunk;
   const int col0 = c.hf * 64 + colw;
@@ -145,10 +124,8 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   c.sel_tot[c.wg][c.row] = ls[0];
   tc_fence_before_sync();
   if (c.drain_reduce && threadIdx.x == 0) bulk_wait_read();
-  SA_MARK(marks, 2)
   named_barrier(kComputeBarrier, kComputeThreads);      // also: every thread has finished reading L0^T
   tc_fence_after_sync();
-  SA_MARK(marks, 3)
   float later = 0.f, all = 0.f;
 #pragma unroll
   for (int w = 0; w < kGroups; ++w) {
@@ -221,10 +198,8 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   fence_async_smem();                                    // dz tile half -> visible to the MMAs
   tmem_st_wait();                                        // P^T in TMEM
   tc_fence_before_sync();
-  SA_MARK(marks, 4)
   named_barrier(kComputeBarrier, kComputeThreads);      // every thread is done with S^T, dP^T and L0^T
   if (threadIdx.x == 0) mbar_arrive(c.bar_early);
-  SA_MARK(marks, 5)
   later = 0.f;
   all = 0.f;
 #pragma unroll
@@ -254,7 +229,6 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
     put8(c.smem + L::g, c.row, col0, lx);
     put8(c.smem + L::g, c.row, col0 + 8, lx + 8);
   }
-  SA_MARK(marks, 6)
 }
 
 template <bool SELF>
@@ -262,9 +236,10 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
     const __grid_constant__ CUtensorMap map_dq, const __grid_constant__ CUtensorMap map_dq0,
+    const __grid_constant__ CUtensorMap map_q0, const __grid_constant__ CUtensorMap map_k0,
     const float* __restrict__ lse2, const float* __restrict__ carry, const float* __restrict__ dbar,
     float* __restrict__ dk_acc, float* __restrict__ dk0, __nv_bfloat16* __restrict__ dv, int heads, int seq,
-    int ntiles, int exempt, float scale, unsigned int* status) {
+    int ntiles, int exempt, float scale, WaitCtx status) {
   using L = BwdSmem;
   constexpr int D = 64;
   const int nrows = gridDim.x / ntiles;                  // batch * heads
@@ -316,7 +291,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         uint8_t* st = smem + L::stage + (it & 1) * 3 * kRowTile;
         mbar_expect_tx(&bar_ld[it & 1], (SELF ? 2 : 3) * kRowTile);
         tma_load_4d(st, &map_q, &bar_ld[it & 1], 0, mi * kTile, h, b);
-        if (!SELF) tma_load_4d(st + kRowTile, &map_q, &bar_ld[it & 1], 0, mi * kTile, 0, b);
+        if (!SELF) tma_load_4d(st + kRowTile, &map_q0, &bar_ld[it & 1], 0, mi * kTile, 0, b);
         tma_load_4d(st + 2 * kRowTile, &map_do, &bar_ld[it & 1], 0, mi * kTile, n, 0);
       };
       // Operand descriptors are built once; an MMA's descriptor is a base plus a byte offset / 16, so the
@@ -372,7 +347,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       mbar_expect_tx(&bar_kv, (SELF ? 2 : 3) * kRowTile);
       tma_load_4d(smem + L::k, &map_k, &bar_kv, 0, nj * kTile, h, b);
       tma_load_4d(smem + L::v, &map_v, &bar_kv, 0, nj * kTile, h, b);
-      if (!SELF) tma_load_4d(smem + L::k0, &map_k, &bar_kv, 0, nj * kTile, 0, b);
+      if (!SELF) tma_load_4d(smem + L::k0, &map_k0, &bar_kv, 0, nj * kTile, 0, b);
       load_stage(0);
       if (n_iter > 1) load_stage(1);
       mbar_wait(&bar_kv, 0, status, 400);
@@ -472,18 +447,11 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       return (j < seq) ? load_ahead(carry + ((int64_t)b * (ntiles + 1) + mi + 1) * seq + j) : 0.f;
     };
     float next_lse = fetch_lse(ntiles - 1), next_dbar = fetch_dbar(ntiles - 1), next_carry = fetch_carry(ntiles - 1);
-#ifdef SA_BWD_TIMING
-    Marks marks;
-    for (int k2 = 0; k2 < 16; ++k2) marks.acc[k2] = 0;
-    marks.on = (tid == 0);
-    marks.last = clock64();
-#endif
 
     for (int it = 0; it < n_iter; ++it) {
       const int mi = ntiles - 1 - it;
       const int i0 = mi * kTile;
       const bool diag = (mi == nj);
-      SA_MARK(marks, 12)
       if (tid < kTile) {
         lse_s[tid] = -next_lse;                                // negated: both enter packed adds directly
         dbar_s[tid] = -next_dbar;
@@ -495,22 +463,19 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         next_carry = fetch_carry(mi - 1);
       }
       float sel_state = 0.f;         // selection of the tile's queries already visited, this key (raw logit units)
-      SA_MARK(marks, 0)
 
 #pragma unroll 1
       for (int hf = 1; hf >= 0; --hf) {
         mbar_wait(&bar_a, a_phase, status, 410);
         a_phase ^= 1;
         tc_fence_after_sync();
-        SA_MARK(marks, 1)
         ctx.hf = hf;
         ctx.drain_reduce = (hf == 1) && (it > 0);
-        if (diag) process_half<true, SELF>(ctx, sel_state, dz_state SA_MARKS_PASS);
-        else process_half<false, SELF>(ctx, sel_state, dz_state SA_MARKS_PASS);
+        if (diag) process_half<true, SELF>(ctx, sel_state, dz_state);
+        else process_half<false, SELF>(ctx, sel_state, dz_state);
         fence_async_smem();                                    // g tile half -> visible to the MMAs
         __syncwarp();
         if (lane == 0) mbar_arrive(&bar_half[hf]);
-        SA_MARK(marks, 7)
       }
 
       // ---- dQ, then dQ0, of this query tile: TMEM -> scaled fp32 staging in shared memory (the dz / g tiles,
@@ -532,30 +497,22 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       };
       mbar_wait(&bar_dq, it & 1, status, 412);
       tc_fence_after_sync();
-      SA_MARK(marks, 8)
       stage_tile(kColDQ, smem + L::dz);
       if (tid == 0) {
         tma_reduce_add_4d(&map_dq, smem + L::dz, 0, i0, n, 0);
         tma_reduce_add_4d(&map_dq, smem + L::dz + kRowTile, 32, i0, n, 0);
         bulk_commit();
       }
-      SA_MARK(marks, 10)
       if (SELF) continue;                                      // dQ already carries the selection path
       mbar_wait(&bar_b, it & 1, status, 411);
       tc_fence_after_sync();
-      SA_MARK(marks, 11)
       stage_tile(kColDQ0, smem + L::g);
       if (tid == 0) {
         tma_reduce_add_4d(&map_dq0, smem + L::g, 0, i0, b, 0);
         tma_reduce_add_4d(&map_dq0, smem + L::g + kRowTile, 32, i0, b, 0);
         bulk_commit();
       }
-      SA_MARK(marks, 9)
     }
-#ifdef SA_BWD_TIMING
-    if (tid == 0)
-      for (int k2 = 0; k2 < 16; ++k2) atomicAdd(&g_bwd_timing[k2], marks.acc[k2]);
-#endif
 
     // ---- epilogue: dV, dK (this head) and this head's share of dK0 ------------------------------------------
     {
@@ -599,17 +556,6 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 
 }  // namespace
 
-#ifdef SA_BWD_TIMING
-extern "C" int sa_debug_bwd_timing(unsigned long long* host16, int clear) {
-  SA_CUDA_CHECK(cudaMemcpyFromSymbol(host16, g_bwd_timing, 16 * sizeof(unsigned long long)));
-  if (clear) {
-    unsigned long long z[16] = {0};
-    SA_CUDA_CHECK(cudaMemcpyToSymbol(g_bwd_timing, z, sizeof(z)));
-  }
-  return 0;
-}
-#endif
-
 int backward(const Problem& p, const float* lse2, const float* carry, const float* dbar, const void* d_out_bf16,
              float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv, cudaStream_t s) {
   if (p.head_dim != 64) return SA_ERR_UNSUPPORTED;
@@ -629,24 +575,30 @@ int backward(const Problem& p, const float* lse2, const float* carry, const floa
   if (st != SA_OK) return st;
   st = make_map_f32_rows(&map_dq0, dq0, p.seq, p.batch);
   if (st != SA_OK) return st;
-  unsigned int* status = nullptr;
-  st = status_word(&status);
+  CUtensorMap map_q0, map_k0;                            // the selector's rows: (d, token, 1, batch)
+  st = make_map_16bit(&map_q0, p.q0.ptr, 64, p.seq, 1, p.batch, p.q0.st, 0, p.q0.sb, kTile);
+  if (st != SA_OK) return st;
+  st = make_map_16bit(&map_k0, p.k0.ptr, 64, p.seq, 1, p.batch, p.k0.st, 0, p.k0.sb, kTile);
+  if (st != SA_OK) return st;
+  WaitCtx status;
+  st = wait_ctx(&status);
   if (st != SA_OK) return st;
   const int smem = BwdSmem::total + 1024;
   // One head per selector (the per-head form): the selection logits are the head's own, and the kernel merges the
   // two gradient paths before the MMAs.
-  const bool self = (p.heads == 1);
+  const bool self = (p.heads == 1) && !p.external_selector;
   if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   else SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   {
     ProfileScope prof(SA_KERNEL_TC_BACKWARD, s);
+    count_launch();
     if (self)
       backward_kernel<true><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
-          map_q, map_k, map_v, map_do, map_dq, map_dq0, lse2, carry, dbar, dk_acc, dk0,
+          map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
           static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status);
     else
       backward_kernel<false><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
-          map_q, map_k, map_v, map_do, map_dq, map_dq0, lse2, carry, dbar, dk_acc, dk0,
+          map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
           static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status);
   }
   SA_CUDA_CHECK(cudaGetLastError());

@@ -49,7 +49,7 @@ template <int D>
 __global__ void __launch_bounds__(128) colsum_kernel(const __grid_constant__ CUtensorMap map_q,
                                                      const __grid_constant__ CUtensorMap map_k, float* __restrict__ carry,
                                                      int seq, int ntiles, int exempt, float scale,
-                                                     unsigned int* status) {
+                                                     WaitCtx status) {
   constexpr int DK = D / 64;
   const int nj = blockIdx.x, b = blockIdx.z;
   const int mi0 = nj + blockIdx.y * kColsumChunk;
@@ -214,9 +214,10 @@ constexpr int kWideBarrier = 1;                        // hardware barrier id of
 template <int D, bool SELF>
 __global__ void __launch_bounds__(kWideThreads, 1)
     forward_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v, const float* __restrict__ carry,
+                        const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_q0,
+                        const __grid_constant__ CUtensorMap map_k0, const float* __restrict__ carry,
                         float* __restrict__ out, float* __restrict__ lse2, int heads, int seq, int ntiles, int exempt,
-                        float scale, unsigned int* status) {
+                        float scale, WaitCtx status) {
   using L = WideSmem<D>;
   constexpr int DK = D / 64, DH = D / 4, NC = 32, ST = L::kStages;
   // TMEM columns: S and L0 (fp32, 128 each), the output accumulator (D), Q and Q0 as bf16 pairs (D / 2 each)
@@ -281,7 +282,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
           tma_load_4d(smem + off + slot(it) * L::kTileBytes + s2 * kRowTile, map, bar, s2 * 64, (steps - 1 - it) * kTile, head, b);
       };
       auto load_k = [&](int it) { load_tile(L::k, &map_k, bar_k, it, h); };
-      auto load_k0 = [&](int it) { if (!SELF) load_tile(L::k0, &map_k, bar_k0, it, 0); };   // SELF: K0 is K
+      auto load_k0 = [&](int it) { if (!SELF) load_tile(L::k0, &map_k0, bar_k0, it, 0); };   // SELF: K0 is K
       auto load_v = [&](int it) { load_tile(L::v, &map_v, bar_v, it, h); };
       const uint32_t idesc_s = instr_desc_bf16(128, 128, false, false);
       const uint32_t idesc_tri = instr_desc_bf16(128, 128, false, true, /*negate_a=*/true);
@@ -328,7 +329,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       mbar_expect_tx(&bar_q, (SELF ? 1 : 2) * DK * kRowTile);
       for (int s2 = 0; s2 < DK; ++s2) {
         tma_load_4d(smem + L::q + s2 * kRowTile, &map_q, &bar_q, s2 * 64, i0, h, b);
-        if (!SELF) tma_load_4d(smem + L::q0_landing + s2 * kRowTile, &map_q, &bar_q, s2 * 64, i0, 0, b);
+        if (!SELF) tma_load_4d(smem + L::q0_landing + s2 * kRowTile, &map_q0, &bar_q, s2 * 64, i0, 0, b);
       }
       load_k0(0);
       load_k(0);
@@ -592,8 +593,13 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   if (st != SA_OK) return st;
   st = make_map_16bit(&map_v128, p.v.ptr, D, p.seq, p.heads, p.batch, p.v.st, p.v.sh, p.v.sb, kTile);
   if (st != SA_OK) return st;
-  unsigned int* status = nullptr;
-  st = status_word(&status);
+  CUtensorMap map_q0, map_k0;                            // the selector's rows: (d, token, 1, batch)
+  st = make_map_16bit(&map_q0, p.q0.ptr, D, p.seq, 1, p.batch, p.q0.st, 0, p.q0.sb, kTile);
+  if (st != SA_OK) return st;
+  st = make_map_16bit(&map_k0, p.k0.ptr, D, p.seq, 1, p.batch, p.k0.st, 0, p.k0.sb, kTile);
+  if (st != SA_OK) return st;
+  WaitCtx status;
+  st = wait_ctx(&status);
   if (st != SA_OK) return st;
 
   constexpr int DK = D / 64;
@@ -602,29 +608,32 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   dim3 gc(ntiles, (ntiles + kColsumChunk - 1) / kColsumChunk, p.batch);
   {
     ProfileScope prof(SA_KERNEL_TC_COLSUM, s);
-    colsum_kernel<D><<<gc, 128, colsum_smem, s>>>(map_q, map_k128, carry, p.seq, ntiles, p.exempt, p.scale, status);
+    count_launch();
+    colsum_kernel<D><<<gc, 128, colsum_smem, s>>>(map_q0, map_k0, carry, p.seq, ntiles, p.exempt, p.scale, status);
   }
   SA_CUDA_CHECK(cudaGetLastError());
   dim3 gs((p.seq + 255) / 256, p.batch);
   {
     ProfileScope prof(SA_KERNEL_TC_SCAN, s);
+    count_launch();
     scan_kernel<<<gs, 256, 0, s>>>(carry, total, p.seq, ntiles);
   }
   SA_CUDA_CHECK(cudaGetLastError());
 
   const unsigned grid = (unsigned)ntiles * p.batch * p.heads;
-  const bool self = (p.heads == 1);            // one head per selector: the selection logits are the head's own
+  const bool self = (p.heads == 1) && !p.external_selector;   // one head per selector: the selection logits are the head's own
   {
     const int wide_smem = WideSmem<D>::total + 1024;
     if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(forward_wide_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
     else SA_CUDA_CHECK(cudaFuncSetAttribute(forward_wide_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
     {
       ProfileScope prof(SA_KERNEL_TC_FORWARD, s);
+      count_launch();
       if (self)
-        forward_wide_kernel<D, true><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, carry, out, lse2,
+        forward_wide_kernel<D, true><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2,
                                                                             p.heads, p.seq, ntiles, p.exempt, p.scale, status);
       else
-        forward_wide_kernel<D, false><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, carry, out, lse2,
+        forward_wide_kernel<D, false><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2,
                                                                              p.heads, p.seq, ntiles, p.exempt, p.scale, status);
     }
     SA_CUDA_CHECK(cudaGetLastError());

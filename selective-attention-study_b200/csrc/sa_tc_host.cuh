@@ -30,10 +30,10 @@ inline int make_map_16bit(CUtensorMap* map, const void* base, int head_dim, int 
   auto fn = encode_fn();
   if (fn == nullptr) return SA_ERR_CUDA;
   if ((reinterpret_cast<uintptr_t>(base) & 15) != 0) return SA_ERR_ALIGNMENT;
-  if (((st * 2) & 15) || ((sh * 2) & 15) || ((sb * 2) & 15)) return SA_ERR_ALIGNMENT;
-  // A dimension of extent 1 may carry any stride; give it a valid one.
+  // A dimension of extent 1 may carry any stride; give it a valid one before the alignment rule is applied.
   if (heads == 1) sh = st * seq;
   if (batch == 1) sb = sh * heads;
+  if (((st * 2) & 15) || ((sh * 2) & 15) || ((sb * 2) & 15)) return SA_ERR_ALIGNMENT;
   cuuint64_t dims[4] = {(cuuint64_t)head_dim, (cuuint64_t)seq, (cuuint64_t)heads, (cuuint64_t)batch};
   cuuint64_t strides[3] = {(cuuint64_t)st * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
   cuuint32_t box[4] = {64, (cuuint32_t)box_rows, 1, 1};
@@ -68,8 +68,33 @@ inline int make_map_f32_rows(CUtensorMap* map, const void* base, int seq, int ro
   return SA_OK;
 }
 
-int status_word(unsigned int** device_ptr);            // per-device status word of the bounded waits
-int read_status(unsigned int* host_value, bool clear); // synchronous read (and reset) of that word
+// What a kernel with bounded waits is given (see sa_tc_ptx.cuh for how the device side uses it).
+struct WaitCtx {
+  unsigned int* word;
+  unsigned int* host_flag;
+  unsigned int epoch;          // never 0
+  unsigned int limit_kcycles;  // a wait gives up after this many clock64 ticks / 1024
+};
+
+// Context for the next launch sequence on the current device: a fresh epoch and the default limit.  The
+// mapped host flag (one page of pinned host memory per device) is created on first use unless
+// `may_create_host_flag` is false (entry points that must not call an allocating routine), in which case the
+// context carries whatever exists (possibly none).
+int wait_ctx(WaitCtx* out, bool may_create_host_flag = true);
+// While one of these is alive on a host thread, wait_ctx never creates the host flag on that thread.
+struct NoHostAllocScope {
+  NoHostAllocScope();
+  ~NoHostAllocScope();
+};
+// Non-zero when a bounded wait has run out on the current device and the word has not been cleared; reads
+// only host memory, so entry points call it first and refuse to launch (SA_ERR_DEVICE_TIMEOUT).
+unsigned int timeout_pending();
+// Synchronous read (and reset) of the sticky word.  Uses cudaMemcpy on the legacy default stream: it is ordered
+// after work on blocking streams only; callers on non-blocking streams synchronise first.
+int read_status(unsigned int* host_value, bool clear);
+// Runs one CTA that waits, with the given limit, on an mbarrier nobody arrives on: the wait runs out, reports
+// site 900 and the kernel returns.
+int selftest_wait_timeout(unsigned int limit_kcycles, cudaStream_t s);
 int selftest(void* scratch, float* result, cudaStream_t s);
 
 }  // namespace tc

@@ -1,7 +1,7 @@
 // sm_100a primitives used by the tensor-core engine: mbarriers with bounded waits, TMA tile loads,
 // tensor-memory allocation, tcgen05 MMA issue / commit / load / store, and the shared-memory and
 // instruction descriptors of tcgen05.mma.  Every wait is bounded: when a wait runs out it records a
-// code in the device status word and returns, so a kernel always terminates and frees its TMEM.
+// code in the device status words and returns, so a kernel always terminates and frees its TMEM.
 #pragma once
 
 #include <cuda.h>
@@ -9,16 +9,28 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include "sa_tc_host.cuh"
+
 namespace sa {
 namespace tc {
 
-// ---- device status word -----------------------------------------------------------------------------
-// Kernels receive a pointer to one status word per device (status_word() on the host).  0 = fine;
-// otherwise (site << 8) | 1 of the first bounded wait that ran out.  sa_device_status() reads it.
-constexpr long long kWaitLimitCycles = 400000000LL;   // ~0.2 s at 2 GHz; an honest wait is microseconds
+// ---- bounded waits: what a kernel is given, and what it reports ---------------------------------------
+// Every kernel that waits receives a WaitCtx by value.  Device memory holds two words per device:
+//   word[0]  sticky: (site << 8) | 1 of the FIRST bounded wait that ever ran out (diagnosis; cleared by the host)
+//   word[1]  the epoch of the launch sequence that gave up: waits of THAT sequence return at once, so a broken
+//            kernel ends quickly and frees its TMEM, while launches with another epoch are not affected
+// and the host keeps a mapped copy of the sticky word (host_flag, may be null) that a kernel writes only on
+// the failure path, so the next entry-point call can refuse to run without synchronising the device.
+constexpr unsigned int kWaitLimitKCycles = 400000u;   // ~0.2 s at 2 GHz; an honest wait is microseconds
 
-__device__ __forceinline__ void report(unsigned int* status, unsigned int site) {
-  atomicCAS(status, 0u, (site << 8) | 1u);
+__device__ __forceinline__ void report(const WaitCtx& w, unsigned int site) {
+  const unsigned int code = (site << 8) | 1u;
+  atomicCAS(w.word, 0u, code);
+  *reinterpret_cast<volatile unsigned int*>(w.word + 1) = w.epoch;
+  if (w.host_flag != nullptr) {
+    *reinterpret_cast<volatile unsigned int*>(w.host_flag) = code;
+    __threadfence_system();
+  }
 }
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -49,18 +61,19 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return done != 0;
 }
-// Waits for the phase with the given parity to complete.  Gives up after kWaitLimitCycles, or at once
-// when another wait has already given up (the status word is set), so a broken kernel ends quickly.
+// Waits for the phase with the given parity to complete.  Gives up after the context's limit, or at once
+// when another wait of the same launch sequence has already given up, so a broken kernel ends quickly.
 // Callable by a single thread of a warp: it contains no warp-wide operation.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, unsigned int* status, unsigned int site) {
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, const WaitCtx& w, unsigned int site) {
   if (mbar_try_wait(bar, parity)) return;
   const long long start = clock64();
+  const long long limit = (long long)w.limit_kcycles << 10;
   int spins = 0;
   while (!mbar_try_wait(bar, parity)) {
     if ((++spins & 63) == 0) {
-      if (*reinterpret_cast<volatile unsigned int*>(status) != 0u) return;
-      if (clock64() - start > kWaitLimitCycles) {
-        report(status, site);
+      if (*reinterpret_cast<volatile unsigned int*>(w.word + 1) == w.epoch) return;
+      if (clock64() - start > limit) {
+        report(w, site);
         return;
       }
     }

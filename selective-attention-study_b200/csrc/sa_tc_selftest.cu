@@ -17,8 +17,6 @@ namespace tc {
 
 namespace {
 
-__device__ unsigned int g_status = 0;
-
 
 __device__ __forceinline__ float pattern(int salt, int r, int c) {
   return (float)(((r * 7 + c * 13 + salt * 5 + (r * c) % 11) % 9) - 4);   // integers in [-4, 4]
@@ -48,7 +46,7 @@ __global__ void __launch_bounds__(128) selftest_kernel(const __grid_constant__ C
                                                        const __grid_constant__ CUtensorMap map_y,
                                                        const __nv_bfloat16* __restrict__ xg,
                                                        const __nv_bfloat16* __restrict__ yg, float* result,
-                                                       unsigned int* status) {
+                                                       WaitCtx status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* xs = smem;                 // [128][64] from TMA
@@ -260,28 +258,11 @@ int selftest(void* scratch, float* result, cudaStream_t s) {
   if (st != SA_OK) return st;
   const int smem = 98304 + 1024;
   SA_CUDA_CHECK(cudaFuncSetAttribute(selftest_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  unsigned int* status = nullptr;
-  st = status_word(&status);
+  WaitCtx status;
+  st = wait_ctx(&status);
   if (st != SA_OK) return st;
   selftest_kernel<<<1, 128, smem, s>>>(mx, my, x, y, result, status);
   SA_CUDA_CHECK(cudaGetLastError());
-  return SA_OK;
-}
-
-// Address of the status word on the current device (a file-scope __device__ variable: no allocation).
-int status_word(unsigned int** ptr) {
-  void* p = nullptr;
-  SA_CUDA_CHECK(cudaGetSymbolAddress(&p, g_status));
-  *ptr = static_cast<unsigned int*>(p);
-  return SA_OK;
-}
-
-int read_status(unsigned int* host_value, bool clear) {
-  unsigned int* p = nullptr;
-  int st = status_word(&p);
-  if (st != SA_OK) return st;
-  SA_CUDA_CHECK(cudaMemcpy(host_value, p, sizeof(unsigned int), cudaMemcpyDeviceToHost));
-  if (clear && *host_value != 0) SA_CUDA_CHECK(cudaMemset(p, 0, sizeof(unsigned int)));
   return SA_OK;
 }
 

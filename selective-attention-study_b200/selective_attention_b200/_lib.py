@@ -22,7 +22,8 @@ DAMP_CODES = {"none": 0, "linear": 1, "sqrt": 2}
 # every symbol include/selective_attention_b200.h declares
 EXPORTS = ("sa_abi_version", "sa_status_string", "sa_last_cuda_error", "sa_engine_available", "sa_engine_supports", "sa_carry_rows", "sa_carry_checkpoints", "sa_forward",
            "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step", "sa_device_status", "sa_selftest_tcgen05", "sa_profile_enable",
-           "sa_profile_collect", "sa_static_scratch_floats", "sa_forward_static_scratch")
+           "sa_profile_collect", "sa_static_scratch_floats", "sa_forward_static_scratch", "sa_forward_selector",
+           "sa_backward_selector", "sa_selection_carry", "sa_launch_count", "sa_selftest_wait_timeout")
 
 
 class Problem(ctypes.Structure):
@@ -31,6 +32,11 @@ class Problem(ctypes.Structure):
                 ("head_dim", ctypes.c_int32), ("exempt", ctypes.c_int32), ("damp", ctypes.c_int32),
                 ("train_len", ctypes.c_int32), ("q_stride", ctypes.c_int64 * 3), ("k_stride", ctypes.c_int64 * 3),
                 ("v_stride", ctypes.c_int64 * 3)]
+
+
+class Selector(ctypes.Structure):
+    _fields_ = [("struct_bytes", ctypes.c_int32), ("reserved", ctypes.c_int32), ("q0", ctypes.c_void_p),
+                ("k0", ctypes.c_void_p), ("q0_stride", ctypes.c_int64 * 2), ("k0_stride", ctypes.c_int64 * 2)]
 
 
 class LibraryError(RuntimeError):
@@ -70,6 +76,16 @@ def load() -> ctypes.CDLL:
     lib.sa_carry_checkpoints.argtypes = [i32, i32]
     lib.sa_forward.restype = i32
     lib.sa_forward.argtypes = [pp, vp, vp, vp, f32p, f32p, f32p, f32p, vp]
+    sp = ctypes.POINTER(Selector)
+    lib.sa_forward_selector.restype = i32
+    lib.sa_forward_selector.argtypes = [pp, vp, vp, vp, sp, f32p, f32p, f32p, f32p, vp]
+    lib.sa_backward_selector.restype = i32
+    lib.sa_backward_selector.argtypes = [pp, vp, vp, vp, sp, f32p, f32p, f32p, vp, i32, vp, vp, vp, f32p, f32p, vp, sz, vp]
+    lib.sa_selection_carry.restype = i32
+    lib.sa_selection_carry.argtypes = [pp, vp, vp, sp, f32p, f32p, vp]
+    lib.sa_launch_count.restype = ctypes.c_ulonglong
+    lib.sa_selftest_wait_timeout.restype = i32
+    lib.sa_selftest_wait_timeout.argtypes = [ctypes.c_uint, vp]
     lib.sa_backward_workspace_bytes.restype = sz
     lib.sa_backward_workspace_bytes.argtypes = [pp]
     lib.sa_backward.restype = i32
@@ -109,6 +125,11 @@ def profile_collect(capacity: int = 512) -> list[float]:
     return [buf[i] for i in range(n)]
 
 
+def launch_count() -> int:
+    """Kernels of the library launched by this process so far."""
+    return int(load().sa_launch_count())
+
+
 def device_status(clear: bool = True) -> int:
     """Status word of the tensor-core engine's bounded waits on the current device (0 = fine)."""
     value = ctypes.c_uint(0)
@@ -122,4 +143,6 @@ def check(fn: str, status: int) -> None:
         detail = lib.sa_status_string(status).decode()
         if status == 5:
             detail += f", cudaError {lib.sa_last_cuda_error()}"
+        if status == 6:
+            detail += "; results of the launch that gave up are invalid; read and clear the word with device_status()"
         raise LibraryError(fn, status, detail)

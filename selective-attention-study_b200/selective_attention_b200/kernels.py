@@ -147,6 +147,38 @@ def _problem(q, k, v, engine: int, exempt: int, damp: int = 0, train_len: int = 
     return p
 
 
+def _selector_struct(q0: torch.Tensor, k0: torch.Tensor) -> _lib.Selector:
+    s = _lib.Selector()
+    s.struct_bytes = ctypes.sizeof(_lib.Selector)
+    s.q0, s.k0 = q0.data_ptr(), k0.data_ptr()
+    s.q0_stride[:] = [q0.stride(0), q0.stride(1)]
+    s.k0_stride[:] = [k0.stride(0), k0.stride(1)]
+    return s
+
+
+def _check_selector(selector, q: torch.Tensor):
+    """(q0, k0): the selection head's rows, (B, T, D) or (B, 1, T, D), on q's device."""
+    if selector is None:
+        return None
+    try:
+        q0, k0 = selector
+    except (TypeError, ValueError):
+        raise ValueError("selector must be a pair (q0, k0) of tensors") from None
+    b, _, t, d = q.shape
+    out = []
+    for x in (q0, k0):
+        if x.dim() == 4 and x.shape[1] == 1:
+            x = x[:, 0]
+        if tuple(x.shape) != (b, t, d):
+            raise ValueError(f"selector tensors must all be (B, T, D) = {(b, t, d)}; got {tuple(x.shape)}")
+        if x.device != q.device:
+            raise ValueError("selector tensors must be CUDA tensors on q's device")
+        if x.dtype not in DTYPES:
+            raise ValueError(f"selector dtype must be float16, bfloat16 or float32; got {x.dtype}")
+        out.append(x)
+    return tuple(out)
+
+
 def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -163,26 +195,68 @@ def _prepare(q, k, v, lowp: bool):
     return tuple(t if t.dtype == want else t.to(want) for t in (q, k, v))
 
 
-def _forward(q, k, v, lowp: bool, exempt: int, damp: int, train_len: int, with_backward: bool = False):
+def _prepare_selector(selector, want: torch.dtype, tc: bool):
+    if selector is None:
+        return None
+    out = []
+    for x in selector:
+        x = x if x.dtype == want else x.to(want)
+        ok = x.stride(2) == 1
+        if ok and tc:
+            es = x.element_size()
+            ok = x.data_ptr() % 16 == 0 and all((st * es) % 16 == 0 for st in x.stride()[:2])
+        out.append(x if ok else x.contiguous())
+    return tuple(out)
+
+
+def _carry_rows_request(carry_rows):
+    if carry_rows is None:
+        env = os.environ.get("SA_B200_CARRY_ROWS", "")
+        carry_rows = int(env) if env else None
+    if carry_rows not in (None, 32, 128):
+        raise ValueError(f"carry_rows must be None, 32 or 128; got {carry_rows}")
+    return carry_rows
+
+
+def _selection_carry32(q, k, sel, exempt: int, zero: bool):
+    """Checkpoints every 32 queries (the reference's CARRY layout) from the CUDA-core selection pass."""
+    lib = _lib.load()
+    b, _, t, _ = q.shape
+    alloc = torch.zeros if zero else torch.empty
+    carry = alloc(b, lib.sa_carry_checkpoints(_lib.ENGINE_SIMT, t), t, device=q.device, dtype=torch.float32)
+    total = torch.empty(b, t, device=q.device, dtype=torch.float32)
+    prob = _problem(q, k, q, _lib.ENGINE_SIMT, exempt)
+    sel_ref = ctypes.byref(_selector_struct(*sel)) if sel is not None else None
+    with torch.cuda.device(q.device):
+        st = lib.sa_selection_carry(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), sel_ref, carry.data_ptr(),
+                                    total.data_ptr(), _stream(q.device))
+    _lib.check("sa_selection_carry", st)
+    return carry
+
+
+def _forward(q, k, v, lowp: bool, exempt: int, damp: int, train_len: int, selector=None, zero_carry: bool = False):
     lib = _lib.load()
     b, h, t, d = q.shape
-    engine = _engine(lowp, d, with_backward)
+    engine = _engine(lowp, d, False)
     if damp and engine == _lib.ENGINE_TCGEN05:
         engine = _lib.ENGINE_SIMT          # row-scaled F is an evaluation-only option of the CUDA-core engine
     tc = engine == _lib.ENGINE_TCGEN05
     q, k, v = (_strided(x, tc) for x in _prepare(q, k, v, lowp))
+    sel = _prepare_selector(selector, q.dtype, tc)
     dev = q.device
     carry_m = lib.sa_carry_rows(engine)
     out = torch.empty(b, h, t, d, device=dev, dtype=torch.float32)
     lse2 = torch.empty(b, h, t, device=dev, dtype=torch.float32)
-    carry = torch.empty(b, lib.sa_carry_checkpoints(engine, t), t, device=dev, dtype=torch.float32)
+    alloc = torch.zeros if zero_carry else torch.empty
+    carry = alloc(b, lib.sa_carry_checkpoints(engine, t), t, device=dev, dtype=torch.float32)
     total = torch.empty(b, t, device=dev, dtype=torch.float32)
     prob = _problem(q, k, v, engine, exempt, damp, train_len)
+    sel_ref = ctypes.byref(_selector_struct(*sel)) if sel is not None else None
     with torch.cuda.device(dev):
-        st = lib.sa_forward(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                            lse2.data_ptr(), carry.data_ptr(), total.data_ptr(), _stream(dev))
+        st = lib.sa_forward_selector(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), sel_ref,
+                                     out.data_ptr(), lse2.data_ptr(), carry.data_ptr(), total.data_ptr(), _stream(dev))
     _lib.check("sa_forward", st)
-    return out, lse2, carry, total, (q, k, v), engine, carry_m
+    return out, lse2, carry, total, (q, k, v), sel, engine, carry_m
 
 
 def selective_attention_forward(
@@ -200,6 +274,8 @@ def selective_attention_forward(
     *,
     damp: str = "none",
     train_len: int = 0,
+    selector=None,
+    carry_rows: int | None = None,
 ):
     """Forward without autograd: fp32 (B, H, T, D).  With ``return_aux`` also a dict with ``rmax``
     (the row log-sum-exp in log2 units), ``rden`` (ones), ``carry``, ``carry_m`` and
@@ -207,7 +283,13 @@ def selective_attention_forward(
     decode accumulator after this prefix.  ``damp`` ("none" | "linear" | "sqrt") with ``train_len``
     scales the history term of query i by min(1, train_len / (i + 1)) or its square root
     (evaluation only; the backward does not implement it).  block_m / block_n / num_warps /
-    num_stages / group are accepted for signature compatibility and only validated."""
+    num_stages / group are accepted for signature compatibility and only validated.
+
+    Beyond the reference's signature (keyword-only): ``selector=(q0, k0)`` takes the selection head's
+    rows, (B, T, D), from outside q / k (for a call that holds only some heads of each sequence);
+    ``carry_rows=32`` (or the environment variable SA_B200_CARRY_ROWS=32) returns ``aux["carry"]`` with the
+    reference's checkpoint every 32 queries whichever engine ran (an extra selection pass on the CUDA
+    cores); by default the spacing is the engine's own, reported in ``aux["carry_m"]``."""
     check_inputs(q, k, v)
     exempt = _check_exempt(exempt)
     lowp = _lowp(dot_precision, q.dtype)
@@ -216,13 +298,50 @@ def selective_attention_forward(
         raise ValueError(f"damp must be 'none', 'linear' or 'sqrt'; got {damp!r}")
     if _lib.DAMP_CODES[damp] and train_len < 1:
         raise ValueError("damp needs train_len (the trained context length)")
-    out, lse2, carry, total, _, _, carry_m = _forward(q, k, v, lowp, exempt, _lib.DAMP_CODES[damp], train_len)
+    selector = _check_selector(selector, q)
+    carry_rows = _carry_rows_request(carry_rows) if return_aux else None
+    out, lse2, carry, total, operands, sel, _, carry_m = _forward(
+        q, k, v, lowp, exempt, _lib.DAMP_CODES[damp], train_len, selector=selector, zero_carry=return_aux)
     if not return_aux:
         return out
     b, h, t, _ = q.shape
+    if carry_rows is not None and carry_rows != carry_m:
+        if carry_rows != 32:
+            raise ValueError("carry_rows=128 is only available where the tensor-core engine runs")
+        carry, carry_m = _selection_carry32(operands[0], operands[1], sel, exempt, zero=True), 32
     aux = dict(rmax=lse2.view(b * h, t), rden=torch.ones(b * h, t, device=q.device, dtype=torch.float32),
                carry=carry[:, :(t + carry_m - 1) // carry_m], carry_m=carry_m, selected_total=total)
     return out, aux
+
+
+def _backward_call(ctx, dout, dq0=None, dk0=None):
+    q, k, v, out, lse2, carry = ctx.saved_tensors[:6]
+    sel = tuple(ctx.saved_tensors[6:8]) if len(ctx.saved_tensors) > 6 else None
+    lib = _lib.load()
+    dev = q.device
+    if dout.dtype not in _DTYPE_CODE:
+        dout = dout.float()
+    dout = dout.contiguous()
+    engine = ctx.engine
+    if engine == _lib.ENGINE_TCGEN05 and not lib.sa_engine_supports(engine, _DTYPE_CODE[q.dtype], q.shape[3], 1):
+        # The tensor-core forward ran, but this head_dim has no tensor-core backward: the CUDA-core backward takes
+        # the forward's out / lse and its own 32-query checkpoints from a selection pass of its own.
+        engine = _lib.ENGINE_SIMT
+        carry = _selection_carry32(q, k, sel, ctx.exempt, zero=False)
+    prob = _problem(q, k, v, engine, ctx.exempt)
+    need = lib.sa_backward_workspace_bytes(ctypes.byref(prob))
+    workspace = torch.empty(max(need, 1), device=dev, dtype=torch.uint8)
+    dq, dk, dv = (torch.empty(q.shape, device=dev, dtype=q.dtype) for _ in range(3))
+    sel_ref = ctypes.byref(_selector_struct(*sel)) if sel is not None else None
+    with torch.cuda.device(dev):
+        st = lib.sa_backward_selector(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), sel_ref,
+                                      out.data_ptr(), lse2.data_ptr(), carry.data_ptr(), dout.data_ptr(),
+                                      _DTYPE_CODE[dout.dtype], dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                      dq0.data_ptr() if dq0 is not None else None,
+                                      dk0.data_ptr() if dk0 is not None else None, workspace.data_ptr(), need,
+                                      _stream(dev))
+    _lib.check("sa_backward", st)
+    return dq, dk, dv
 
 
 class _SelectiveAttentionFn(torch.autograd.Function):
@@ -233,7 +352,7 @@ class _SelectiveAttentionFn(torch.autograd.Function):
         exempt = _check_exempt(exempt)
         lowp = _lowp(dot_precision, q.dtype)
         _check_blocks(block_m, block_n)
-        out, lse2, carry, _, operands, engine, _ = _forward(q, k, v, lowp, exempt, 0, 0, with_backward=True)
+        out, lse2, carry, _, operands, _, engine, _ = _forward(q, k, v, lowp, exempt, 0, 0)
         ctx.save_for_backward(*operands, out, lse2, carry)
         ctx.engine, ctx.exempt, ctx.bwd_group = engine, exempt, bwd_group
         ctx.grad_dtypes = (q.dtype, k.dtype, v.dtype)
@@ -243,24 +362,41 @@ class _SelectiveAttentionFn(torch.autograd.Function):
     @once_differentiable
     def backward(ctx, dout):
         _check_bwd_group(ctx.bwd_group)
-        q, k, v, out, lse2, carry = ctx.saved_tensors
-        lib = _lib.load()
-        dev = q.device
-        if dout.dtype not in _DTYPE_CODE:
-            dout = dout.float()
-        dout = dout.contiguous()
-        prob = _problem(q, k, v, ctx.engine, ctx.exempt)
-        need = lib.sa_backward_workspace_bytes(ctypes.byref(prob))
-        workspace = torch.empty(max(need, 1), device=dev, dtype=torch.uint8)
-        dq, dk, dv = (torch.empty(q.shape, device=dev, dtype=q.dtype) for _ in range(3))
-        with torch.cuda.device(dev):
-            st = lib.sa_backward(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(),
-                                 lse2.data_ptr(), carry.data_ptr(), dout.data_ptr(), _DTYPE_CODE[dout.dtype],
-                                 dq.data_ptr(), dk.data_ptr(), dv.data_ptr(), workspace.data_ptr(), need,
-                                 _stream(dev))
-        _lib.check("sa_backward", st)
-        grads = tuple(g if g.dtype == want else g.to(want) for g, want in zip((dq, dk, dv), ctx.grad_dtypes))
+        grads = _backward_call(ctx, dout)
+        grads = tuple(g if g.dtype == want else g.to(want) for g, want in zip(grads, ctx.grad_dtypes))
         return grads + (None,) * 11
+
+
+class _SelectiveAttentionSelectorFn(torch.autograd.Function):
+    """The operator for a call that holds only some heads of each sequence: the selection head's rows come
+    in as their own tensors (q0, k0), and the gradient that reaches them through the history term comes
+    back as THEIR gradient, in fp32 precision before the cast, not folded into any head of q / k.  Ranks that
+    share a sequence sum these partial gradients (all-reduce) like any replicated parameter's."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, q0, k0, dot_precision, exempt):
+        check_inputs(q, k, v)
+        exempt = _check_exempt(exempt)
+        lowp = _lowp(dot_precision, q.dtype)
+        selector = _check_selector((q0, k0), q)
+        out, lse2, carry, _, operands, sel, engine, _ = _forward(q, k, v, lowp, exempt, 0, 0, selector=selector)
+        ctx.save_for_backward(*operands, out, lse2, carry, *sel)
+        ctx.engine, ctx.exempt = engine, exempt
+        ctx.grad_dtypes = (q.dtype, k.dtype, v.dtype)
+        ctx.sel_shapes = (q0.shape, k0.shape, q0.dtype, k0.dtype)
+        return out
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, dout):
+        q = ctx.saved_tensors[0]
+        b, _, t, d = q.shape
+        dq0 = torch.empty(b, t, d, device=q.device, dtype=torch.float32)
+        dk0 = torch.empty(b, t, d, device=q.device, dtype=torch.float32)
+        grads = _backward_call(ctx, dout, dq0, dk0)
+        grads = tuple(g if g.dtype == want else g.to(want) for g, want in zip(grads, ctx.grad_dtypes))
+        q0_shape, k0_shape, q0_dtype, k0_dtype = ctx.sel_shapes
+        return grads + (dq0.reshape(q0_shape).to(q0_dtype), dk0.reshape(k0_shape).to(k0_dtype), None, None)
 
 
 def selective_attention(
@@ -278,12 +414,23 @@ def selective_attention(
     bwd_group: int | None = None,
     num_stages: int | None = None,
     exempt: int = 1,
+    *,
+    selector=None,
 ) -> torch.Tensor:
     """Differentiable Selective Attention.  q / k / v: (B, H, T, D) CUDA tensors (fp16, bf16 or fp32;
     D in 16, 32, 64, 128; any strides).  Returns fp32 (B, H, T, D); gradients come back in the input
     dtypes.  dot_precision: None -> "bf16" for bf16 inputs, otherwise "tf32"; "ieee" and "tf32" both
     run exact fp32 products.  exempt: keys [0, exempt) are never selected (1 = <BOS>, the paper's rule).
-    The remaining keywords are the reference's launch-tuning knobs: validated, otherwise unused."""
+    The remaining positional keywords are the reference's launch-tuning knobs: validated, otherwise unused.
+
+    ``selector=(q0, k0)`` (keyword-only, beyond the reference's signature) shards the heads of a sequence:
+    q / k / v hold any subset of its heads and q0 / k0, (B, T, D), are a replica of the selection head's rows.
+    Gradients flow to q0 / k0 as this call's partial sums; sum them over the calls that share the selector."""
+    if selector is not None:
+        _check_blocks(block_m, block_n)
+        _check_bwd_group(bwd_group)
+        q0, k0 = selector
+        return _SelectiveAttentionSelectorFn.apply(q, k, v, q0, k0, dot_precision, exempt)
     return _SelectiveAttentionFn.apply(q, k, v, dot_precision, block_m, block_n, num_warps, bwd_block_n,
                                        bwd_num_warps, bwd_num_stages, group, bwd_group, num_stages, exempt)
 

@@ -29,3 +29,20 @@ def golden():
             return {k: (torch.from_numpy(data[k]) if data[k].ndim else data[k].item()) for k in data.files}
 
     return load
+
+
+@pytest.fixture(scope="session")
+def achieved():
+    """Records the error a parity test achieved (not only that it was under its bar): prints it, so it shows
+    with ``pytest -rP`` / ``-s``, and appends a JSON line to the file named by SA_PARITY_LOG when that is set."""
+    import json
+
+    def record(case: str, **values):
+        line = {"case": case, **{k: (float(v) if v is not None else None) for k, v in values.items()}}
+        print("achieved:", json.dumps(line))
+        path = os.environ.get("SA_PARITY_LOG")
+        if path:
+            with open(path, "a") as fh:
+                fh.write(json.dumps(line) + "\n")
+
+    return record

@@ -136,10 +136,28 @@ def test_backward_exempt_prefix(exempt, heads):
         assert _rel(a, b) < 2e-2, (name, _rel(a, b))
 
 
-def test_head_dim_128_trains_through_the_cuda_core_engine():
-    """The tensor-core backward covers head_dim 64; 128 must still give correct gradients."""
-    q, k, v, w = _inputs(1, 2, 200, 128, seed=9, scale=0.5)
+@pytest.mark.parametrize("seq", [129, 1000, 2049])
+def test_head_dim_128_training_keeps_the_tensor_core_forward(seq):
+    """head_dim 128 has a tensor-core forward but no tensor-core backward: under autograd the forward still runs on
+    the tensor cores (carry checkpoints every 128 queries) and the backward runs on the CUDA cores from the
+    forward's out / lse with 32-query checkpoints of its own."""
+    q, k, v, w = _inputs(1, 2, seq, 128, seed=9 + seq, scale=0.5)
+    before = _lib.launch_count()
     got = _fwd_bwd(q, k, v, w)
+    assert _lib.launch_count() - before == 3 + 5          # colsum, scan, forward | dbar, carry, backward, 2 x fold
     want = oracle.attention_grads(q.float(), k.float(), v.float(), w.float())
     for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
         assert _rel(a, b) < 2e-2, (name, _rel(a, b))
+
+
+def test_reference_layout_of_the_carry_on_request():
+    """aux["carry"] every 32 queries (the reference's CARRY_M) from the bf16 path, zero where nothing is stored."""
+    q, k, v, _ = _inputs(2, 2, 300, 64, seed=21)
+    _, native = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda(), return_aux=True)
+    _, aux = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda(), return_aux=True, carry_rows=32)
+    assert native["carry_m"] == 128 and aux["carry_m"] == 32 and aux["carry"].shape == (2, 10, 300)
+    sel = oracle.selection_matrix(q[:, 0].float(), k[:, 0].float())
+    for rb in range(10):
+        want = sel[:, : 32 * rb].sum(dim=1)                 # zero for keys at or after the block, stored or not
+        torch.testing.assert_close(aux["carry"][:, rb].cpu(), want, atol=1e-3, rtol=1e-3)
+    assert (native["carry"][:, 0] == 0).all() and (aux["carry"][:, 0] == 0).all()
