@@ -1,22 +1,29 @@
 """Benchmark of the Selective Attention operator on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4|decode|c5]
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N ... bench.py --gpus N ...
 
 A step is one forward + backward of the operator over one batch of synthetic input (workload c2:
 B=4, H=16, T=16384, D=64, bf16 q/k/v/dO ~ N(0,1), causal, <BOS> exempt, head 0 selects for all heads).
-With N > 1 every rank runs its own batch of the same shape (weak scaling, no communication inside the
-operator) and the reported value is the tokens of all ranks over the slowest rank's device time.
+
+With N > 1 the SAME batch is sharded over the ranks (strong scaling): whole sequences per rank while N <= B,
+and beyond that the heads of a sequence are split between N / B ranks, each of which holds a replica of the
+selection head's q, k rows (``selector=``) and returns partial gradients for them; those partial gradients are
+summed with one NCCL all-reduce per group of ranks sharing a sequence, inside the timed region and also
+reported on its own.  No other data crosses GPUs.  ``--replicas`` instead gives every rank its own full batch
+(weak scaling).  The reported value is the tokens of the whole job over the slowest rank's device time.
 
 One JSON line is printed by rank 0:
   value        tokens/s with inputs resident in HBM (device time of the forward and backward calls)
   e2e          the same through the public Python API with host buffers: pinned host -> device copies of
-               q, k, v, dO and device -> host copies of out and the three gradients inside the timed region
+               q, k, v, dO and device -> host copies of out and the gradients inside the timed region
   roofline     the backward kernel (the dominant launch): algorithmic FLOPs over its device time, measured
                with CUDA events around that launch, against the measured bf16 tensor peak
-  cpu_baseline the CPU oracle timed on this host on a bounded sample (rank 0, N = 1 only)
---impl reference times the CPU restatement of the reference's algorithm instead (oracle/), on a bounded
-sample of the same workload, with all host threads.
+  cpu_baseline the reference's CPU listing timed on this host on a bounded sample (rank 0, N = 1 only)
+--impl reference times the reference's own CPU implementation of the operator (its dense listing with
+autograd, from the installed copy under baseline/_ref; the CPU oracle port when that copy is absent) on a
+bounded sample of the same workload with all host threads, and, where the reference's Triton kernels run on
+this GPU, also reports them at the full configuration under "reference_gpu".
 """
 
 from __future__ import annotations
@@ -48,11 +55,19 @@ WORKLOADS = {
 }
 METRIC = "selective-attn fwd+bwd tokens/s/GPU @T=16K bf16; % of tcgen05 bf16 peak"
 NOMINAL_BF16_TFLOPS = 2250.0
-FALLBACK_BF16_TFLOPS = 1590.0      # earlier measurement on this pool (burst); used only without MEASURED_PEAKS.json
+FALLBACK_BF16_TFLOPS = 1590.0      # B200 cuBLAS bf16 burst; used only when MEASURED_PEAKS.json is absent
 
-# dram__bytes_read.sum + dram__bytes_write.sum per launch of the backward kernel, from the ncu capture
-# summarised under profiles/ (captured on a smaller case and scaled by head-tiles; None = not captured).
-BACKWARD_DRAM_TRAFFIC_PER_HEAD_TILE = 1375.65e6 / 132096   # B=1 capture, profiles/backward_kernel_B1_H16_T16384_D64.md
+
+def captured_traffic_per_head_tile(kernel: str):
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of `kernel` divided by the head-tiles of the
+    captured (smaller) case, from the record kept beside the ncu summaries; None when no capture is recorded."""
+    path = os.path.join(ROOT, "profiles", "dram_traffic.json")
+    try:
+        with open(path) as fh:
+            rec = json.load(fh)[kernel]
+        return float(rec["dram_bytes_per_launch"]) / float(rec["head_tiles"])
+    except (OSError, KeyError, ValueError):
+        return None
 
 
 def pairs(seq: int) -> float:
@@ -190,9 +205,71 @@ def max_over_ranks(value_ms: float, world: int, device) -> float:
     return float(t.item())
 
 
-def whole_job_tokens_per_second(tokens_per_rank: int, world: int, ms_per_step: float) -> float:
-    """Every rank processes its own batch of `tokens_per_rank` tokens per step (weak scaling)."""
-    return world * tokens_per_rank / (ms_per_step * 1e-3)
+def whole_job_tokens_per_second(tokens_per_step: int, ms_per_step: float) -> float:
+    """Tokens the whole job (all ranks together) processes per step over the slowest rank's device time."""
+    return tokens_per_step / (ms_per_step * 1e-3)
+
+
+def shard_plan(w: dict, rank: int, world: int, replicas: bool) -> dict:
+    """Which part of the workload's batch this rank runs.
+
+    replicas: every rank runs the whole batch (weak scaling, `tokens` grows with the ranks).
+    otherwise (strong scaling, `tokens` is the workload's): whole sequences per rank while world <= batch;
+    beyond that `world / batch` ranks share a sequence and split its heads evenly, each holding a replica of the
+    selection head's rows.  The per-head variant has no shared selector: its (batch x heads) rows split evenly."""
+    b, h = w["batch"], w["heads"]
+    if replicas or world == 1:
+        return dict(seqs=range(b), heads=range(h), selector=False, group=[rank], tokens=b * w["seq"] * world,
+                    scaling="weak" if world > 1 else "strong", parallelism=f"{world} independent replicas" if world > 1 else "1 GPU")
+    if w["per_head"]:
+        rows = b * h
+        if rows % world:
+            raise ValueError(f"{rows} (batch x heads) rows do not split over {world} ranks")
+        per = rows // world
+        if per >= h:                      # whole sequences
+            n = per // h
+            return dict(seqs=range(rank * n, (rank + 1) * n), heads=range(h), selector=False, group=[rank],
+                        tokens=b * w["seq"], scaling="strong", parallelism=f"batch split {world} ways")
+        first = rank * per
+        return dict(seqs=range(first // h, first // h + 1), heads=range(first % h, first % h + per), selector=False,
+                    group=[rank], tokens=b * w["seq"], scaling="strong", parallelism=f"(batch x heads) rows split {world} ways")
+    if world <= b:
+        if b % world:
+            raise ValueError(f"batch {b} does not split over {world} ranks")
+        n = b // world
+        return dict(seqs=range(rank * n, (rank + 1) * n), heads=range(h), selector=False, group=[rank],
+                    tokens=b * w["seq"], scaling="strong", parallelism=f"batch split {world} ways")
+    if world % b or h % (world // b):
+        raise ValueError(f"{world} ranks do not split batch {b} x heads {h}")
+    share = world // b                    # ranks per sequence
+    per = h // share
+    seq_index, part = rank // share, rank % share
+    return dict(seqs=range(seq_index, seq_index + 1), heads=range(part * per, (part + 1) * per), selector=True,
+                group=list(range(seq_index * share, (seq_index + 1) * share)), tokens=b * w["seq"], scaling="strong",
+                parallelism=f"batch split {b} ways x heads split {share} ways (selector replicated, its gradient all-reduced)")
+
+
+def bind_near_gpu(device_index: int, local_rank: int, local_world: int) -> str:
+    """Pins this process to a slice of the CPU cores nearest its GPU, before any pinned buffer is allocated, so the
+    host side of every copy stays on that GPU's NUMA node and ranks do not share cores."""
+    try:
+        props = torch.cuda.get_device_properties(device_index)
+        bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
+        with open(f"/sys/bus/pci/devices/{bus}/local_cpulist") as fh:
+            text = fh.read().strip()
+        cores = []
+        for part in text.split(","):
+            lo, _, hi = part.partition("-")
+            cores.extend(range(int(lo), int(hi or lo) + 1))
+        allowed = sorted(set(cores) & set(os.sched_getaffinity(0)))
+        if len(allowed) < local_world:
+            return f"unbound ({len(allowed)} local cores)"
+        per = len(allowed) // local_world
+        mine = allowed[local_rank * per:(local_rank + 1) * per]
+        os.sched_setaffinity(0, mine)
+        return f"cores {mine[0]}-{mine[-1]} of local list {text}"
+    except (OSError, ValueError, AttributeError) as exc:
+        return f"unbound ({type(exc).__name__})"
 
 
 def make_inputs(w: dict, seed: int):
@@ -202,71 +279,113 @@ def make_inputs(w: dict, seed: int):
     return tuple(torch.randn(shape, generator=g).bfloat16() for _ in range(4))
 
 
-def selector_view(t, w):
-    if not w["per_head"]:
-        return t
-    b, h, s, d = t.shape
-    return t.reshape(b * h, 1, s, d)
-
-
 def run_ours(args, w, rank, world, device):
     from selective_attention_b200 import _lib, kernels
 
     if not kernels.HAS_KERNELS:
         raise RuntimeError("the CUDA library is missing; build it first (python __graft_entry__.py)")
-    q_h, k_h, v_h, do_h = (selector_view(t, w).contiguous() for t in make_inputs(w, seed=rank))
-    tokens = w["batch"] * w["seq"]
+    plan = shard_plan(w, rank, world, args.replicas)
+    affinity = bind_near_gpu(device.index, int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("LOCAL_WORLD_SIZE", str(world))))
+    # The full synthetic batch is generated from one seed and every rank slices its shard (replicas: own seed).
+    full = make_inputs(w, seed=rank if plan["scaling"] == "weak" and world > 1 else 0)
+    sl = (slice(plan["seqs"].start, plan["seqs"].stop), slice(plan["heads"].start, plan["heads"].stop))
+    q_h, k_h, v_h, do_h = (t[sl[0], sl[1]].contiguous() for t in full)
+    sel_h = tuple(t[sl[0], 0].contiguous() for t in full[:2]) if plan["selector"] else ()
+    del full
+    if w["per_head"]:                    # every head is its own one-head sequence
+        q_h, k_h, v_h, do_h = (t.reshape(-1, 1, t.shape[2], t.shape[3]) for t in (q_h, k_h, v_h, do_h))
+    tokens = plan["tokens"]
     flops = algorithmic_flops(w)
+    group = None
+    if plan["selector"]:
+        for first in range(0, world, len(plan["group"])):          # every rank creates every group, in the same order
+            ranks = list(range(first, first + len(plan["group"])))
+            g = torch.distributed.new_group(ranks)
+            if ranks == plan["group"]:
+                group = g
+
+    def operator(q, k, v, sel):
+        return kernels.selective_attention(q, k, v, selector=sel) if sel else kernels.selective_attention(q, k, v)
+
+    def reduce_selector_grads(sel, record=None):
+        """The ranks that share a sequence sum their partial gradients of the replicated selector rows."""
+        flat = torch.cat([sel[0].grad.float().reshape(-1), sel[1].grad.float().reshape(-1)])
+        if record is not None:
+            record[0].record()
+        torch.distributed.all_reduce(flat, group=group)
+        if record is not None:
+            record[1].record()
+        return flat
 
     # ---- device-resident arm --------------------------------------------------------------------------
     q, k, v = (t.to(device).requires_grad_(w["backward"]) for t in (q_h, k_h, v_h))
+    sel = tuple(t.to(device).requires_grad_(w["backward"]) for t in sel_h)
     d_out = do_h.to(device).float()            # the operator returns fp32, so its cotangent is fp32
 
     def step(record=None):
-        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
-        e2 = torch.cuda.Event(enable_timing=True)
-        e0.record()
+        ev = [torch.cuda.Event(enable_timing=True) for _ in range(5)]
+        ev[0].record()
         if w["backward"]:
-            out = kernels.selective_attention(q, k, v)
-            e1.record()
+            out = operator(q, k, v, sel)
+            ev[1].record()
             out.backward(d_out)
+            ev[2].record()
+            if sel:
+                reduce_selector_grads(sel, (ev[2], ev[3]))
+                sel[0].grad = sel[1].grad = None
+            else:
+                ev[3].record()
             q.grad = k.grad = v.grad = None
         else:
             with torch.no_grad():
-                out, aux = kernels.selective_attention_forward(q, k, v, return_aux=True)
-            e1.record()
-        e2.record()
+                kernels.selective_attention_forward(q, k, v, return_aux=True, selector=sel or None)
+            ev[1].record(); ev[2].record(); ev[3].record()
+        ev[4].record()
         if record is not None:
-            record.append((e0, e1, e2))
+            record.append(ev)
 
     def barrier():
         if world > 1:
             torch.distributed.barrier()
         torch.cuda.synchronize()
 
+    if not w["backward"] and world > 1 and sel:                    # every shard must see the same per-key totals
+        with torch.no_grad():
+            _, aux = kernels.selective_attention_forward(q, k, v, return_aux=True, selector=sel)
+        mine = aux["selected_total"].clone()
+        theirs = mine.clone()
+        torch.distributed.broadcast(theirs, src=plan["group"][0], group=group)
+        if not torch.equal(mine, theirs):
+            raise RuntimeError("selected_total differs between the ranks that share a sequence")
     for _ in range(args.warmup):
         step()
     dominant = "tc_backward" if w["backward"] else "tc_forward"
     _lib.profile_enable(dominant)
     events = []
     barrier()
+    launches_before = _lib.launch_count()
     with ClockSampler(device.index) as sampler:
         for _ in range(args.steps):
             step(events)
         barrier()
+    launches = _lib.launch_count() - launches_before
     kernel_ms = _lib.profile_collect()
     _lib.profile_enable("none")
-    fwd_ms = sum(a.elapsed_time(b) for a, b, _ in events)
-    bwd_ms = sum(b.elapsed_time(c) for _, b, c in events)
-    total_ms = max_over_ranks(fwd_ms + bwd_ms, world, device)
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in events)
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in events)
+    reduce_ms = sum(e[2].elapsed_time(e[3]) for e in events)
+    total_ms = max_over_ranks(sum(e[0].elapsed_time(e[4]) for e in events), world, device)
     status = _lib.device_status()
     if status:
         raise RuntimeError(f"a bounded device-side wait ran out (status {status:#x}); the timing is invalid")
 
     # ---- end-to-end arm: host buffers in, host buffers out ------------------------------------------------
-    pinned_in = [t.pin_memory() for t in (q_h, k_h, v_h, do_h)]
-    pinned_out = [torch.empty(q_h.shape, dtype=torch.bfloat16).pin_memory() for _ in range(4 if w["backward"] else 1)]
-    h2d = sum(t.numel() * t.element_size() for t in (pinned_in if w["backward"] else pinned_in[:3]))
+    host_in = [q_h, k_h, v_h] + ([do_h] if w["backward"] else []) + list(sel_h)
+    pinned_in = [t.pin_memory() for t in host_in]
+    n_main = 4 if w["backward"] else 3
+    out_shapes = [q_h.shape] * (4 if w["backward"] else 1) + ([sel_h[0].shape] * 2 if sel_h and w["backward"] else [])
+    pinned_out = [torch.empty(shape, dtype=torch.bfloat16).pin_memory() for shape in out_shapes]
+    h2d = sum(t.numel() * t.element_size() for t in pinned_in)
     d2h = sum(t.numel() * t.element_size() for t in pinned_out)
 
     # Every step copies its own inputs in and its own results out; the copies of neighbouring steps run on
@@ -274,8 +393,7 @@ def run_ours(args, w, rank, world, device):
     # or training loop that feeds the operator from host memory would arrange it.
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
     s_comp = torch.cuda.current_stream(device)
-    n_in = 4 if w["backward"] else 3
-    dev_in = [[torch.empty_like(t, device=device) for t in pinned_in[:n_in]] for _ in range(2)]
+    dev_in = [[torch.empty_like(t, device=device) for t in pinned_in] for _ in range(2)]
     uploaded = [torch.cuda.Event() for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
     downloaded = torch.cuda.Event()
@@ -290,15 +408,21 @@ def run_ours(args, w, rank, world, device):
             uploaded[slot].record(s_in)
         s_comp.wait_event(uploaded[slot])
         qd, kd, vd = (t.detach() for t in dev_in[slot][:3])
+        sd = tuple(t.detach() for t in dev_in[slot][n_main:])
         if w["backward"]:
             dd = dev_in[slot][3].float()
-            qd.requires_grad_(True); kd.requires_grad_(True); vd.requires_grad_(True)
-            out = kernels.selective_attention(qd, kd, vd)
+            for t in (qd, kd, vd) + sd:
+                t.requires_grad_(True)
+            out = operator(qd, kd, vd, sd)
             out.backward(dd)
-            results = (out.detach().to(torch.bfloat16), qd.grad, kd.grad, vd.grad)
+            results = [out.detach().to(torch.bfloat16), qd.grad, kd.grad, vd.grad]
+            if sd:
+                flat = reduce_selector_grads(sd)
+                half = flat.numel() // 2
+                results += [flat[:half].to(torch.bfloat16).view(sd[0].shape), flat[half:].to(torch.bfloat16).view(sd[1].shape)]
         else:
             with torch.no_grad():
-                results = (kernels.selective_attention_forward(qd, kd, vd).to(torch.bfloat16),)
+                results = [kernels.selective_attention_forward(qd, kd, vd, selector=sd or None).to(torch.bfloat16)]
         consumed[slot].record(s_comp)
         done = torch.cuda.Event()
         done.record(s_comp)
@@ -309,48 +433,75 @@ def run_ours(args, w, rank, world, device):
                 dst.copy_(src, non_blocking=True)
             downloaded.record(s_out)
 
-    e2e_steps = max(2, min(args.steps, 6))
     for i in range(2):
         e2e_step(i)
     barrier()
     s0 = torch.cuda.Event(enable_timing=True); s1 = torch.cuda.Event(enable_timing=True)
     s0.record(s_in)
-    for i in range(e2e_steps):
+    for i in range(args.steps):
         e2e_step(i)
     s_comp.wait_event(downloaded)
     s1.record(s_comp)
     barrier()
-    e2e_ms = max_over_ranks(s0.elapsed_time(s1) / e2e_steps, world, device)
+    e2e_ms = max_over_ranks(s0.elapsed_time(s1) / args.steps, world, device)
+
+    # the copies alone (no compute between them): the host-side ceiling of this rank's end-to-end step
+    def copies_only():
+        with torch.cuda.stream(s_in):
+            for dst, src in zip(dev_in[0], pinned_in):
+                dst.copy_(src, non_blocking=True)
+        with torch.cuda.stream(s_out):
+            for dst in pinned_out:
+                dst.copy_(dev_in[1][0].view(-1)[:dst.numel()].view(dst.shape), non_blocking=True)
+    copies_only()
+    barrier()
+    c0 = torch.cuda.Event(enable_timing=True); c1 = torch.cuda.Event(enable_timing=True); c2 = torch.cuda.Event(enable_timing=True); c3 = torch.cuda.Event(enable_timing=True)
+    c0.record(s_in); c2.record(s_out)
+    for _ in range(3):
+        copies_only()
+    c1.record(s_in); c3.record(s_out)
+    barrier()
+    h2d_gbs = 3 * h2d / (c0.elapsed_time(c1) * 1e-3) / 1e9
+    d2h_gbs = 3 * d2h / (c2.elapsed_time(c3) * 1e-3) / 1e9
 
     ms_per_step = total_ms / args.steps
-    value = whole_job_tokens_per_second(tokens, world, ms_per_step)
+    value = whole_job_tokens_per_second(tokens, ms_per_step)
     peak, peak_kind = measured_peaks()
-    kflops = flops["backward"] if w["backward"] else flops["forward"]
+    share = (len(plan["seqs"]) * len(plan["heads"])) / (w["batch"] * w["heads"])      # this rank's part of the batch
+    kflops = (flops["backward"] if w["backward"] else flops["forward"]) * share
     kernel_avg_ms = sum(kernel_ms) / max(len(kernel_ms), 1)
     achieved = kflops / (kernel_avg_ms * 1e-3) / 1e12 if kernel_ms else None
-    head_tiles = w["batch"] * w["heads"] * (math.ceil(w["seq"] / 128) * (math.ceil(w["seq"] / 128) + 1) // 2)
+    ntile = math.ceil(w["seq"] / 128)
+    head_tiles = len(plan["seqs"]) * len(plan["heads"]) * (ntile * (ntile + 1) // 2)
+    per_tile = captured_traffic_per_head_tile(dominant)
+    step_flops = (flops["forward"] + flops["backward"]) * (world if plan["scaling"] == "weak" else 1)
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak",
+        "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": plan["scaling"],
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"{args.workload}: selective attention fwd{'+bwd' if w['backward'] else ''} B={w['batch']} "
                                f"H={w['heads']} T={w['seq']} D={w['dim']} bf16, "
-                               f"{'per-head' if w['per_head'] else 'shared head-0'} selection, per GPU",
-                   "l2": "inputs (q, k, v, dO) exceed the 126 MB L2; no explicit flush",
+                               f"{'per-head' if w['per_head'] else 'shared head-0'} selection, "
+                               f"{'whole batch per GPU' if plan['scaling'] == 'weak' else 'one batch over all GPUs'}",
+                   "parallelism": plan["parallelism"],
+                   "rank0_shard": f"sequences {plan['seqs'].start}..{plan['seqs'].stop - 1}, heads {plan['heads'].start}..{plan['heads'].stop - 1}",
+                   "l2": "inputs (q, k, v, dO) of every rank exceed the 126 MB L2; no explicit flush",
                    "engine": "tcgen05", "fwd_ms": fwd_ms / args.steps, "bwd_ms": bwd_ms / args.steps,
-                   "algorithmic_tflop_per_step": (flops["forward"] + flops["backward"]) / 1e12,
-                   "attention_only_tflop_per_step": flops["attention_only"] / 1e12,
-                   "step_tflops": (flops["forward"] + flops["backward"]) / (ms_per_step * 1e-3) / 1e12,
-                   "frac_of_nominal_2250": (flops["forward"] + flops["backward"]) / (ms_per_step * 1e-3) / 1e12
-                                           / NOMINAL_BF16_TFLOPS},
-        "e2e": {"value": whole_job_tokens_per_second(tokens, world, e2e_ms), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
-                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": e2e_steps},
-        "gpu_launches": args.steps * (7 if w["backward"] else 3),
+                   "selector_grad_allreduce_ms": reduce_ms / args.steps if sel else None,
+                   "selector_grad_allreduce_bytes": (2 * sel[0].numel() * 4) if sel else 0,
+                   "algorithmic_tflop_per_step": step_flops / 1e12,
+                   "attention_only_tflop_per_step": flops["attention_only"] * (world if plan["scaling"] == "weak" else 1) / 1e12,
+                   "step_tflops_per_gpu": step_flops / world / (ms_per_step * 1e-3) / 1e12,
+                   "frac_of_nominal_2250_per_gpu": step_flops / world / (ms_per_step * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS,
+                   "host_affinity": affinity},
+        "e2e": {"value": whole_job_tokens_per_second(tokens, e2e_ms), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
+                "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.steps,
+                "copies_alone_gbs": {"h2d": h2d_gbs, "d2h": d2h_gbs}, "bytes_are": "per rank"},
+        "gpu_launches": launches,
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": (achieved / peak) if achieved else None, "peak_kind": peak_kind,
                      "launch_ms": kernel_avg_ms, "launches_timed": len(kernel_ms),
-                     "traffic": (BACKWARD_DRAM_TRAFFIC_PER_HEAD_TILE * head_tiles
-                                 if BACKWARD_DRAM_TRAFFIC_PER_HEAD_TILE and w["backward"] else None)},
+                     "traffic": (per_tile * head_tiles) if per_tile else None},
         "clocks": sampler.summary(),
     }
     return line
@@ -388,6 +539,7 @@ def run_decode(args, w, rank, world, device):
             torch.distributed.barrier()
         torch.cuda.synchronize()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        before = _lib.launch_count()
         with ClockSampler(device.index) as sampler:
             e0.record()
             for _ in range(args.steps):
@@ -398,11 +550,12 @@ def run_decode(args, w, rank, world, device):
         if not host:
             _lib.profile_enable("none")
             clocks = sampler.summary()
+            launches = _lib.launch_count() - before
     algorithmic_bytes = 2 * b * h * (t + 1) * d * 2 + b * (t + 1) * 8       # K and V once, `selected` read + written
-    hbm_peak = 6550.1
+    hbm_peak, hbm_kind = 6650.0, "fallback"
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
-        hbm_peak = float(json.load(open(path))["hbm_gbs"])
+        hbm_peak, hbm_kind = float(json.load(open(path))["hbm_gbs"]), "measured (device copy)"
     achieved = algorithmic_bytes / (results[False] * 1e-3) / 1e9
     return {"metric": "selective-attn cached decode steps/s (batch tokens/s) @131K-token cache bf16", "value":
             world * b / (results[False] * 1e-3), "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
@@ -412,9 +565,9 @@ def run_decode(args, w, rank, world, device):
                        "l2": "the K and V cache (512 MiB) exceeds the 126 MB L2"},
             "e2e": {"value": world * b / (results[True] * 1e-3), "unit": "tokens/s", "ms_per_step": results[True],
                     "h2d_bytes_per_step": 3 * b * h * d * 2, "d2h_bytes_per_step": b * h * d * 4},
-            "gpu_launches": 4 * args.steps,
+            "gpu_launches": launches,
             "roofline": {"bound": "hbm", "kernel": "decode step (append, attend, combine, update)", "achieved": achieved,
-                         "peak": hbm_peak, "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None},
+                         "peak": hbm_peak, "peak_kind": hbm_kind, "unit": "GB/s", "frac": achieved / hbm_peak, "traffic": None},
             "clocks": clocks}
 
 
@@ -423,6 +576,7 @@ def run_decoder(args, w, rank, world, device):
     signal, vocab 50304, T = 16384, bf16 autocast, fused AdamW): forward, backward, optimizer step.  Data
     parallel: one sequence per GPU, gradients all-reduced by DistributedDataParallel (NCCL, bucketed and
     overlapped with the backward)."""
+    from selective_attention_b200 import _lib
     from selective_attention_b200.decoder import SelectiveDecoder, synthetic_batch
 
     torch.manual_seed(0)
@@ -461,6 +615,7 @@ def run_decoder(args, w, rank, world, device):
         torch.cuda.synchronize()
         e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
         n_steps = args.steps if not host else max(1, min(args.steps, 3))
+        before = _lib.launch_count()
         with ClockSampler(device.index) as sampler:
             e0.record()
             for _ in range(n_steps):
@@ -472,12 +627,12 @@ def run_decoder(args, w, rank, world, device):
         times[host] = max_over_ranks(e0.elapsed_time(e1) / n_steps, world, device)
         if not host:
             clocks, last_loss = sampler.summary(), float(loss.detach())
+            launches = _lib.launch_count() - before
     if not math.isfinite(last_loss):
         raise RuntimeError("the training loss is not finite")
     tokens = w["batch"] * w["seq"]
-    attn_launches = 7 * w["layers"]
     return {"metric": "decoder training step tokens/s (24L d1024 16x64, T=16384, bf16, selective attention)",
-            "value": whole_job_tokens_per_second(tokens, world, times[False]), "unit": "tokens/s", "n_gpus": world,
+            "value": whole_job_tokens_per_second(tokens * world, times[False]), "unit": "tokens/s", "n_gpus": world,
             "steps": args.steps, "warmup": args.warmup, "ms_per_step": times[False], "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {"workload": f"c5: decoder training step, {w['layers']} layers, d_model {w['heads'] * w['dim']}, "
@@ -485,65 +640,160 @@ def run_decoder(args, w, rank, world, device):
                                    f"T={w['seq']}, {w['batch']} sequence(s) per GPU, AdamW, grad clip 1.0",
                        "parameters": params, "parallelism": f"dp{world}", "loss": last_loss,
                        "l2": "activations and weights far exceed the 126 MB L2"},
-            "e2e": {"value": whole_job_tokens_per_second(tokens, world, times[True]), "unit": "tokens/s",
+            "e2e": {"value": whole_job_tokens_per_second(tokens * world, times[True]), "unit": "tokens/s",
                     "ms_per_step": times[True], "h2d_bytes_per_step": 2 * tokens * 8, "d2h_bytes_per_step": 4},
-            "gpu_launches": attn_launches * args.steps, "clocks": clocks}
+            "gpu_launches": launches, "clocks": clocks}
+
+
+REF_DIR = os.path.join(ROOT, "baseline", "_ref")
+
+
+def reference_listing():
+    """The reference's own dense implementation of the operator (its ``selective_attention_reference``) from the
+    installed copy under baseline/_ref, or None where that copy is absent (then the CPU oracle port stands in)."""
+    if not os.path.isdir(os.path.join(REF_DIR, "selective_attention")):
+        return None
+    if REF_DIR not in sys.path:
+        sys.path.append(REF_DIR)
+    try:
+        from selective_attention.kernels import selective_attention_reference
+        return selective_attention_reference
+    except Exception:
+        return None
+
+
+def _listing_fwd_bwd(listing, q, k, v, w):
+    """One forward + backward on the CPU: autograd through the reference's listing, or the oracle port."""
+    if listing is not None:
+        qq, kk, vv = (t.clone().requires_grad_(True) for t in (q, k, v))
+        listing(qq, kk, vv).backward(w)
+        return
+    import selective_oracle as oracle
+    if q.shape[2] > 4096:
+        for b in range(q.shape[0]):
+            oracle.sequence_fwd_bwd(q[b], k[b], v[b], w[b], head_chunk=1)
+    else:
+        oracle.attention_grads(q, k, v, w)
 
 
 def cpu_baseline(seconds: float = 12.0) -> dict:
-    """The CPU oracle (a port of the reference's paper listing and its backward algebra) on the
-    reference's own CPU-sized case: B=2, H=4, T=1024, D=64, fp32, seed 0."""
-    import selective_oracle as oracle
-
+    """The reference's CPU implementation (or the oracle port of it) on the reference's own CPU-sized case:
+    B=2, H=4, T=1024, D=64, fp32, seed 0."""
+    listing = reference_listing()
     g = torch.Generator("cpu").manual_seed(0)
     q, k, v, w = (torch.randn(2, 4, 1024, 64, generator=g) for _ in range(4))
-    oracle.attention_grads(q, k, v, w)
+    _listing_fwd_bwd(listing, q, k, v, w)
     reps, t0 = 0, time.perf_counter()
     while time.perf_counter() - t0 < seconds:
-        oracle.attention_grads(q, k, v, w)
+        _listing_fwd_bwd(listing, q, k, v, w)
         reps += 1
     dt = (time.perf_counter() - t0) / reps
-    return {"value": 2 * 1024 / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"oracle fwd+bwd at B=2 H=4 T=1024 D=64 fp32 (the reference's CPU case), {reps} passes, "
-                      f"{dt * 1e3:.1f} ms each"}
+    kind = "reference" if listing is not None else "port"
+    return {"value": 2 * 1024 / dt, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
+            "sample": f"{'reference listing + autograd' if listing else 'oracle'} fwd+bwd at B=2 H=4 T=1024 D=64 fp32 "
+                      f"(the reference's CPU case), {reps} passes, {dt * 1e3:.1f} ms each"}
+
+
+def reference_on_gpu(args, w, device) -> dict:
+    """The reference's own Triton kernels (installed copy, unmodified) on this GPU at the workload's full
+    configuration, timed like the product arm (CUDA events, same warm-up and steps)."""
+    try:
+        if REF_DIR not in sys.path:
+            sys.path.append(REF_DIR)
+        from selective_attention import kernels as ref
+        if not ref.HAS_TRITON:
+            return {"unavailable": "triton is not importable"}
+        torch.cuda.set_device(device)
+        q, k, v, d_out = (t.to(device) for t in make_inputs(w, seed=0))
+        if w["per_head"]:
+            q, k, v, d_out = (t.reshape(-1, 1, t.shape[2], t.shape[3]) for t in (q, k, v, d_out))
+        d_out = d_out.float()
+        for t in (q, k, v):
+            t.requires_grad_(w["backward"])
+
+        def step():
+            if w["backward"]:
+                ref.selective_attention(q, k, v).backward(d_out)
+                q.grad = k.grad = v.grad = None
+            else:
+                with torch.no_grad():
+                    ref.selective_attention_forward(q, k, v, return_aux=True)
+
+        for _ in range(max(args.warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        e0 = torch.cuda.Event(enable_timing=True); e1 = torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / args.steps
+        return {"value": w["batch"] * w["seq"] / (ms * 1e-3), "unit": "tokens/s", "ms_per_step": ms,
+                "what": "the reference's Triton kernels through its selective_attention(), unmodified, on this GPU; "
+                        "same shapes, dtype and inputs as the product arm, inputs resident in HBM"}
+    except Exception as exc:                                     # a Triton build that cannot target this GPU, etc.
+        return {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
 
 
 def run_reference(args, w):
-    """The reference's algorithm on the host CPU: the oracle port (the reference itself is a Python
-    package that does not travel with this repository).  Each step is one sequence of the workload
-    restricted to 2 of its heads (head 0, the selector, and one more) at the full sequence length;
-    per-head work is equal, so the full-sequence time is the sample's time x heads / 2."""
-    import selective_oracle as oracle
-
+    """The reference's CPU implementation of the operator on the host cores.  Each step is one sequence of the
+    workload restricted to 2 of its heads (head 0, the selector, and one more) at a sample length T_s chosen so
+    that the whole run stays within a few minutes; per-head work is equal and the work per head grows with the
+    causal pairs T (T + 1) / 2, so the full workload's time is the sample's time x heads / 2 x pairs(T) / pairs(T_s)."""
     torch.set_num_threads(os.cpu_count() or 1)       # torchrun sets OMP_NUM_THREADS=1; this arm runs on rank 0 alone
+    listing = reference_listing()
     heads_sample = min(2, w["heads"])
-    seq = w["seq"]
     g = torch.Generator("cpu").manual_seed(0)
-    q, k, v, d = (torch.randn(heads_sample, seq, w["dim"], generator=g).bfloat16().float() for _ in range(4))
 
-    def one():
+    def sample(seq):
+        return tuple(torch.randn(1, heads_sample, seq, w["dim"], generator=g).bfloat16().float() for _ in range(4))
+
+    def one(q, k, v, d):
         if w["backward"]:
-            oracle.sequence_fwd_bwd(q, k, v, d, head_chunk=1)
+            _listing_fwd_bwd(listing, q, k, v, d)
+        elif listing is not None:
+            with torch.no_grad():
+                listing(q, k, v)
         else:
-            oracle.tail_rows(q[None], k[None], v[None], tail=min(4096, seq), chunk=4096)
+            import selective_oracle as oracle
+            oracle.tail_rows(q, k, v, tail=q.shape[2], chunk=4096)
 
+    # calibrate on a short sequence, then take the longest sample length that keeps the run under ~3 minutes
+    probe = sample(min(2048, w["seq"]))
+    one(*probe)
+    t0 = time.perf_counter()
+    one(*probe)
+    per_pair = (time.perf_counter() - t0) / pairs(probe[0].shape[2])
+    seq_s = w["seq"]
+    steps_total = args.steps + min(args.warmup, 1)
+    avail = 0.45 * (os.sysconf("SC_PAGE_SIZE") * os.sysconf("SC_PHYS_PAGES"))
+    while seq_s > 2048 and (per_pair * pairs(seq_s) * steps_total > 180.0 or 14 * heads_sample * seq_s * seq_s * 4 > avail):
+        seq_s //= 2
+    q, k, v, d = sample(seq_s)
     for _ in range(min(args.warmup, 1)):
-        one()
+        one(q, k, v, d)
     t0 = time.perf_counter()
     for _ in range(args.steps):
-        one()
+        one(q, k, v, d)
     dt = (time.perf_counter() - t0) / args.steps
-    scale = w["heads"] / heads_sample if w["backward"] else w["heads"] / heads_sample * seq / min(4096, seq)
-    value = seq / (dt * scale)
-    sample = (f"1 sequence x {heads_sample} of {w['heads']} heads at T={seq}, D={w['dim']}, "
-              f"{'fwd+bwd' if w['backward'] else 'last 4096 query rows, forward'}; {dt:.2f} s per step, scaled x{scale:g}")
-    return {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
+    scale = w["heads"] / heads_sample * pairs(w["seq"]) / pairs(seq_s)
+    value = w["seq"] / (dt * scale)
+    kind = "reference" if listing is not None else "port"
+    what = ("the reference's selective_attention_reference with autograd (baseline/_ref)" if listing is not None
+            else "CPU oracle port of the reference's listing")
+    smp = (f"{what}: 1 sequence x {heads_sample} of {w['heads']} heads at T_s={seq_s} of T={w['seq']}, D={w['dim']}, "
+           f"{'fwd+bwd' if w['backward'] else 'forward'}; {dt:.2f} s per step, scaled x{scale:g}")
+    line = {"impl": "reference", "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": args.gpus,
             "steps": args.steps, "warmup": min(args.warmup, 1), "ms_per_step": dt * 1e3, "higher_is_better": True,
-            "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": f"{args.workload}: CPU oracle port on a bounded sample"},
-            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": "port",
-                             "sample": sample},
+            "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+            "config": {"workload": f"{args.workload}: the reference's CPU implementation on a bounded sample"},
+            "cpu_baseline": {"value": value, "unit": "tokens/s", "cores": torch.get_num_threads(), "kind": kind,
+                             "sample": smp},
             "e2e": {"value": value, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+    if torch.cuda.is_available() and not args.no_reference_gpu and args.workload in ("c2", "c3", "c4"):
+        line["reference_gpu"] = reference_on_gpu(args, w, torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))))
+    return line
 
 
 def main():
@@ -557,6 +807,10 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="override B (profiling on a small case)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count of the c5 decoder")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-reference-gpu", action="store_true",
+                    help="--impl reference: skip timing the reference's Triton kernels on the GPU")
+    ap.add_argument("--replicas", action="store_true",
+                    help="N > 1: every rank runs its own full batch (weak scaling) instead of a shard of one batch")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 0)
     w = dict(WORKLOADS[args.workload])

@@ -19,7 +19,8 @@ def _rank_main(rank, world, port, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     slowest = bench.max_over_ranks(10.0 + 5.0 * rank, world, torch.device("cpu"))
-    out[rank] = (slowest, bench.whole_job_tokens_per_second(65536, world, slowest))
+    plan = bench.shard_plan(bench.WORKLOADS["c2"], rank, world, replicas=False)
+    out[rank] = (slowest, bench.whole_job_tokens_per_second(plan["tokens"], slowest), list(plan["seqs"]))
     dist.destroy_process_group()
 
 
@@ -28,10 +29,55 @@ def test_two_ranks_report_the_slowest_time_and_the_whole_job_rate():
     out = manager.dict()
     mp.spawn(_rank_main, args=(2, 29731, out), nprocs=2, join=True)
     for rank in (0, 1):
-        slowest, value = out[rank]
+        slowest, value, seqs = out[rank]
         assert slowest == 15.0
-        assert abs(value - 2 * 65536 / 15e-3) < 1e-6
+        assert abs(value - 65536 / 15e-3) < 1e-6            # one batch over both ranks: strong scaling
+        assert seqs == [2 * rank, 2 * rank + 1]
     assert bench.max_over_ranks(7.0, 1, torch.device("cpu")) == 7.0
+
+
+def test_shard_plans_cover_the_batch_exactly_once():
+    c2, c3, c4 = (bench.WORKLOADS[n] for n in ("c2", "c3", "c4"))
+    for w in (c2, c3, c4):
+        for world in (1, 2, 4, 8):
+            if w is c4 and world == 1:
+                continue
+            seen = set()
+            for rank in range(world):
+                plan = bench.shard_plan(w, rank, world, replicas=False)
+                assert plan["scaling"] == "strong" and plan["tokens"] == w["batch"] * w["seq"]
+                assert rank in plan["group"]
+                for b in plan["seqs"]:
+                    for h in plan["heads"]:
+                        assert (b, h) not in seen
+                        seen.add((b, h))
+            assert len(seen) == w["batch"] * w["heads"]
+    eight = [bench.shard_plan(c2, r, 8, replicas=False) for r in range(8)]
+    assert all(p["selector"] and len(p["heads"]) == 8 for p in eight)
+    assert eight[5]["group"] == [4, 5] and list(eight[5]["seqs"]) == [2] and list(eight[5]["heads"]) == list(range(8, 16))
+    assert not bench.shard_plan(c2, 3, 4, replicas=False)["selector"]
+    assert bench.shard_plan(c4, 1, 2, replicas=False)["selector"]                  # B = 1: heads split from 2 GPUs on
+    weak = bench.shard_plan(c2, 1, 4, replicas=True)
+    assert weak["scaling"] == "weak" and weak["tokens"] == 4 * 65536
+
+
+def _selector_rank(rank, world, port, out):
+    """The reduction the head-sharded ranks run on their partial selector gradients, with gloo on the CPU."""
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    g = torch.Generator().manual_seed(5)
+    parts = torch.randn(world, 2, 16, 8, generator=g)            # every rank knows all partial sums (for the check)
+    flat = parts[rank].reshape(-1).clone()
+    dist.all_reduce(flat)
+    out[rank] = bool(torch.allclose(flat.view(2, 16, 8), parts.sum(0), atol=1e-6))
+    dist.destroy_process_group()
+
+
+def test_partial_selector_gradients_sum_across_two_ranks():
+    manager = mp.Manager()
+    out = manager.dict()
+    mp.spawn(_selector_rank, args=(2, 29733, out), nprocs=2, join=True)
+    assert out[0] and out[1]
 
 
 def test_algorithmic_flops_match_the_counted_figures():
@@ -56,4 +102,4 @@ def test_reference_arm_prints_one_line_on_rank_zero_only():
     assert first.returncode == 0, first.stderr
     line = json.loads(first.stdout.strip().splitlines()[-1])
     assert line["impl"] == "reference" and line["unit"] == "tokens/s" and line["value"] > 0
-    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["cpu_baseline"]["kind"] == "port"
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["cpu_baseline"]["kind"] in ("port", "reference")
