@@ -249,9 +249,10 @@ def shard_plan(w: dict, rank: int, world: int, replicas: bool) -> dict:
                 parallelism=f"batch split {b} ways x heads split {share} ways (selector replicated, its gradient all-reduced)")
 
 
-def bind_near_gpu(device_index: int, local_rank: int, local_world: int) -> str:
-    """Pins this process to a slice of the CPU cores nearest its GPU, before any pinned buffer is allocated, so the
-    host side of every copy stays on that GPU's NUMA node and ranks do not share cores."""
+def bind_near_gpu(device_index: int) -> str:
+    """Restricts this process to the CPU cores of its GPU's NUMA node, before any pinned buffer is allocated, so
+    the host side of every copy stays on that node.  (The whole node, not a slice of it: on a shared host a
+    fixed slice can coincide with cores another job keeps busy, which starves a rank's launch thread.)"""
     try:
         props = torch.cuda.get_device_properties(device_index)
         bus = f"{props.pci_domain_id:04x}:{props.pci_bus_id:02x}:{props.pci_device_id:02x}.0"
@@ -262,12 +263,10 @@ def bind_near_gpu(device_index: int, local_rank: int, local_world: int) -> str:
             lo, _, hi = part.partition("-")
             cores.extend(range(int(lo), int(hi or lo) + 1))
         allowed = sorted(set(cores) & set(os.sched_getaffinity(0)))
-        if len(allowed) < local_world:
-            return f"unbound ({len(allowed)} local cores)"
-        per = len(allowed) // local_world
-        mine = allowed[local_rank * per:(local_rank + 1) * per]
-        os.sched_setaffinity(0, mine)
-        return f"cores {mine[0]}-{mine[-1]} of local list {text}"
+        if not allowed:
+            return "unbound (no local core is allowed)"
+        os.sched_setaffinity(0, allowed)
+        return f"{len(allowed)} cores of the GPU's local list {text}"
     except (OSError, ValueError, AttributeError) as exc:
         return f"unbound ({type(exc).__name__})"
 
@@ -285,7 +284,7 @@ def run_ours(args, w, rank, world, device):
     if not kernels.HAS_KERNELS:
         raise RuntimeError("the CUDA library is missing; build it first (python __graft_entry__.py)")
     plan = shard_plan(w, rank, world, args.replicas)
-    affinity = bind_near_gpu(device.index, int(os.environ.get("LOCAL_RANK", "0")), int(os.environ.get("LOCAL_WORLD_SIZE", str(world))))
+    affinity = bind_near_gpu(device.index)
     # The full synthetic batch is generated from one seed and every rank slices its shard (replicas: own seed).
     full = make_inputs(w, seed=rank if plan["scaling"] == "weak" and world > 1 else 0)
     sl = (slice(plan["seqs"].start, plan["seqs"].stop), slice(plan["heads"].start, plan["heads"].stop))
@@ -374,7 +373,14 @@ def run_ours(args, w, rank, world, device):
     fwd_ms = sum(e[0].elapsed_time(e[1]) for e in events)
     bwd_ms = sum(e[1].elapsed_time(e[2]) for e in events)
     reduce_ms = sum(e[2].elapsed_time(e[3]) for e in events)
-    total_ms = max_over_ranks(sum(e[0].elapsed_time(e[4]) for e in events), world, device)
+    own_ms = sum(e[0].elapsed_time(e[4]) for e in events)
+    total_ms = max_over_ranks(own_ms, world, device)
+    per_rank = None
+    if world > 1:                        # every rank's own split of a step, for the record
+        mine = torch.tensor([fwd_ms, bwd_ms, reduce_ms, own_ms], dtype=torch.float64, device=device) / args.steps
+        gathered = [torch.zeros_like(mine) for _ in range(world)]
+        torch.distributed.all_gather(gathered, mine)
+        per_rank = [[round(float(x), 3) for x in g] for g in gathered]
     status = _lib.device_status()
     if status:
         raise RuntimeError(f"a bounded device-side wait ran out (status {status:#x}); the timing is invalid")
@@ -487,13 +493,13 @@ def run_ours(args, w, rank, world, device):
                    "rank0_shard": f"sequences {plan['seqs'].start}..{plan['seqs'].stop - 1}, heads {plan['heads'].start}..{plan['heads'].stop - 1}",
                    "l2": "inputs (q, k, v, dO) of every rank exceed the 126 MB L2; no explicit flush",
                    "engine": "tcgen05", "fwd_ms": fwd_ms / args.steps, "bwd_ms": bwd_ms / args.steps,
-                   "selector_grad_allreduce_ms": reduce_ms / args.steps if sel else None,
-                   "selector_grad_allreduce_bytes": (2 * sel[0].numel() * 4) if sel else 0,
+                   "selector_grad_allreduce_ms": reduce_ms / args.steps if (sel and w["backward"]) else None,
+                   "selector_grad_allreduce_bytes": (2 * sel[0].numel() * 4) if (sel and w["backward"]) else 0,
                    "algorithmic_tflop_per_step": step_flops / 1e12,
                    "attention_only_tflop_per_step": flops["attention_only"] * (world if plan["scaling"] == "weak" else 1) / 1e12,
                    "step_tflops_per_gpu": step_flops / world / (ms_per_step * 1e-3) / 1e12,
                    "frac_of_nominal_2250_per_gpu": step_flops / world / (ms_per_step * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS,
-                   "host_affinity": affinity},
+                   "per_rank_ms_fwd_bwd_allreduce_step": per_rank, "host_affinity": affinity},
         "e2e": {"value": whole_job_tokens_per_second(tokens, e2e_ms), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.steps,
                 "copies_alone_gbs": {"h2d": h2d_gbs, "d2h": d2h_gbs}, "bytes_are": "per rank"},
