@@ -25,6 +25,8 @@
 // MMAs: dK += (dz + g)^T Q and dQ = (dz + g) K.  40 MMAs per query tile instead of 64, no Q0 / K0 tiles, one
 // read-out per tile.
 // Reference for the arithmetic: src/selective_attention/kernels.py:196-268.
+#include <stdlib.h>
+
 #include "sa_tc_host.cuh"
 #include "sa_tc_ptx.cuh"
 
@@ -556,9 +558,15 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 
 }  // namespace
 
+int backward_shared(const Problem& p, const float* lse2, const float* carry, const float* dbar, const void* d_out_bf16,
+                    float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv, cudaStream_t s);
+
 int backward(const Problem& p, const float* lse2, const float* carry, const float* dbar, const void* d_out_bf16,
              float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv, cudaStream_t s) {
   if (p.head_dim != 64) return SA_ERR_UNSUPPORTED;
+  // A selector shared by the heads: the form with two sets of score columns (sa_tc_bwd_shared.cu).
+  if (!((p.heads == 1) && !p.external_selector) && getenv("SA_B200_BWD_SINGLE_SET") == nullptr)
+    return backward_shared(p, lse2, carry, dbar, d_out_bf16, dq_acc, dk_acc, dq0, dk0, dv, s);
   const int ntiles = (p.seq + kTile - 1) / kTile;
   const int nrows = p.batch * p.heads;
   CUtensorMap map_q, map_k, map_v, map_do, map_dq, map_dq0;
