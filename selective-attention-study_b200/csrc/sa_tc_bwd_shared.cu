@@ -256,9 +256,11 @@ __global__ void __launch_bounds__(kThreads, 1) backward_shared_kernel(
     int ntiles, int exempt, float scale, WaitCtx status) {
   using L = Smem;
   constexpr int D = 64;
-  const int nrows = gridDim.x / ntiles;                  // batch * heads
-  const int nj = (int)(blockIdx.x / nrows);              // key tiles with the most query tiles first
-  const int n = blockIdx.x % nrows;
+  // One (batch, head) row after the other, and within a row the key tiles with the most query tiles first: the CTAs
+  // resident at one time belong to one or two rows and walk the same query tiles from the last one down, so every
+  // Q, Q0, dO tile is fetched from DRAM once and then served from L2 to the row's other CTAs.
+  const int n = (int)(blockIdx.x / ntiles);
+  const int nj = (int)(blockIdx.x % ntiles);
   const int b = n / heads, h = n - b * heads;
   const int n_iter = ntiles - nj;
   const int n_half = 2 * n_iter;
