@@ -78,6 +78,17 @@ typedef struct sa_selector {
   int64_t k0_stride[2];
 } sa_selector;
 
+/* A tensor in the caller's own layout, for the layout-fused entry points: rows of head_dim contiguous elements
+ * whose starts are given by batch / head / token strides (in elements), e.g. the (batch, seq, heads, head_dim)
+ * view of a model's (batch, seq, heads * head_dim) activation, or the q / k / v slots of a fused
+ * (batch, seq, 3, heads, head_dim) projection gradient. */
+typedef struct sa_tensor {
+  void* ptr;             /* 16-byte aligned                                                            */
+  int32_t dtype;         /* sa_dtype; must equal p->dtype                                              */
+  int32_t reserved;      /* 0                                                                          */
+  int64_t stride[3];     /* batch, head, token strides in elements; each a multiple of 16 bytes        */
+} sa_tensor;
+
 /* Library / build identification. */
 int sa_abi_version(void);
 const char* sa_status_string(int status);
@@ -128,6 +139,16 @@ int sa_forward_selector(const sa_problem* p, const void* q, const void* k, const
  *   total  (batch, seq) fp32 */
 int sa_selection_carry(const sa_problem* p, const void* q, const void* k, const sa_selector* sel,
                        float* carry, float* total, void* stream);
+
+/* Layout-fused forward (tensor-core engine).  As sa_forward_selector, and in the same launch the output is ALSO
+ * written in the operand dtype at the rows `out_lowp` names, so the caller's next GEMM reads it in place.
+ * Replaces what the reference's layer does after the kernel: the `.to(v.dtype)` pass over the fp32 output
+ * (src/selective_attention/mixers.py:94) and the transpose-and-copy of _merge_heads
+ * (src/selective_attention/model.py:69-71).  out_lowp == NULL: identical to sa_forward_selector. */
+int sa_forward_fused(const sa_problem* p, const void* q, const void* k, const void* v,
+                     const sa_selector* sel,
+                     float* out, const sa_tensor* out_lowp, float* lse2, float* carry, float* total,
+                     void* stream);
 
 /* Forward for callers that must not allocate.  It has no counterpart in the reference (whose forward
  * allocates its CARRY scratch with torch on every call, src/selective_attention/kernels.py:573-580).
@@ -188,6 +209,19 @@ int sa_backward_selector(const sa_problem* p, const void* q, const void* k, cons
                          const void* d_out, int d_out_dtype,
                          void* dq, void* dk, void* dv, float* dq0, float* dk0,
                          void* workspace, size_t workspace_bytes, void* stream);
+
+/* Layout-fused backward (tensor-core engine).  As sa_backward_selector, with the cotangent read from, and the
+ * three gradients written to, tensors in the caller's layout (element type p->dtype): d_out is typically the
+ * (batch, seq, heads, head_dim) view of the gradient of the merged activation, dq / dk / dv the three slots of
+ * the fused projection's gradient.  Replaces the `.contiguous()` copy of the cotangent
+ * (src/selective_attention/kernels.py:632-635) and the copies autograd makes to scatter dq / dk / dv back through
+ * _split_heads (src/selective_attention/model.py:59-67). */
+int sa_backward_fused(const sa_problem* p, const void* q, const void* k, const void* v,
+                      const sa_selector* sel,
+                      const float* out, const float* lse2, const float* carry,
+                      const sa_tensor* d_out,
+                      const sa_tensor* dq, const sa_tensor* dk, const sa_tensor* dv, float* dq0, float* dk0,
+                      void* workspace, size_t workspace_bytes, void* stream);
 
 /* Bytes of scratch sa_decode_step needs: per-split partial sums, the step's new selection values and the
  * tickets with which the last CTA of a row / key range is found.  Contents undefined on entry and exit; two

@@ -73,6 +73,9 @@ int to_problem(const sa_problem* in, const void* q, const void* k, const void* v
   p->q = Strided{q, in->q_stride[0], in->q_stride[1], in->q_stride[2]};
   p->k = Strided{k, in->k_stride[0], in->k_stride[1], in->k_stride[2]};
   p->v = Strided{v, in->v_stride[0], in->v_stride[1], in->v_stride[2]};
+  p->out_lowp = nullptr;
+  p->out_lowp_rows = contiguous_rows(in->heads, in->seq, in->head_dim);
+  p->dv_rows = contiguous_rows(in->heads, in->seq, in->head_dim);
   p->external_selector = (sel != nullptr);
   if (sel != nullptr) {
     p->q0 = Strided{sel->q0, sel->q0_stride[0], 0, sel->q0_stride[1]};
@@ -160,12 +163,39 @@ int sa_carry_checkpoints(int engine, int seq) {
   return 0;
 }
 
+namespace {
+// A caller-layout tensor of the layout-fused entry points: element type of the problem, 16-byte aligned rows.
+int rows_of(const sa_tensor* t, int dtype, RowLayout* rows) {
+  if (t == nullptr || t->ptr == nullptr || t->dtype != dtype) return SA_ERR_BAD_ARGUMENT;
+  const int64_t es = (dtype == SA_F32) ? 4 : 2;
+  if ((reinterpret_cast<uintptr_t>(t->ptr) & 15) != 0) return SA_ERR_ALIGNMENT;
+  for (int i = 0; i < 3; ++i)
+    if ((t->stride[i] * es) & 15) return SA_ERR_ALIGNMENT;
+  *rows = RowLayout{t->stride[0], t->stride[1], t->stride[2]};
+  return SA_OK;
+}
+}  // namespace
+
+int sa_forward_fused(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
+                     float* out, const sa_tensor* out_lowp, float* lse2, float* carry, float* total, void* stream);
+
 int sa_forward_selector(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
                         float* out, float* lse2, float* carry, float* total, void* stream) {
+  return sa_forward_fused(in, q, k, v, sel, out, nullptr, lse2, carry, total, stream);
+}
+
+int sa_forward_fused(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
+                     float* out, const sa_tensor* out_lowp, float* lse2, float* carry, float* total, void* stream) {
   Problem p;
   int st = to_problem(in, q, k, v, sel, &p);
   if (st != SA_OK) return st;
   if (!q || !k || !v || !out || !lse2 || !carry || !total) return SA_ERR_BAD_ARGUMENT;
+  if (out_lowp != nullptr) {
+    if (in->engine != SA_ENGINE_TCGEN05) return SA_ERR_UNSUPPORTED;
+    st = rows_of(out_lowp, in->dtype, &p.out_lowp_rows);
+    if (st != SA_OK) return st;
+    p.out_lowp = out_lowp->ptr;
+  }
   if (tc::timeout_pending()) return SA_ERR_DEVICE_TIMEOUT;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   if (in->engine == SA_ENGINE_SIMT) return simt_forward(p, out, lse2, carry, total, s);
@@ -246,13 +276,47 @@ size_t sa_backward_workspace_bytes(const sa_problem* in) {
   return carve(in).total;
 }
 
+namespace {
+int backward_common(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
+                    const float* out, const float* lse2, const float* carry, const void* d_out, int d_out_dtype,
+                    const RowLayout* d_out_rows, void* dq, void* dk, void* dv, const RowLayout* dq_rows,
+                    const RowLayout* dk_rows, const RowLayout* dv_rows, float* dq0_out, float* dk0_out, void* workspace,
+                    size_t workspace_bytes, void* stream);
+}  // namespace
+
 int sa_backward_selector(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
                          const float* out, const float* lse2, const float* carry, const void* d_out, int d_out_dtype,
                          void* dq, void* dk, void* dv, float* dq0_out, float* dk0_out, void* workspace,
                          size_t workspace_bytes, void* stream) {
+  return backward_common(in, q, k, v, sel, out, lse2, carry, d_out, d_out_dtype, nullptr, dq, dk, dv, nullptr, nullptr,
+                         nullptr, dq0_out, dk0_out, workspace, workspace_bytes, stream);
+}
+
+int sa_backward_fused(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
+                      const float* out, const float* lse2, const float* carry, const sa_tensor* d_out,
+                      const sa_tensor* dq, const sa_tensor* dk, const sa_tensor* dv, float* dq0_out, float* dk0_out,
+                      void* workspace, size_t workspace_bytes, void* stream) {
+  if (in == nullptr || in->engine != SA_ENGINE_TCGEN05) return in ? SA_ERR_UNSUPPORTED : SA_ERR_BAD_ARGUMENT;
+  RowLayout r_do, r_dq, r_dk, r_dv;
+  int st = rows_of(d_out, in->dtype, &r_do);
+  if (st == SA_OK) st = rows_of(dq, in->dtype, &r_dq);
+  if (st == SA_OK) st = rows_of(dk, in->dtype, &r_dk);
+  if (st == SA_OK) st = rows_of(dv, in->dtype, &r_dv);
+  if (st != SA_OK) return st;
+  return backward_common(in, q, k, v, sel, out, lse2, carry, d_out->ptr, d_out->dtype, &r_do, dq->ptr, dk->ptr, dv->ptr,
+                         &r_dq, &r_dk, &r_dv, dq0_out, dk0_out, workspace, workspace_bytes, stream);
+}
+
+namespace {
+int backward_common(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
+                    const float* out, const float* lse2, const float* carry, const void* d_out, int d_out_dtype,
+                    const RowLayout* d_out_rows, void* dq, void* dk, void* dv, const RowLayout* dq_rows,
+                    const RowLayout* dk_rows, const RowLayout* dv_rows, float* dq0_out, float* dk0_out, void* workspace,
+                    size_t workspace_bytes, void* stream) {
   Problem p;
   int st = to_problem(in, q, k, v, sel, &p);
   if (st != SA_OK) return st;
+  if (dv_rows != nullptr) p.dv_rows = *dv_rows;
   if (!q || !k || !v || !out || !lse2 || !carry || !d_out || !dq || !dk || !dv || !workspace) return SA_ERR_BAD_ARGUMENT;
   if (sel != nullptr && (!dq0_out || !dk0_out)) return SA_ERR_BAD_ARGUMENT;
   if (!dtype_ok(d_out_dtype) || in->damp != SA_DAMP_NONE) return SA_ERR_BAD_ARGUMENT;
@@ -294,25 +358,26 @@ int sa_backward_selector(const sa_problem* in, const void* q, const void* k, con
       copy = base + w.d_out_lowp;
       d_out_f32 = static_cast<const float*>(copy);
     }
-    st = launch_dbar(out, d_out, d_out_dtype, rows, p.head_dim, dbar, copy, SA_F32, s);
+    st = launch_dbar(out, d_out, d_out_dtype, rows, p.head_dim, dbar, copy, SA_F32, nullptr, p.heads, p.seq, s);
     if (st != SA_OK) return st;
     st = simt_backward(p, lse2, carry, dbar, d_out_f32, dq_acc, dk_acc, dq0, dk0, dv, s);
     if (st != SA_OK) return st;
-    st = launch_fold_cast(dk_acc, fold_k, dk, p.dtype, p.batch, p.heads, per_head, s);
+    st = launch_fold_cast(dk_acc, fold_k, dk, p.dtype, p.batch, p.heads, per_head, nullptr, p.head_dim, s);
     if (st != SA_OK) return st;
-    return launch_fold_cast(dq_acc, fold_q, dq, p.dtype, p.batch, p.heads, per_head, s);
+    return launch_fold_cast(dq_acc, fold_q, dq, p.dtype, p.batch, p.heads, per_head, nullptr, p.head_dim, s);
   }
   st = tc_backward_supported(p);
   if (st != SA_OK) return st;
   void* d_out_lowp = base + w.d_out_lowp;
-  st = launch_dbar(out, d_out, d_out_dtype, rows, p.head_dim, dbar, d_out_lowp, p.dtype, s);
+  st = launch_dbar(out, d_out, d_out_dtype, rows, p.head_dim, dbar, d_out_lowp, p.dtype, d_out_rows, p.heads, p.seq, s);
   if (st != SA_OK) return st;
   st = tc_backward(p, lse2, carry, dbar, d_out_lowp, dq_acc, dk_acc, dq0, dk0, dv, s);
   if (st != SA_OK) return st;
-  st = launch_fold_cast(dk_acc, fold_k, dk, p.dtype, p.batch, p.heads, per_head, s);
+  st = launch_fold_cast(dk_acc, fold_k, dk, p.dtype, p.batch, p.heads, per_head, dk_rows, p.head_dim, s);
   if (st != SA_OK) return st;
-  return launch_fold_cast(dq_acc, fold_q, dq, p.dtype, p.batch, p.heads, per_head, s);
+  return launch_fold_cast(dq_acc, fold_q, dq, p.dtype, p.batch, p.heads, per_head, dq_rows, p.head_dim, s);
 }
+}  // namespace
 
 int sa_backward(const sa_problem* in, const void* q, const void* k, const void* v, const float* out,
                 const float* lse2, const float* carry, const void* d_out, int d_out_dtype, void* dq, void* dk,

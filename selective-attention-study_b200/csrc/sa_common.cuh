@@ -30,6 +30,15 @@ struct Strided {
   int64_t sb, sh, st;   // batch, head, token strides in elements
 };
 
+// Element offset of row (b, h, t) of a (batch, heads, seq, head_dim) tensor with a contiguous innermost axis.
+struct RowLayout {
+  int64_t sb, sh, st;
+  __host__ __device__ int64_t at(int b, int h, int64_t t) const { return b * sb + h * sh + t * st; }
+};
+inline RowLayout contiguous_rows(int heads, int seq, int dim) {
+  return RowLayout{(int64_t)heads * seq * dim, (int64_t)seq * dim, (int64_t)dim};
+}
+
 struct Problem {
   int batch, heads, seq, head_dim;
   int exempt, damp, train_len;
@@ -41,6 +50,11 @@ struct Problem {
   // own tensors, and then no head of q / k is the selector: nothing is folded into head 0 by the backward.
   Strided q0, k0;
   bool external_selector;
+  // Layout-fused calls (tensor-core engine): an extra copy of the output in the operand dtype written straight into the
+  // caller's (batch, seq, heads * head_dim) activation, and dv written straight into the caller's gradient buffer.
+  void* out_lowp;        // null: not requested
+  RowLayout out_lowp_rows;
+  RowLayout dv_rows;     // where dv rows go (default: contiguous (batch, heads, seq, head_dim))
 };
 
 // ---- engine entry points (host) -------------------------------------------------------------------
@@ -60,11 +74,14 @@ int tc_backward(const Problem& p, const float* lse2, const float* carry, const f
 
 // ---- helper launches shared by both engines --------------------------------------------------------
 // dbar[row] = sum_d d_out[row, d] * out[row, d]; optionally also writes d_out rounded to `lowp_dtype`.
+// `d_out_rows` (may be null: contiguous) says where the rows of d_out start; `heads`, `seq` split a row index.
 int launch_dbar(const float* out, const void* d_out, int d_out_dtype, int64_t rows, int head_dim,
-                float* dbar, void* d_out_lowp, int lowp_dtype, cudaStream_t s);
-// dst[b, h] = cast(acc[b, h] + (h == 0 ? acc0[b] : 0)), rows of head_dim elements.
+                float* dbar, void* d_out_lowp, int lowp_dtype, const RowLayout* d_out_rows, int heads, int seq,
+                cudaStream_t s);
+// dst[b, h] = cast(acc[b, h] + (h == 0 ? acc0[b] : 0)), rows of head_dim elements; `dst_rows` (may be null:
+// contiguous) says where the rows of dst start.
 int launch_fold_cast(const float* acc, const float* acc0, void* dst, int dtype, int batch, int heads,
-                     int64_t seq_times_dim, cudaStream_t s);
+                     int64_t seq_times_dim, const RowLayout* dst_rows, int head_dim, cudaStream_t s);
 
 size_t decode_workspace_floats(int batch, int heads, int groups, int length, int head_dim);
 int decode_step(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim, int exempt,

@@ -15,7 +15,8 @@ namespace {
 template <typename TDO, typename TLOW, int D, bool kWriteLow>
 __global__ void __launch_bounds__(256) dbar_kernel(const float* __restrict__ out, const TDO* __restrict__ d_out,
                                                    int64_t rows, float* __restrict__ dbar,
-                                                   TLOW* __restrict__ d_out_low) {
+                                                   TLOW* __restrict__ d_out_low, bool strided, RowLayout in_rows, int heads,
+                                                   int seq) {
   constexpr int kLanes = D / 4;
   const int64_t gid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   const int64_t row = gid / kLanes;
@@ -23,10 +24,17 @@ __global__ void __launch_bounds__(256) dbar_kernel(const float* __restrict__ out
   float sum = 0.f;
   if (row < rows) {
     const int64_t off = row * D + lane * 4;
+    int64_t off_in = off;
+    if (strided) {                            // d_out rows sit in the caller's (batch, seq, heads, head_dim) activation gradient
+      const int64_t bh = row / seq;
+      const int64_t t = row - bh * seq;
+      const int b = (int)(bh / heads), h = (int)(bh - (int64_t)b * heads);
+      off_in = in_rows.at(b, h, t) + lane * 4;
+    }
     float4 o = *reinterpret_cast<const float4*>(out + off);
     float g[4];
 #pragma unroll
-    for (int e = 0; e < 4; ++e) g[e] = to_float<TDO>(d_out[off + e]);
+    for (int e = 0; e < 4; ++e) g[e] = to_float<TDO>(d_out[off_in + e]);
     sum = g[0] * o.x + g[1] * o.y + g[2] * o.z + g[3] * o.w;
     if (kWriteLow) {
 #pragma unroll
@@ -40,17 +48,19 @@ __global__ void __launch_bounds__(256) dbar_kernel(const float* __restrict__ out
 
 template <typename TDO, typename TLOW, bool kWriteLow>
 int dbar_by_dim(const float* out, const void* d_out, int64_t rows, int head_dim, float* dbar, void* low,
-                cudaStream_t s) {
+                const RowLayout* in_rows, int heads, int seq, cudaStream_t s) {
+  const bool strided = in_rows != nullptr;
+  const RowLayout rl = strided ? *in_rows : RowLayout{0, 0, 0};
   const int64_t threads = rows * (head_dim / 4);
   const unsigned blocks = (unsigned)((threads + 255) / 256);
   const TDO* g = static_cast<const TDO*>(d_out);
   TLOW* l = static_cast<TLOW*>(low);
   ProfileScope prof(SA_KERNEL_DBAR, s);
   switch (head_dim) {
-    case 16: count_launch(), dbar_kernel<TDO, TLOW, 16, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
-    case 32: count_launch(), dbar_kernel<TDO, TLOW, 32, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
-    case 64: count_launch(), dbar_kernel<TDO, TLOW, 64, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
-    case 128: count_launch(), dbar_kernel<TDO, TLOW, 128, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l); break;
+    case 16: count_launch(), dbar_kernel<TDO, TLOW, 16, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l, strided, rl, heads, seq); break;
+    case 32: count_launch(), dbar_kernel<TDO, TLOW, 32, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l, strided, rl, heads, seq); break;
+    case 64: count_launch(), dbar_kernel<TDO, TLOW, 64, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l, strided, rl, heads, seq); break;
+    case 128: count_launch(), dbar_kernel<TDO, TLOW, 128, kWriteLow><<<blocks, 256, 0, s>>>(out, g, rows, dbar, l, strided, rl, heads, seq); break;
     default: return SA_ERR_UNSUPPORTED;
   }
   SA_CUDA_CHECK(cudaGetLastError());
@@ -59,11 +69,11 @@ int dbar_by_dim(const float* out, const void* d_out, int64_t rows, int head_dim,
 
 template <typename TDO>
 int dbar_by_low(const float* out, const void* d_out, int64_t rows, int head_dim, float* dbar, void* low,
-                int low_dtype, cudaStream_t s) {
-  if (low == nullptr) return dbar_by_dim<TDO, float, false>(out, d_out, rows, head_dim, dbar, nullptr, s);
-  if (low_dtype == SA_BF16) return dbar_by_dim<TDO, __nv_bfloat16, true>(out, d_out, rows, head_dim, dbar, low, s);
-  if (low_dtype == SA_F16) return dbar_by_dim<TDO, __half, true>(out, d_out, rows, head_dim, dbar, low, s);
-  if (low_dtype == SA_F32) return dbar_by_dim<TDO, float, true>(out, d_out, rows, head_dim, dbar, low, s);
+                int low_dtype, const RowLayout* in_rows, int heads, int seq, cudaStream_t s) {
+  if (low == nullptr) return dbar_by_dim<TDO, float, false>(out, d_out, rows, head_dim, dbar, nullptr, in_rows, heads, seq, s);
+  if (low_dtype == SA_BF16) return dbar_by_dim<TDO, __nv_bfloat16, true>(out, d_out, rows, head_dim, dbar, low, in_rows, heads, seq, s);
+  if (low_dtype == SA_F16) return dbar_by_dim<TDO, __half, true>(out, d_out, rows, head_dim, dbar, low, in_rows, heads, seq, s);
+  if (low_dtype == SA_F32) return dbar_by_dim<TDO, float, true>(out, d_out, rows, head_dim, dbar, low, in_rows, heads, seq, s);
   return SA_ERR_BAD_ARGUMENT;
 }
 
@@ -71,7 +81,7 @@ int dbar_by_low(const float* out, const void* d_out, int64_t rows, int head_dim,
 template <typename T>
 __global__ void __launch_bounds__(256) fold_cast_kernel(const float* __restrict__ acc, const float* __restrict__ acc0,
                                                         T* __restrict__ dst, int heads, int64_t per_head,
-                                                        int64_t total4) {
+                                                        int64_t total4, bool strided, RowLayout dst_rows, int head_dim) {
   int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= total4) return;
   int64_t e = idx * 4;
@@ -83,10 +93,15 @@ __global__ void __launch_bounds__(256) fold_cast_kernel(const float* __restrict_
     float4 z = *reinterpret_cast<const float4*>(acc0 + (int64_t)b * per_head + within);
     a.x += z.x; a.y += z.y; a.z += z.z; a.w += z.w;
   }
-  dst[e + 0] = from_float<T>(a.x);
-  dst[e + 1] = from_float<T>(a.y);
-  dst[e + 2] = from_float<T>(a.z);
-  dst[e + 3] = from_float<T>(a.w);
+  int64_t o = e;
+  if (strided) {                              // rows go into the caller's (batch, seq, ..., heads, head_dim) gradient buffer
+    const int64_t t = within / head_dim;
+    o = dst_rows.at(b, h, t) + (within - t * head_dim);
+  }
+  dst[o + 0] = from_float<T>(a.x);
+  dst[o + 1] = from_float<T>(a.y);
+  dst[o + 2] = from_float<T>(a.z);
+  dst[o + 3] = from_float<T>(a.w);
 }
 
 // ---- decode -----------------------------------------------------------------------------------------
@@ -429,33 +444,35 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
 }  // namespace
 
 int launch_dbar(const float* out, const void* d_out, int d_out_dtype, int64_t rows, int head_dim, float* dbar,
-                void* d_out_lowp, int lowp_dtype, cudaStream_t s) {
+                void* d_out_lowp, int lowp_dtype, const RowLayout* d_out_rows, int heads, int seq, cudaStream_t s) {
   switch (d_out_dtype) {
-    case SA_F32: return dbar_by_low<float>(out, d_out, rows, head_dim, dbar, d_out_lowp, lowp_dtype, s);
-    case SA_BF16: return dbar_by_low<__nv_bfloat16>(out, d_out, rows, head_dim, dbar, d_out_lowp, lowp_dtype, s);
-    case SA_F16: return dbar_by_low<__half>(out, d_out, rows, head_dim, dbar, d_out_lowp, lowp_dtype, s);
+    case SA_F32: return dbar_by_low<float>(out, d_out, rows, head_dim, dbar, d_out_lowp, lowp_dtype, d_out_rows, heads, seq, s);
+    case SA_BF16: return dbar_by_low<__nv_bfloat16>(out, d_out, rows, head_dim, dbar, d_out_lowp, lowp_dtype, d_out_rows, heads, seq, s);
+    case SA_F16: return dbar_by_low<__half>(out, d_out, rows, head_dim, dbar, d_out_lowp, lowp_dtype, d_out_rows, heads, seq, s);
   }
   return SA_ERR_BAD_ARGUMENT;
 }
 
 int launch_fold_cast(const float* acc, const float* acc0, void* dst, int dtype, int batch, int heads,
-                     int64_t seq_times_dim, cudaStream_t s) {
+                     int64_t seq_times_dim, const RowLayout* dst_rows, int head_dim, cudaStream_t s) {
+  const bool strided = dst_rows != nullptr;
+  const RowLayout rl = strided ? *dst_rows : RowLayout{0, 0, 0};
   const int64_t total4 = (int64_t)batch * heads * seq_times_dim / 4;
   const unsigned blocks = (unsigned)((total4 + 255) / 256);
   switch (dtype) {
     case SA_F32:
       count_launch();
-      fold_cast_kernel<float><<<blocks, 256, 0, s>>>(acc, acc0, static_cast<float*>(dst), heads, seq_times_dim, total4);
+      fold_cast_kernel<float><<<blocks, 256, 0, s>>>(acc, acc0, static_cast<float*>(dst), heads, seq_times_dim, total4, strided, rl, head_dim);
       break;
     case SA_BF16:
       count_launch();
       fold_cast_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(acc, acc0, static_cast<__nv_bfloat16*>(dst), heads,
-                                                             seq_times_dim, total4);
+                                                             seq_times_dim, total4, strided, rl, head_dim);
       break;
     case SA_F16:
       count_launch();
       fold_cast_kernel<__half><<<blocks, 256, 0, s>>>(acc, acc0, static_cast<__half*>(dst), heads, seq_times_dim,
-                                                      total4);
+                                                      total4, strided, rl, head_dim);
       break;
     default: return SA_ERR_BAD_ARGUMENT;
   }

@@ -241,7 +241,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     const __grid_constant__ CUtensorMap map_q0, const __grid_constant__ CUtensorMap map_k0,
     const float* __restrict__ lse2, const float* __restrict__ carry, const float* __restrict__ dbar,
     float* __restrict__ dk_acc, float* __restrict__ dk0, __nv_bfloat16* __restrict__ dv, int heads, int seq,
-    int ntiles, int exempt, float scale, WaitCtx status) {
+    int ntiles, int exempt, float scale, WaitCtx status, RowLayout dv_rows) {
   using L = BwdSmem;
   constexpr int D = 64;
   const int nrows = gridDim.x / ntiles;                  // batch * heads
@@ -519,7 +519,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     // ---- epilogue: dV, dK (this head) and this head's share of dK0 ------------------------------------------
     {
       const int c0 = wg * kChunk;
-      __nv_bfloat16* dv_row = dv + ((int64_t)n * seq + j) * D + c0;
+      __nv_bfloat16* dv_row = dv + dv_rows.at(b, h, j) + c0;
       float* dk_row = dk_acc + ((int64_t)n * seq + j) * D + c0;
       float* dk0_row = dk0 + ((int64_t)b * seq + j) * D + c0;
       uint32_t rv[16], rk[16], r0[16];
@@ -603,11 +603,11 @@ int backward(const Problem& p, const float* lse2, const float* carry, const floa
     if (self)
       backward_kernel<true><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
           map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status);
+          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
     else
       backward_kernel<false><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
           map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status);
+          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
   }
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;

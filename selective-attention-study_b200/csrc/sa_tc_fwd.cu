@@ -217,7 +217,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_q0,
                         const __grid_constant__ CUtensorMap map_k0, const float* __restrict__ carry,
                         float* __restrict__ out, float* __restrict__ lse2, int heads, int seq, int ntiles, int exempt,
-                        float scale, WaitCtx status) {
+                        float scale, WaitCtx status, __nv_bfloat16* __restrict__ out_lowp, RowLayout out_lowp_rows) {
   using L = WideSmem<D>;
   constexpr int DK = D / 64, DH = D / 4, NC = 32, ST = L::kStages;
   // TMEM columns: S and L0 (fp32, 128 each), the output accumulator (D), Q and Q0 as bf16 pairs (D / 2 each)
@@ -576,6 +576,15 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         orow[d >> 2] = make_float4(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv,
                                    __uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv);
       if (wg == 0) lse2[(int64_t)n * seq + i] = run_max + log2f(den);
+      if (out_lowp != nullptr) {                               // the same rows in the operand dtype, in the caller's layout
+        uint4* lrow = reinterpret_cast<uint4*>(out_lowp + out_lowp_rows.at(b, h, i) + wg * DH);
+#pragma unroll
+        for (int d = 0; d < DH; d += 8)
+          lrow[d >> 3] = make_uint4(pack_bf16(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv),
+                                    pack_bf16(__uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv),
+                                    pack_bf16(__uint_as_float(r[d + 4]) * inv, __uint_as_float(r[d + 5]) * inv),
+                                    pack_bf16(__uint_as_float(r[d + 6]) * inv, __uint_as_float(r[d + 7]) * inv));
+      }
     }
   }
   tc_fence_before_sync();
@@ -631,10 +640,12 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
       count_launch();
       if (self)
         forward_wide_kernel<D, true><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2,
-                                                                            p.heads, p.seq, ntiles, p.exempt, p.scale, status);
+                                                                            p.heads, p.seq, ntiles, p.exempt, p.scale, status,
+                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows);
       else
         forward_wide_kernel<D, false><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2,
-                                                                             p.heads, p.seq, ntiles, p.exempt, p.scale, status);
+                                                                             p.heads, p.seq, ntiles, p.exempt, p.scale, status,
+                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows);
     }
     SA_CUDA_CHECK(cudaGetLastError());
     return SA_OK;

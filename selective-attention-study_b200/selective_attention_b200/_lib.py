@@ -23,7 +23,7 @@ DAMP_CODES = {"none": 0, "linear": 1, "sqrt": 2}
 EXPORTS = ("sa_abi_version", "sa_status_string", "sa_last_cuda_error", "sa_engine_available", "sa_engine_supports", "sa_carry_rows", "sa_carry_checkpoints", "sa_forward",
            "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step", "sa_device_status", "sa_selftest_tcgen05", "sa_profile_enable",
            "sa_profile_collect", "sa_static_scratch_floats", "sa_forward_static_scratch", "sa_forward_selector",
-           "sa_backward_selector", "sa_selection_carry", "sa_launch_count", "sa_selftest_wait_timeout")
+           "sa_backward_selector", "sa_forward_fused", "sa_backward_fused", "sa_selection_carry", "sa_launch_count", "sa_selftest_wait_timeout")
 
 
 class Problem(ctypes.Structure):
@@ -37,6 +37,12 @@ class Problem(ctypes.Structure):
 class Selector(ctypes.Structure):
     _fields_ = [("struct_bytes", ctypes.c_int32), ("reserved", ctypes.c_int32), ("q0", ctypes.c_void_p),
                 ("k0", ctypes.c_void_p), ("q0_stride", ctypes.c_int64 * 2), ("k0_stride", ctypes.c_int64 * 2)]
+
+
+class Tensor(ctypes.Structure):
+    """sa_tensor: rows of head_dim contiguous elements at batch / head / token strides."""
+    _fields_ = [("ptr", ctypes.c_void_p), ("dtype", ctypes.c_int32), ("reserved", ctypes.c_int32),
+                ("stride", ctypes.c_int64 * 3)]
 
 
 class LibraryError(RuntimeError):
@@ -81,6 +87,11 @@ def load() -> ctypes.CDLL:
     lib.sa_forward_selector.argtypes = [pp, vp, vp, vp, sp, f32p, f32p, f32p, f32p, vp]
     lib.sa_backward_selector.restype = i32
     lib.sa_backward_selector.argtypes = [pp, vp, vp, vp, sp, f32p, f32p, f32p, vp, i32, vp, vp, vp, f32p, f32p, vp, sz, vp]
+    tp = ctypes.POINTER(Tensor)
+    lib.sa_forward_fused.restype = i32
+    lib.sa_forward_fused.argtypes = [pp, vp, vp, vp, sp, f32p, tp, f32p, f32p, f32p, vp]
+    lib.sa_backward_fused.restype = i32
+    lib.sa_backward_fused.argtypes = [pp, vp, vp, vp, sp, f32p, f32p, f32p, tp, tp, tp, tp, f32p, f32p, vp, sz, vp]
     lib.sa_selection_carry.restype = i32
     lib.sa_selection_carry.argtypes = [pp, vp, vp, sp, f32p, f32p, vp]
     lib.sa_launch_count.restype = ctypes.c_ulonglong

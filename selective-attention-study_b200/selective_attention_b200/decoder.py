@@ -5,9 +5,10 @@ MLP of width 4 d (``:276-286``), tied input / output embeddings (``:365-366``), 
 initialisation (``:379-385``), no position signal.  The loss is computed over the sequence in chunks so the
 (T x vocab) logits never exist at once (the reference does this for evaluation, ``:420-447``).
 
-The attention layer hands the operator the transposed views of the fused QKV projection as they are
-(the tensor-core engine reads strided (B, T, H, D) data through TMA descriptors); nothing is copied
-before the kernel."""
+The attention layer hands the operator the fused QKV projection output as it is (the tensor-core engine
+reads strided (B, T, H, D) data through TMA descriptors), gets the merged (B, T, H * D) activation written by
+the forward kernel, and gets dq, dk, dv written straight into the projection's gradient: nothing is copied
+on either side of the kernels in either pass (bf16; fp32 runs take the unfused call)."""
 
 from __future__ import annotations
 
@@ -28,6 +29,8 @@ class SelectiveSelfAttention(nn.Module):
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         b, t, _ = x.shape
         qkv = self.c_attn(x).view(b, t, 3, self.n_heads, self.d_model // self.n_heads)
+        if kernels.packed_supported(qkv):                                    # bf16: no copy on either side of the kernels
+            return self.c_proj(kernels.selective_attention_packed(qkv, exempt=self.exempt))
         q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))          # (B, H, T, D) views, no copy
         y = kernels.selective_attention(q, k, v, exempt=self.exempt).to(x.dtype)
         return self.c_proj(y.transpose(1, 2).reshape(b, t, self.d_model))

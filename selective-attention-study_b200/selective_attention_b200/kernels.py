@@ -435,6 +435,87 @@ def selective_attention(
                                        bwd_num_warps, bwd_num_stages, group, bwd_group, num_stages, exempt)
 
 
+# ---- layout-fused form for a model's attention layer -------------------------------------------------
+
+def _tensor_struct(t: torch.Tensor) -> _lib.Tensor:
+    """sa_tensor for a (B, H, T, D) view with a contiguous last axis."""
+    d = _lib.Tensor()
+    d.ptr, d.dtype = t.data_ptr(), _DTYPE_CODE[t.dtype]
+    d.stride[:] = list(t.stride()[:3])
+    return d
+
+
+def packed_supported(qkv: torch.Tensor) -> bool:
+    """True when ``selective_attention_packed`` can take this fused projection output: bf16 on a CUDA device,
+    (B, T, 3, H, D) with D = 64, contiguous, and the library built."""
+    return (HAS_KERNELS and qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 5 and qkv.shape[2] == 3
+            and qkv.shape[4] == 64 and qkv.is_contiguous() and os.environ.get("SA_B200_ENGINE", "") != "simt")
+
+
+class _SelectiveAttentionPackedFn(torch.autograd.Function):
+    """The operator between a model's fused QKV projection and its output projection, without the copies around it:
+    q, k, v are read in place from the (B, T, 3, H, D) projection output (strided TMA descriptors), the result is
+    written by the forward kernel as (B, T, H * D) in the activation dtype, the cotangent is read in that layout,
+    and dq, dk, dv are written by the backward's kernels into one (B, T, 3, H, D) gradient."""
+
+    @staticmethod
+    def forward(ctx, qkv, exempt):
+        exempt = _check_exempt(exempt)
+        lib = _lib.load()
+        b, t, _, h, d = qkv.shape
+        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))          # (B, H, T, D) views
+        dev = qkv.device
+        engine = _lib.ENGINE_TCGEN05
+        out = torch.empty(b, h, t, d, device=dev, dtype=torch.float32)       # kept for the backward's row sums
+        merged = torch.empty(b, t, h * d, device=dev, dtype=qkv.dtype)
+        lse2 = torch.empty(b, h, t, device=dev, dtype=torch.float32)
+        carry = torch.empty(b, lib.sa_carry_checkpoints(engine, t), t, device=dev, dtype=torch.float32)
+        total = torch.empty(b, t, device=dev, dtype=torch.float32)
+        prob = _problem(q, k, v, engine, exempt)
+        low = _tensor_struct(merged.view(b, t, h, d).transpose(1, 2))
+        with torch.cuda.device(dev):
+            st = lib.sa_forward_fused(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), None, out.data_ptr(),
+                                      ctypes.byref(low), lse2.data_ptr(), carry.data_ptr(), total.data_ptr(), _stream(dev))
+        _lib.check("sa_forward_fused", st)
+        ctx.save_for_backward(qkv, out, lse2, carry)
+        ctx.exempt = exempt
+        return merged
+
+    @staticmethod
+    @once_differentiable
+    def backward(ctx, d_merged):
+        qkv, out, lse2, carry = ctx.saved_tensors
+        lib = _lib.load()
+        b, t, _, h, d = qkv.shape
+        dev = qkv.device
+        q, k, v = (qkv[:, :, i].transpose(1, 2) for i in range(3))
+        d_merged = d_merged.to(qkv.dtype)
+        if not d_merged.is_contiguous():
+            d_merged = d_merged.contiguous()
+        d_qkv = torch.empty_like(qkv)
+        dq, dk, dv = (d_qkv[:, :, i].transpose(1, 2) for i in range(3))
+        prob = _problem(q, k, v, _lib.ENGINE_TCGEN05, ctx.exempt)
+        need = lib.sa_backward_workspace_bytes(ctypes.byref(prob))
+        workspace = torch.empty(max(need, 1), device=dev, dtype=torch.uint8)
+        descs = [_tensor_struct(x) for x in (d_merged.view(b, t, h, d).transpose(1, 2), dq, dk, dv)]
+        with torch.cuda.device(dev):
+            st = lib.sa_backward_fused(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), None, out.data_ptr(),
+                                       lse2.data_ptr(), carry.data_ptr(), *(ctypes.byref(x) for x in descs), None, None,
+                                       workspace.data_ptr(), need, _stream(dev))
+        _lib.check("sa_backward_fused", st)
+        return d_qkv, None
+
+
+def selective_attention_packed(qkv: torch.Tensor, exempt: int = 1) -> torch.Tensor:
+    """Differentiable Selective Attention on a fused projection output.  qkv: (B, T, 3, H, D) bf16, contiguous
+    (``packed_supported``); returns (B, T, H * D) bf16, ready for the output projection.  Head 0 selects for all
+    heads.  Same arithmetic as ``selective_attention`` on the three (B, H, T, D) views; what is saved is every
+    copy between the projections and the kernels."""
+    if not packed_supported(qkv):
+        raise ValueError("qkv must be a contiguous bf16 CUDA tensor (B, T, 3, H, 64); use selective_attention otherwise")
+    return _SelectiveAttentionPackedFn.apply(qkv, exempt)
+
+
 # ---- cached decode ------------------------------------------------------------------------------------
 
 def decode_step(cache: dict, q1: torch.Tensor, k1: torch.Tensor, v1: torch.Tensor, exempt: int = 1) -> torch.Tensor:

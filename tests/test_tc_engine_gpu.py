@@ -161,3 +161,35 @@ def test_reference_layout_of_the_carry_on_request():
         want = sel[:, : 32 * rb].sum(dim=1)                 # zero for keys at or after the block, stored or not
         torch.testing.assert_close(aux["carry"][:, rb].cpu(), want, atol=1e-3, rtol=1e-3)
     assert (native["carry"][:, 0] == 0).all() and (aux["carry"][:, 0] == 0).all()
+
+
+@pytest.mark.parametrize("seq,heads", [(300, 3), (1000, 2), (129, 1)])
+def test_packed_projection_form_equals_the_plain_call(seq, heads):
+    """The layout-fused entry (q, k, v read in place from a (B, T, 3, H, D) projection output, merged (B, T, H D)
+    output and packed gradients written by the kernels) against the plain call on the three views, and the oracle."""
+    g = torch.Generator("cpu").manual_seed(seq)
+    b, d = 2, 64
+    qkv = torch.randn(b, seq, 3, heads, d, generator=g).bfloat16().cuda()
+    w = torch.randn(b, seq, heads * d, generator=g).bfloat16().cuda()
+    assert kernels.packed_supported(qkv)
+    x = qkv.clone().requires_grad_(True)
+    before = _lib.launch_count()
+    y = kernels.selective_attention_packed(x)
+    y.backward(w)
+    assert _lib.launch_count() - before == 7          # colsum, scan, forward | dbar, backward, 2 x fold: no copy kernels of ours
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert y.shape == (b, seq, heads * d) and y.dtype == torch.bfloat16 and x.grad.shape == qkv.shape
+
+    x2 = qkv.clone().requires_grad_(True)
+    q, k, v = (x2[:, :, i].transpose(1, 2) for i in range(3))
+    y2 = kernels.selective_attention(q, k, v).to(torch.bfloat16).transpose(1, 2).reshape(b, seq, heads * d)
+    y2.backward(w)
+    torch.testing.assert_close(y.float(), y2.float(), atol=0, rtol=0)         # the same kernel, the same rounding
+    assert _rel(x.grad.float().cpu(), x2.grad.float().cpu()) < 2e-3            # atomics' order only
+    qf, kf, vf = (qkv[:, :, i].transpose(1, 2).float().cpu() for i in range(3))
+    wf = w.view(b, seq, heads, d).transpose(1, 2).float().cpu()
+    want = oracle.attention_grads(qf, kf, vf, wf)
+    got = [y.view(b, seq, heads, d).transpose(1, 2).float().cpu()] + [x.grad[:, :, i].transpose(1, 2).float().cpu() for i in range(3)]
+    for name, a, bb in zip(("out", "dq", "dk", "dv"), got, want):
+        assert _rel(a, bb) < 2e-2, (name, _rel(a, bb))
