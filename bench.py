@@ -386,10 +386,22 @@ def run_ours(args, w, rank, world, device):
         raise RuntimeError(f"a bounded device-side wait ran out (status {status:#x}); the timing is invalid")
 
     # ---- end-to-end arm: host buffers in, host buffers out ------------------------------------------------
-    host_in = [q_h, k_h, v_h] + ([do_h] if w["backward"] else []) + list(sel_h)
+    # Whole sequences with a shared selector go through the layer-facing call: one packed (B, T, 3, H, D) projection
+    # output and one (B, T, H D) cotangent in, the merged output and the packed gradient out (the same bytes).
+    packed = w["backward"] and not w["per_head"] and not sel_h and w["dim"] == 64
+    if packed:
+        q_h, k_h, v_h, do_h = (t.transpose(1, 2) for t in (q_h, k_h, v_h, do_h))       # (B, T, H, D)
+        qkv_h = torch.stack([q_h, k_h, v_h], dim=2).contiguous()                       # (B, T, 3, H, D)
+        do_h = do_h.reshape(do_h.shape[0], do_h.shape[1], -1).contiguous()              # (B, T, H D)
+        host_in = [qkv_h, do_h]
+    else:
+        host_in = [q_h, k_h, v_h] + ([do_h] if w["backward"] else []) + list(sel_h)
     pinned_in = [t.pin_memory() for t in host_in]
     n_main = 4 if w["backward"] else 3
-    out_shapes = [q_h.shape] * (4 if w["backward"] else 1) + ([sel_h[0].shape] * 2 if sel_h and w["backward"] else [])
+    if packed:
+        out_shapes = [do_h.shape, qkv_h.shape]
+    else:
+        out_shapes = [q_h.shape] * (4 if w["backward"] else 1) + ([sel_h[0].shape] * 2 if sel_h and w["backward"] else [])
     pinned_out = [torch.empty(shape, dtype=torch.bfloat16).pin_memory() for shape in out_shapes]
     h2d = sum(t.numel() * t.element_size() for t in pinned_in)
     d2h = sum(t.numel() * t.element_size() for t in pinned_out)
@@ -413,6 +425,21 @@ def run_ours(args, w, rank, world, device):
                 dst.copy_(src, non_blocking=True)
             uploaded[slot].record(s_in)
         s_comp.wait_event(uploaded[slot])
+        if packed:
+            xd = dev_in[slot][0].detach().requires_grad_(True)
+            y = kernels.selective_attention_packed(xd)
+            y.backward(dev_in[slot][1])
+            results = [y.detach(), xd.grad]
+            consumed[slot].record(s_comp)
+            done = torch.cuda.Event()
+            done.record(s_comp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for dst, src in zip(pinned_out, results):
+                    src.record_stream(s_out)
+                    dst.copy_(src, non_blocking=True)
+                downloaded.record(s_out)
+            return
         qd, kd, vd = (t.detach() for t in dev_in[slot][:3])
         sd = tuple(t.detach() for t in dev_in[slot][n_main:])
         if w["backward"]:
@@ -502,7 +529,9 @@ def run_ours(args, w, rank, world, device):
                    "per_rank_ms_fwd_bwd_allreduce_step": per_rank, "host_affinity": affinity},
         "e2e": {"value": whole_job_tokens_per_second(tokens, e2e_ms), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.steps,
-                "copies_alone_gbs": {"h2d": h2d_gbs, "d2h": d2h_gbs}, "bytes_are": "per rank"},
+                "copies_alone_gbs": {"h2d": h2d_gbs, "d2h": d2h_gbs}, "bytes_are": "per rank",
+                "call": "selective_attention_packed (fused QKV layout in, merged output and packed gradient out)" if packed
+                        else "selective_attention / selective_attention_forward on (B, H, T, D) tensors"},
         "gpu_launches": launches,
         "roofline": {"bound": "tensor", "kernel": dominant, "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                      "frac": (achieved / peak) if achieved else None, "peak_kind": peak_kind,

@@ -150,6 +150,21 @@ int sa_forward_fused(const sa_problem* p, const void* q, const void* k, const vo
                      float* out, const sa_tensor* out_lowp, float* lse2, float* carry, float* total,
                      void* stream);
 
+/* Prefill continuation (tensor-core engine): the forward for a chunk of NEW tokens appended to a cache.  p->seq is
+ * the total length (cached + new); q_new holds only the new queries, (batch, heads, seq - cached, head_dim) at the
+ * strides of p->q_stride; k_cache / v_cache hold all p->seq keys and values at p->k_stride / p->v_stride (the new
+ * tokens' rows already written); selected[b * selected_stride + j] is the selection key j has received from the
+ * `cached` queries before (zero for the new keys).  Computes exactly what sa_forward computes for the last
+ * seq - cached queries of the whole sequence, without the earlier queries:
+ *   out, lse2  (batch, heads, seq - cached, ...) for the new queries
+ *   total      (batch, seq): selection received from ALL queries so far (the cache's new `selected`)
+ *   carry      (batch, sa_carry_checkpoints(engine, seq), seq) scratch
+ * The reference has no such entry: its begin_cache prefills from position 0 only
+ * (src/selective_attention/mixers.py:105-113) and continues token by token with step_cache (:115-130). */
+int sa_prefill_extend(const sa_problem* p, int cached, const void* q_new, const void* k_cache, const void* v_cache,
+                      const float* selected, int64_t selected_stride,
+                      float* out, float* lse2, float* carry, float* total, void* stream);
+
 /* Forward for callers that must not allocate.  It has no counterpart in the reference (whose forward
  * allocates its CARRY scratch with torch on every call, src/selective_attention/kernels.py:573-580).
  *

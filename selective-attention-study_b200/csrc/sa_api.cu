@@ -73,6 +73,9 @@ int to_problem(const sa_problem* in, const void* q, const void* k, const void* v
   p->q = Strided{q, in->q_stride[0], in->q_stride[1], in->q_stride[2]};
   p->k = Strided{k, in->k_stride[0], in->k_stride[1], in->k_stride[2]};
   p->v = Strided{v, in->v_stride[0], in->v_stride[1], in->v_stride[2]};
+  p->q_offset = 0;
+  p->carry_init = nullptr;
+  p->carry_init_stride = 0;
   p->out_lowp = nullptr;
   p->out_lowp_rows = contiguous_rows(in->heads, in->seq, in->head_dim);
   p->dv_rows = contiguous_rows(in->heads, in->seq, in->head_dim);
@@ -217,6 +220,24 @@ int sa_selection_carry(const sa_problem* in, const void* q, const void* k, const
 int sa_forward(const sa_problem* in, const void* q, const void* k, const void* v, float* out, float* lse2,
                float* carry, float* total, void* stream) {
   return sa_forward_selector(in, q, k, v, nullptr, out, lse2, carry, total, stream);
+}
+
+int sa_prefill_extend(const sa_problem* in, int cached, const void* q_new, const void* k_cache, const void* v_cache,
+                      const float* selected, int64_t selected_stride, float* out, float* lse2, float* carry, float* total,
+                      void* stream) {
+  Problem p;
+  int st = to_problem(in, q_new, k_cache, v_cache, nullptr, &p);
+  if (st != SA_OK) return st;
+  if (!q_new || !k_cache || !v_cache || !selected || !out || !lse2 || !carry || !total) return SA_ERR_BAD_ARGUMENT;
+  if (cached < 0 || cached >= in->seq || selected_stride < in->seq) return SA_ERR_BAD_ARGUMENT;
+  if (in->engine != SA_ENGINE_TCGEN05) return SA_ERR_UNSUPPORTED;
+  st = tc_supported(p);
+  if (st != SA_OK) return st;
+  if (tc::timeout_pending()) return SA_ERR_DEVICE_TIMEOUT;
+  p.q_offset = cached;
+  p.carry_init = selected;
+  p.carry_init_stride = selected_stride;
+  return tc_forward(p, out, lse2, carry, total, static_cast<cudaStream_t>(stream));
 }
 
 // ---- forward with library-owned scratch (no allocation anywhere on the call path) ----------------------

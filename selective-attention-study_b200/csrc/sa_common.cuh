@@ -52,6 +52,11 @@ struct Problem {
   bool external_selector;
   // Layout-fused calls (tensor-core engine): an extra copy of the output in the operand dtype written straight into the
   // caller's (batch, seq, heads * head_dim) activation, and dv written straight into the caller's gradient buffer.
+  // Prefill continuation (tensor-core engine): q holds only the queries from position q_offset on, k / v hold all `seq`
+  // keys (the cache); carry_init[b * carry_init_stride + j] is the selection key j received from the queries before.
+  int q_offset;
+  const float* carry_init;
+  int64_t carry_init_stride;
   void* out_lowp;        // null: not requested
   RowLayout out_lowp_rows;
   RowLayout dv_rows;     // where dv rows go (default: contiguous (batch, heads, seq, head_dim))

@@ -49,10 +49,12 @@ template <int D>
 __global__ void __launch_bounds__(128) colsum_kernel(const __grid_constant__ CUtensorMap map_q,
                                                      const __grid_constant__ CUtensorMap map_k, float* __restrict__ carry,
                                                      int seq, int ntiles, int exempt, float scale,
-                                                     WaitCtx status) {
+                                                     WaitCtx status, int q_offset, int mi_first) {
   constexpr int DK = D / 64;
   const int nj = blockIdx.x, b = blockIdx.z;
-  const int mi0 = nj + blockIdx.y * kColsumChunk;
+  // Query tiles from the key tile's own (the diagonal) on; in a prefill continuation from the first tile that holds a
+  // new query on (rows before q_offset are not in the query tensor: TMA fills them with zeros, which select nothing).
+  const int mi0 = max(nj, mi_first) + blockIdx.y * kColsumChunk;
   if (mi0 >= ntiles) return;
   const int count = min(kColsumChunk, ntiles - mi0);
 
@@ -85,7 +87,7 @@ __global__ void __launch_bounds__(128) colsum_kernel(const __grid_constant__ CUt
     uint64_t* bar = &bar_q[it & 1];
     mbar_expect_tx(bar, DK * kRowTile);
     for (int s = 0; s < DK; ++s)
-      tma_load_4d(q0s + ((it & 1) * DK + s) * kRowTile, &map_q, bar, s * 64, (mi0 + it) * kTile, 0, b);
+      tma_load_4d(q0s + ((it & 1) * DK + s) * kRowTile, &map_q, bar, s * 64, (mi0 + it) * kTile - q_offset, 0, b);
   };
   auto issue = [&](int it) {
     mbar_wait(&bar_q[it & 1], (it >> 1) & 1, status, 200);
@@ -138,13 +140,14 @@ __global__ void __launch_bounds__(128) colsum_kernel(const __grid_constant__ CUt
 // One thread per key column: CARRY[b][mi][j] = sum of COLSUM[b][m'][j] over m' < mi, in place; row `ntiles`
 // and total[b][j] receive the sum over all query tiles.  Only rows mi >= j / 128 exist.
 __global__ void __launch_bounds__(256) scan_kernel(float* __restrict__ carry, float* __restrict__ total, int seq,
-                                                   int ntiles) {
+                                                   int ntiles, int mi_first, const float* __restrict__ init,
+                                                   int64_t init_stride) {
   const int j = blockIdx.x * blockDim.x + threadIdx.x;
   const int b = blockIdx.y;
   if (j >= seq) return;
   float* col = carry + (int64_t)b * (ntiles + 1) * seq + j;
-  float run = 0.f;
-  int mi = j / kTile;
+  float run = init ? init[(int64_t)b * init_stride + j] : 0.f;   // what the key received before the first query given
+  int mi = max(j / kTile, mi_first);
   for (; mi + 8 <= ntiles; mi += 8) {
     float x[8];
 #pragma unroll
@@ -217,7 +220,8 @@ __global__ void __launch_bounds__(kWideThreads, 1)
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_q0,
                         const __grid_constant__ CUtensorMap map_k0, const float* __restrict__ carry,
                         float* __restrict__ out, float* __restrict__ lse2, int heads, int seq, int ntiles, int exempt,
-                        float scale, WaitCtx status, __nv_bfloat16* __restrict__ out_lowp, RowLayout out_lowp_rows) {
+                        float scale, WaitCtx status, __nv_bfloat16* __restrict__ out_lowp, RowLayout out_lowp_rows,
+                        int q_offset) {
   using L = WideSmem<D>;
   constexpr int DK = D / 64, DH = D / 4, NC = 32, ST = L::kStages;
   // TMEM columns: S and L0 (fp32, 128 each), the output accumulator (D), Q and Q0 as bf16 pairs (D / 2 each)
@@ -227,7 +231,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   constexpr bool kTmemAB = (D == 64);
   constexpr uint32_t kColTri = 384, kColP = 448;
 
-  const int nrows = gridDim.x / ntiles;                       // batch * heads
+  const int nrows = gridDim.x / (ntiles - q_offset / kTile);  // batch * heads (the grid covers the query tiles with rows to compute)
   const int mi = ntiles - 1 - (int)(blockIdx.x / nrows);      // heaviest query tiles first
   const int n = blockIdx.x % nrows;
   const int b = n / heads, h = n - b * heads;
@@ -328,8 +332,8 @@ __global__ void __launch_bounds__(kWideThreads, 1)
 
       mbar_expect_tx(&bar_q, (SELF ? 1 : 2) * DK * kRowTile);
       for (int s2 = 0; s2 < DK; ++s2) {
-        tma_load_4d(smem + L::q + s2 * kRowTile, &map_q, &bar_q, s2 * 64, i0, h, b);
-        if (!SELF) tma_load_4d(smem + L::q0_landing + s2 * kRowTile, &map_q0, &bar_q, s2 * 64, i0, 0, b);
+        tma_load_4d(smem + L::q + s2 * kRowTile, &map_q, &bar_q, s2 * 64, i0 - q_offset, h, b);
+        if (!SELF) tma_load_4d(smem + L::q0_landing + s2 * kRowTile, &map_q0, &bar_q, s2 * 64, i0 - q_offset, 0, b);
       }
       load_k0(0);
       load_k(0);
@@ -569,15 +573,17 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     uint32_t r[DH];
     tmem_ld_n<DH>(lane_base + kColO + wg * DH, r);
     tmem_ld_wait();
-    if (i < seq) {
-      float4* orow = reinterpret_cast<float4*>(out + ((int64_t)n * seq + i) * D + wg * DH);
+    if (i < seq && i >= q_offset) {                            // rows before q_offset belong to an earlier call
+      const int iq = i - q_offset;                             // row inside the query tensor
+      const int q_rows = seq - q_offset;
+      float4* orow = reinterpret_cast<float4*>(out + ((int64_t)n * q_rows + iq) * D + wg * DH);
 #pragma unroll
       for (int d = 0; d < DH; d += 4)
         orow[d >> 2] = make_float4(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv,
                                    __uint_as_float(r[d + 2]) * inv, __uint_as_float(r[d + 3]) * inv);
-      if (wg == 0) lse2[(int64_t)n * seq + i] = run_max + log2f(den);
+      if (wg == 0) lse2[(int64_t)n * q_rows + iq] = run_max + log2f(den);
       if (out_lowp != nullptr) {                               // the same rows in the operand dtype, in the caller's layout
-        uint4* lrow = reinterpret_cast<uint4*>(out_lowp + out_lowp_rows.at(b, h, i) + wg * DH);
+        uint4* lrow = reinterpret_cast<uint4*>(out_lowp + out_lowp_rows.at(b, h, iq) + wg * DH);
 #pragma unroll
         for (int d = 0; d < DH; d += 8)
           lrow[d >> 3] = make_uint4(pack_bf16(__uint_as_float(r[d]) * inv, __uint_as_float(r[d + 1]) * inv),
@@ -595,15 +601,17 @@ __global__ void __launch_bounds__(kWideThreads, 1)
 template <int D>
 int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float* total, cudaStream_t s) {
   const int ntiles = (p.seq + kTile - 1) / kTile;
+  const int q_rows = p.seq - p.q_offset;                 // rows of the query tensor (all of them unless continuing a prefill)
+  const int mi_first = p.q_offset / kTile;               // first query tile with a row to compute
   CUtensorMap map_q, map_k128, map_v128;                 // boxes of 128 rows x 64 columns
-  int st = make_map_16bit(&map_q, p.q.ptr, D, p.seq, p.heads, p.batch, p.q.st, p.q.sh, p.q.sb, kTile);
+  int st = make_map_16bit(&map_q, p.q.ptr, D, q_rows, p.heads, p.batch, p.q.st, p.q.sh, p.q.sb, kTile);
   if (st != SA_OK) return st;
   st = make_map_16bit(&map_k128, p.k.ptr, D, p.seq, p.heads, p.batch, p.k.st, p.k.sh, p.k.sb, kTile);
   if (st != SA_OK) return st;
   st = make_map_16bit(&map_v128, p.v.ptr, D, p.seq, p.heads, p.batch, p.v.st, p.v.sh, p.v.sb, kTile);
   if (st != SA_OK) return st;
   CUtensorMap map_q0, map_k0;                            // the selector's rows: (d, token, 1, batch)
-  st = make_map_16bit(&map_q0, p.q0.ptr, D, p.seq, 1, p.batch, p.q0.st, 0, p.q0.sb, kTile);
+  st = make_map_16bit(&map_q0, p.q0.ptr, D, q_rows, 1, p.batch, p.q0.st, 0, p.q0.sb, kTile);
   if (st != SA_OK) return st;
   st = make_map_16bit(&map_k0, p.k0.ptr, D, p.seq, 1, p.batch, p.k0.st, 0, p.k0.sb, kTile);
   if (st != SA_OK) return st;
@@ -614,22 +622,23 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   constexpr int DK = D / 64;
   const int colsum_smem = 3 * DK * kRowTile + 1024;
   SA_CUDA_CHECK(cudaFuncSetAttribute(colsum_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, colsum_smem));
-  dim3 gc(ntiles, (ntiles + kColsumChunk - 1) / kColsumChunk, p.batch);
+  dim3 gc(ntiles, (ntiles - mi_first + kColsumChunk - 1) / kColsumChunk, p.batch);
   {
     ProfileScope prof(SA_KERNEL_TC_COLSUM, s);
     count_launch();
-    colsum_kernel<D><<<gc, 128, colsum_smem, s>>>(map_q0, map_k0, carry, p.seq, ntiles, p.exempt, p.scale, status);
+    colsum_kernel<D><<<gc, 128, colsum_smem, s>>>(map_q0, map_k0, carry, p.seq, ntiles, p.exempt, p.scale, status,
+                                                  p.q_offset, mi_first);
   }
   SA_CUDA_CHECK(cudaGetLastError());
   dim3 gs((p.seq + 255) / 256, p.batch);
   {
     ProfileScope prof(SA_KERNEL_TC_SCAN, s);
     count_launch();
-    scan_kernel<<<gs, 256, 0, s>>>(carry, total, p.seq, ntiles);
+    scan_kernel<<<gs, 256, 0, s>>>(carry, total, p.seq, ntiles, mi_first, p.carry_init, p.carry_init_stride);
   }
   SA_CUDA_CHECK(cudaGetLastError());
 
-  const unsigned grid = (unsigned)ntiles * p.batch * p.heads;
+  const unsigned grid = (unsigned)(ntiles - mi_first) * p.batch * p.heads;
   const bool self = (p.heads == 1) && !p.external_selector;   // one head per selector: the selection logits are the head's own
   {
     const int wide_smem = WideSmem<D>::total + 1024;
@@ -641,11 +650,11 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
       if (self)
         forward_wide_kernel<D, true><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2,
                                                                             p.heads, p.seq, ntiles, p.exempt, p.scale, status,
-                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows);
+                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows, p.q_offset);
       else
         forward_wide_kernel<D, false><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2,
                                                                              p.heads, p.seq, ntiles, p.exempt, p.scale, status,
-                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows);
+                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows, p.q_offset);
     }
     SA_CUDA_CHECK(cudaGetLastError());
     return SA_OK;

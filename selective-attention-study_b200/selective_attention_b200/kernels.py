@@ -518,6 +518,61 @@ def selective_attention_packed(qkv: torch.Tensor, exempt: int = 1) -> torch.Tens
 
 # ---- cached decode ------------------------------------------------------------------------------------
 
+def prefill_extend(cache: dict, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, exempt: int = 1) -> torch.Tensor:
+    """Continues a prefill: appends a chunk of new tokens to the cache and returns their outputs, (B, H, Tn, D)
+    fp32, as the full forward over cached + new tokens would give them; ``cache["selected"]`` and ``cache["len"]``
+    move on to the new length.  (The reference prefills from position 0 only and then decodes token by token,
+    ``mixers.py:105-130``; chunked prefill is what a serving loop does with a long prompt.)
+
+    cache: {"k", "v": (B, H, capacity, D) contiguous bf16, "len": int, "selected": (B, G, capacity) fp32} with G = 1
+    (head 0 selects) or G = H (every head its own selector).  q, k, v: (B, H, Tn, D).  bf16 operands on the
+    tensor-core engine only (head_dim 64 or 128)."""
+    lib = _lib.load()
+    exempt = _check_exempt(exempt)
+    kc, vc, selected = cache["k"], cache["v"], cache["selected"]
+    b, h, cap, d = kc.shape
+    cached, tn = int(cache["len"]), q.shape[2]
+    total_len = cached + tn
+    if total_len > cap:
+        raise ValueError("prefill past the cache capacity (context_length)")
+    if tuple(q.shape) != (b, h, tn, d) or k.shape != q.shape or v.shape != q.shape:
+        raise ValueError(f"q, k, v must all be (B, H, Tn, D) matching the cache; got {tuple(q.shape)}")
+    groups = selected.shape[1]
+    if not (kc.is_cuda and kc.dtype == torch.bfloat16 and vc.dtype == torch.bfloat16 and kc.is_contiguous()
+            and vc.is_contiguous() and selected.is_contiguous() and selected.dtype == torch.float32
+            and d in (64, 128) and groups in (1, h)):
+        raise ValueError("prefill_extend needs a contiguous bf16 CUDA cache with head_dim 64 or 128 and one selector "
+                         "per sequence or per head")
+    if cached == 0:
+        raise ValueError("the cache is empty: use selective_attention_forward(return_aux=True) for the first chunk")
+    kc[:, :, cached:total_len] = k
+    vc[:, :, cached:total_len] = v
+    qn = q.to(torch.bfloat16)
+    if groups == h and h > 1:             # every head is its own one-head sequence
+        qn = qn.reshape(b * h, 1, tn, d)
+        kv, vv = kc.view(b * h, 1, cap, d), vc.view(b * h, 1, cap, d)
+    else:
+        kv, vv = kc, vc
+    qn = _strided(qn, True)
+    bb, hh = qn.shape[0], qn.shape[1]
+    dev = kc.device
+    engine = _lib.ENGINE_TCGEN05
+    out = torch.empty(bb, hh, tn, d, device=dev, dtype=torch.float32)
+    lse2 = torch.empty(bb, hh, tn, device=dev, dtype=torch.float32)
+    carry = torch.empty(bb, lib.sa_carry_checkpoints(engine, total_len), total_len, device=dev, dtype=torch.float32)
+    total = torch.empty(bb, total_len, device=dev, dtype=torch.float32)
+    prob = _problem(qn, kv, vv, engine, exempt)
+    prob.seq = total_len
+    with torch.cuda.device(dev):
+        st = lib.sa_prefill_extend(ctypes.byref(prob), cached, qn.data_ptr(), kv.data_ptr(), vv.data_ptr(),
+                                   selected.data_ptr(), cap, out.data_ptr(), lse2.data_ptr(), carry.data_ptr(),
+                                   total.data_ptr(), _stream(dev))
+    _lib.check("sa_prefill_extend", st)
+    selected.view(bb, cap)[:, :total_len] = total
+    cache["len"] = total_len
+    return out.view(b, h, tn, d)
+
+
 def decode_step(cache: dict, q1: torch.Tensor, k1: torch.Tensor, v1: torch.Tensor, exempt: int = 1) -> torch.Tensor:
     """One cached decode step on the device (the reference does this with PyTorch ops,
     ``mixers.py:115-130`` and ``model.py:86-93``).

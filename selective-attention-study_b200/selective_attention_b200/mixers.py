@@ -6,6 +6,7 @@ the reference's layer can call it after ``_split_heads`` and before ``_merge_hea
 
     _attend      -> attend(q, k, v, want_total)            (reference :76-98)
     begin_cache  -> begin_cache(q, k, v, capacity)         (reference :105-113 with model.py:76-83)
+    (none)       -> extend_cache(q, k, v, cache)           a further prompt chunk; the reference prefills once
     step_cache   -> step_cache(q1, k1, v1, cache)          (reference :115-130 with model.py:86-93)
 
 Variants as in the reference (:16-22): "selective" (head 0 selects, <BOS> exempt), "selective_x16"
@@ -78,6 +79,11 @@ class SelectiveAttentionSlot:
         selected[:, :, :t] = total.float()
         cache["selected"] = selected
         return y, cache
+
+    def extend_cache(self, q, k, v, cache: dict):
+        """A further chunk of prompt tokens: (B, H, Tn, D) outputs in v's dtype; appends to the cache and moves
+        ``selected`` on.  Equals the rows a single prefill over all tokens would produce."""
+        return kernels.prefill_extend(cache, q, k, v, self.exempt).to(v.dtype)
 
     def step_cache(self, q1, k1, v1, cache: dict):
         """One token: (B, H, 1, D) in q1's dtype; appends to the cache and updates ``selected``."""

@@ -4,7 +4,7 @@ import pytest
 import torch
 
 import selective_oracle as oracle
-from selective_attention_b200 import mixers
+from selective_attention_b200 import _lib, mixers
 
 pytestmark = pytest.mark.gpu
 
@@ -55,3 +55,35 @@ def test_decode_over_several_splits(dtype, dim):
         tol = 2e-5 if dtype == torch.float32 else 2e-2
         torch.testing.assert_close(got.float().cpu(), want, atol=tol, rtol=tol)
     torch.testing.assert_close(dev["selected"].cpu(), ref["selected"], atol=1e-4, rtol=1e-4)
+
+
+@pytest.mark.parametrize("first,second,heads,per_head", [(256, 200, 3, False), (300, 333, 2, False), (130, 127, 2, True),
+                                                         (1000, 1049, 4, False)])
+def test_chunked_prefill_equals_one_prefill_and_then_decodes(first, second, heads, per_head):
+    """begin_cache on the first chunk + extend_cache on the second must give the rows and the per-key selection of a
+    single prefill over all tokens (cached length aligned to the 128-row tiles or not), and the cache must then decode
+    like the oracle's."""
+    from selective_attention_b200 import mixers
+    g = torch.Generator("cpu").manual_seed(first + second)
+    total = first + second
+    q, k, v = (torch.randn(2, heads, total + 1, 64, generator=g).bfloat16().cuda() for _ in range(3))
+    slot = mixers.SelectiveAttentionSlot(n_heads=heads, context_length=total + 8, per_head=per_head)
+    whole, whole_total = slot.attend(q[:, :, :total], k[:, :, :total], v[:, :, :total], want_total=True)
+    y1, cache = slot.begin_cache(q[:, :, :first], k[:, :, :first], v[:, :, :first])
+    y2 = slot.extend_cache(q[:, :, first:total], k[:, :, first:total], v[:, :, first:total], cache)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0 and cache["len"] == total
+    torch.testing.assert_close(y1.float(), whole[:, :, :first].float(), atol=0, rtol=0)
+    torch.testing.assert_close(y2.float(), whole[:, :, first:].float(), atol=2e-2, rtol=2e-2)
+    assert float((y2.float() - whole[:, :, first:].float()).norm() / whole[:, :, first:].float().norm()) < 2e-3
+    torch.testing.assert_close(cache["selected"][:, :, :total], whole_total, atol=1e-3, rtol=1e-4)
+    assert (cache["selected"][:, :, total:] == 0).all()
+    # one decode step on the extended cache against the oracle's step on a float copy of it
+    groups = heads if per_head else 1
+    ref = {"k": cache["k"].float().cpu().clone(), "v": cache["v"].float().cpu().clone(), "len": total,
+           "selected": cache["selected"].cpu().clone()}
+    want = oracle.decode_step(ref, q[:, :, total:].float().cpu(), k[:, :, total:].float().cpu(), v[:, :, total:].float().cpu(),
+                              groups=groups)
+    got = slot.step_cache(q[:, :, total:], k[:, :, total:], v[:, :, total:], cache)
+    torch.testing.assert_close(got.float().cpu(), want, atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(cache["selected"].cpu(), ref["selected"], atol=2e-3, rtol=1e-3)
