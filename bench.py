@@ -388,7 +388,7 @@ def run_ours(args, w, rank, world, device):
     # ---- end-to-end arm: host buffers in, host buffers out ------------------------------------------------
     # Whole sequences with a shared selector go through the layer-facing call: one packed (B, T, 3, H, D) projection
     # output and one (B, T, H D) cotangent in, the merged output and the packed gradient out (the same bytes).
-    packed = w["backward"] and not w["per_head"] and not sel_h and w["dim"] == 64
+    packed = w["backward"] and not w["per_head"] and not sel_h and w["dim"] == 64 and args.e2e_call == "packed"
     if packed:
         q_h, k_h, v_h, do_h = (t.transpose(1, 2) for t in (q_h, k_h, v_h, do_h))       # (B, T, H, D)
         qkv_h = torch.stack([q_h, k_h, v_h], dim=2).contiguous()                       # (B, T, 3, H, D)
@@ -842,6 +842,8 @@ def main():
     ap.add_argument("--batch", type=int, default=None, help="override B (profiling on a small case)")
     ap.add_argument("--layers", type=int, default=None, help="override the layer count of the c5 decoder")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--e2e-call", default="packed", choices=["packed", "plain"],
+                    help="end-to-end arm: the layer-facing packed call (default where it applies) or the (B, H, T, D) call")
     ap.add_argument("--no-reference-gpu", action="store_true",
                     help="--impl reference: skip timing the reference's Triton kernels on the GPU")
     ap.add_argument("--replicas", action="store_true",
