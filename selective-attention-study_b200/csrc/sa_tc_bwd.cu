@@ -24,9 +24,11 @@
 // are the head's own logits, so L0^T is S^T, and since Q0 = Q and K0 = K the two gradient paths add before the
 // MMAs: dK += (dz + g)^T Q and dQ = (dz + g) K.  40 MMAs per query tile instead of 64, no Q0 / K0 tiles, one
 // read-out per tile.
+//
+// Only the SELF variant is launched from this file.  A selector shared by several heads (or given separately) runs
+// backward_shared_kernel (sa_tc_bwd_shared.cu), which keeps this kernel's arithmetic and changes where the MMA
+// operands live and when the products are issued; the !SELF branches below are that kernel's starting point.
 // Reference for the arithmetic: src/selective_attention/kernels.py:196-268.
-#include <stdlib.h>
-
 #include "sa_tc_host.cuh"
 #include "sa_tc_ptx.cuh"
 
@@ -564,9 +566,10 @@ int backward_shared(const Problem& p, const float* lse2, const float* carry, con
 int backward(const Problem& p, const float* lse2, const float* carry, const float* dbar, const void* d_out_bf16,
              float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv, cudaStream_t s) {
   if (p.head_dim != 64) return SA_ERR_UNSUPPORTED;
-  // A selector shared by the heads: the form with two sets of score columns (sa_tc_bwd_shared.cu).
-  if (!((p.heads == 1) && !p.external_selector) && getenv("SA_B200_BWD_SINGLE_SET") == nullptr)
-    return backward_shared(p, lse2, carry, dbar, d_out_bf16, dq_acc, dk_acc, dq0, dk0, dv, s);
+  // A selector shared by several heads (or given separately) has its own kernel (sa_tc_bwd_shared.cu); the kernel of
+  // this file runs the one-head-per-selector form.
+  const bool self = (p.heads == 1) && !p.external_selector;
+  if (!self) return backward_shared(p, lse2, carry, dbar, d_out_bf16, dq_acc, dk_acc, dq0, dk0, dv, s);
   const int ntiles = (p.seq + kTile - 1) / kTile;
   const int nrows = p.batch * p.heads;
   CUtensorMap map_q, map_k, map_v, map_do, map_dq, map_dq0;
@@ -594,20 +597,13 @@ int backward(const Problem& p, const float* lse2, const float* carry, const floa
   const int smem = BwdSmem::total + 1024;
   // One head per selector (the per-head form): the selection logits are the head's own, and the kernel merges the
   // two gradient paths before the MMAs.
-  const bool self = (p.heads == 1) && !p.external_selector;
-  if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  else SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   {
     ProfileScope prof(SA_KERNEL_TC_BACKWARD, s);
     count_launch();
-    if (self)
-      backward_kernel<true><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
-          map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
-    else
-      backward_kernel<false><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
-          map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
+    backward_kernel<true><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
+        map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
+        static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
   }
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;
