@@ -87,3 +87,45 @@ def test_slot_falls_back_to_the_listing_off_device_like_the_reference(golden):
     torch.testing.assert_close(y, g["out"], atol=1e-5, rtol=1e-5)
     torch.testing.assert_close(total, g["total"], atol=1e-5, rtol=1e-5)
     assert mixers.MIXER_TYPES == ("selective", "selective_x16", "selective_perhead")
+
+
+def test_new_entry_points_check_their_arguments_before_any_launch():
+    """Selector, layout-fused and prefill-continuation entry points refuse bad arguments with a status (no GPU)."""
+    lib = _lib.load()
+    p = _lib.Problem()
+    p.struct_bytes = ctypes.sizeof(_lib.Problem)
+    p.dtype, p.engine, p.batch, p.heads, p.seq, p.head_dim, p.exempt = 1, 1, 1, 2, 256, 64, 1
+    sel = _lib.Selector()                                        # struct_bytes missing
+    assert lib.sa_forward_selector(ctypes.byref(p), 16, 16, 16, ctypes.byref(sel), 16, 16, 16, 16, None) == 1
+    sel.struct_bytes = ctypes.sizeof(_lib.Selector)              # null q0 / k0
+    assert lib.sa_forward_selector(ctypes.byref(p), 16, 16, 16, ctypes.byref(sel), 16, 16, 16, 16, None) == 1
+    assert ctypes.sizeof(_lib.Selector) == 8 + 2 * 8 + 4 * 8 and ctypes.sizeof(_lib.Tensor) == 8 + 8 + 3 * 8
+    low = _lib.Tensor()
+    low.ptr, low.dtype = 16, 0                                   # fp32 descriptor for a bf16 problem
+    low.stride[:] = [64 * 256 * 2, 64, 128]
+    assert lib.sa_forward_fused(ctypes.byref(p), 16, 16, 16, None, 16, ctypes.byref(low), 16, 16, 16, None) == 1
+    low.dtype = 1
+    low.stride[:] = [64 * 256 * 2, 64, 100]                      # token stride of 200 bytes: rows not 16-byte aligned
+    assert lib.sa_forward_fused(ctypes.byref(p), 16, 16, 16, None, 16, ctypes.byref(low), 16, 16, 16, None) == 3
+    p.engine = 0                                                 # the CUDA-core engine has no fused or continuation form
+    low.stride[:] = [64 * 256 * 2, 64, 128]
+    assert lib.sa_forward_fused(ctypes.byref(p), 16, 16, 16, None, 16, ctypes.byref(low), 16, 16, 16, None) == 2
+    assert lib.sa_prefill_extend(ctypes.byref(p), 128, 16, 16, 16, 16, 256, 16, 16, 16, 16, None) == 2
+    p.engine = 1
+    assert lib.sa_prefill_extend(ctypes.byref(p), 256, 16, 16, 16, 16, 256, 16, 16, 16, 16, None) == 1   # nothing new
+    assert lib.sa_prefill_extend(ctypes.byref(p), 128, 16, 16, 16, 16, 100, 16, 16, 16, 16, None) == 1   # selected too short
+    assert lib.sa_selection_carry(ctypes.byref(p), 16, 16, None, 16, 16, None) == 2                      # CUDA-core engine only
+    assert lib.sa_selftest_wait_timeout(0, None) == 1
+    assert lib.sa_launch_count() >= 0
+
+
+def test_selector_and_packed_arguments_are_validated_in_python():
+    q = torch.randn(1, 2, 64, 64)
+    with pytest.raises(ValueError, match="CUDA"):
+        kernels.selective_attention(q, q, q, selector=(q[:, 0], q[:, 0]))
+    assert not kernels.packed_supported(torch.randn(1, 64, 3, 2, 64))          # CPU, fp32
+    with pytest.raises(ValueError, match="contiguous bf16 CUDA"):
+        kernels.selective_attention_packed(torch.randn(1, 64, 3, 2, 64))
+    with pytest.raises(ValueError, match="carry_rows"):
+        kernels._carry_rows_request(64)
+    assert kernels._carry_rows_request(None) is None and kernels._carry_rows_request(32) == 32
