@@ -1,34 +1,41 @@
 // Tensor-core engine, backward (sm_100a: TMA loads and reduce-adds, tcgen05 MMAs, fp32 accumulators in TMEM).
 //
-// One CTA owns one 128-key tile of one head and walks the 128-query tiles LAST TO FIRST.  All
-// score-shaped tiles are computed transposed, KEYS on the TMEM lanes: S^T = K Q^T, dP^T = V dO^T,
-// L0^T = K0 Q0^T, so one thread owns one key and sees that key's queries along its registers.  The
-// two running sums down the query axis are then thread-local fp32 recurrences walked from the last
-// query to the first:
+// One CTA owns one 128-key tile of one head and walks the query tiles LAST TO FIRST in 64-query halves.  All
+// score-shaped tiles are computed transposed, KEYS on the TMEM lanes (S^T = K Q^T, dP^T = V dO^T, L0^T = K0 Q0^T), so
+// one thread owns one key and sees that key's queries along its registers.  The two running sums down the query
+// axis are then thread-local fp32 recurrences walked from the last query to the first:
 //     F[i]  = carry_after_tile - sum_{r >= i} sel[r]          (history term rebuilt per key)
 //     U[i]  = suffix + sum_{i' > i} dz[i']                      (logit gradient of later queries)
 // with  P = exp2(z - lse),  dz = P (dP - dbar),  g = gate ? -U : 0.
 //
-// Roles.  Warps 0-15 (four warpgroups) do the arithmetic: a query tile is handled as two 64-query
-// halves, and within a half each warpgroup takes 16 query columns of every key row; chunk totals are
-// exchanged through shared memory so the recurrences chain across chunks, halves and tiles.  Warp 16 is
-// the control warp: one lane issues every TMA load and every MMA, so MMA issue never stalls arithmetic.
+// Roles.  Warps 0-15 (four warpgroups) do the arithmetic: within a half each warpgroup takes 16 query columns of
+// every key row; chunk totals are exchanged through shared memory so the recurrences chain across chunks, halves
+// and tiles.  Warp 16 is the control warp: one lane issues every TMA load and every MMA.
 //
-// Products per query tile (all on tcgen05, fp32 accumulation in TMEM):
-//     per half : S^T, dP^T, L0^T (N = 64);  dV += P^T dO with P^T read from TMEM as bf16;
-//                dK += dz^T Q;  dK0 += g^T Q0
-//     per tile : dQ = dz K;  dQ0 = g K0  (dz, g read from shared memory M-major) -> scaled, staged in
-//                shared memory and added to the fp32 global accumulators with TMA reduce-add.
+// Operand sources and issue points.  Measured on B200, a head-tile of a form with every operand in shared memory and
+// each product issued when its inputs appear costs ~10.5 k cycles of which the arithmetic is ~3 k and the MMAs ~4 k;
+// the rest is hand-over latency, because every product the arithmetic warps wait for is issued only after an arrival
+// of theirs has travelled to the control warp and the MMA's completion has travelled back.  Here each such product is
+// issued one arithmetic pass EARLIER than it is needed, into columns that are free by then:
+//     L0^T of half n + 1 -> Z   when the selection pass of half n has read Z
+//     S^T  of half n + 1 -> Y   when P^T and dz^T of half n (which live in Y) have been handed to dV and dK
+//     dP^T of half n + 1 -> X   when g^T of half n (which lives in X) has been handed to dK0
+// K and V sit in TMEM as bf16 pairs (A of S^T and dP^T); P^T, dz^T and g^T are written by each thread as bf16 pairs
+// over the score columns that SAME thread has just read (its 16 columns of Y hold P^T then dz^T, 8 packed columns
+// each; its 16 columns of X hold g^T), so no barrier is needed between reading a score tile and overwriting it, and
+// dV, dK, dK0 read their A operand from TMEM with a stride of 16 columns per 16-query step.  L0^T = K0 Q0^T and the
+// per-tile dQ = dz K, dQ0 = g K0 take both operands from shared memory.  TMEM, 512 columns: K, V (32 each) | dV, dK,
+// dK0 | Z | X | Y | one accumulator shared by dQ and dQ0 (64 each): dQ is read out at the tile's end, dQ0 in the
+// middle of the next tile's first half.  The query-side tiles (Q, Q0, dO) arrive per half through a ring of three
+// 24 KB slots; dQ / dQ0 leave through their own fp32 staging tile and TMA reduce-add.
 //
-// SELF variant (one head per selector, i.e. the per-head form reshaped to (B H, 1, T, D)): the selection logits
-// are the head's own logits, so L0^T is S^T, and since Q0 = Q and K0 = K the two gradient paths add before the
-// MMAs: dK += (dz + g)^T Q and dQ = (dz + g) K.  40 MMAs per query tile instead of 64, no Q0 / K0 tiles, one
-// read-out per tile.
+// SELF variant (one head per selector, i.e. the per-head form reshaped to (B H, 1, T, D)): the selection logits are the
+// head's own logits, so S^T serves as L0^T, and since Q0 = Q and K0 = K the two gradient paths add before the MMAs:
+// dK += (dz + g)^T Q and dQ = (dz + g) K, with (dz + g)^T in this thread's X columns.  40 MMAs per query tile instead
+// of 64, no Q0 / K0 tiles, no Z, one read-out per tile (deferred into the next tile's first half).
 //
-// Only the SELF variant is launched from this file.  A selector shared by several heads (or given separately) runs
-// backward_shared_kernel (sa_tc_bwd_shared.cu), which keeps this kernel's arithmetic and changes where the MMA
-// operands live and when the products are issued; the !SELF branches below are that kernel's starting point.
-// Reference for the arithmetic: src/selective_attention/kernels.py:196-268.
+// Reference for the arithmetic: src/selective_attention/kernels.py:196-268 (one head), :271-364 (the shared
+// selection-gradient products).
 #include "sa_tc_host.cuh"
 #include "sa_tc_ptx.cuh"
 
@@ -37,12 +44,14 @@ namespace tc {
 namespace {
 
 constexpr int kTile = 128;
-constexpr int kRowTile = 16384;     // bytes of a [128][64] bf16 operand tile
-constexpr int kGroups = 4;          // arithmetic warpgroups; each owns 16 of a half's 64 query columns
+constexpr int kRowTile = 16384;      // bytes of a [128][64] bf16 operand tile
+constexpr int kHalfTile = 8192;      // bytes of a [64][64] bf16 operand tile
+constexpr int kGroups = 4;           // arithmetic warpgroups; each owns 16 of a half's 64 query columns
 constexpr int kChunk = 64 / kGroups;
 constexpr int kComputeThreads = 128 * kGroups;
 constexpr int kThreads = kComputeThreads + 32;
-constexpr int kComputeBarrier = 1;  // hardware barrier id of the arithmetic warps
+constexpr int kComputeBarrier = 1;   // hardware barrier id of the arithmetic warps
+constexpr int kRing = 3;             // half-tile slots of Q, Q0, dO in flight
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
@@ -50,27 +59,26 @@ __device__ __forceinline__ float ex2(float x) {
   return y;
 }
 
-// A global load the compiler must issue where it is written (volatile asm keeps its place among the other
-// volatile asm statements), so a value fetched one tile ahead is really in flight during that tile.
 __device__ __forceinline__ float load_ahead(const float* p) {
   float v;
   asm volatile("ld.global.nc.f32 %0, [%1];" : "=f"(v) : "l"(p));
   return v;
 }
 
-struct BwdSmem {
-  static constexpr int k = 0;                       // [128 keys][64], stationary
+struct Smem {
+  static constexpr int k = 0;                              // [128 keys][64], stationary
   static constexpr int v = k + kRowTile;
   static constexpr int k0 = v + kRowTile;
-  static constexpr int stage = k0 + kRowTile;       // 2 stages x (Q, Q0, dO) tiles [128 queries][64]
-  static constexpr int dz = stage + 6 * kRowTile;   // [128 keys][128 queries] bf16 as two query-half tiles;
-  static constexpr int g = dz + 2 * kRowTile;       //   after the tile's MMAs: fp32 staging of dQ / dQ0
-  static constexpr int total = g + 2 * kRowTile;
+  static constexpr int ring = k0 + kRowTile;               // kRing x (Q, Q0, dO) half tiles [64 queries][64]
+  static constexpr int dz = ring + kRing * 3 * kHalfTile;  // [128 keys][128 queries] bf16 as two query-half tiles
+  static constexpr int g = dz + 2 * kRowTile;
+  static constexpr int out = g + 2 * kRowTile;             // fp32 [128 queries][64] as two [128][32] boxes
+  static constexpr int total = out + 2 * kRowTile;         // 216 KB
 };
 
-// TMEM columns.  L0T doubles as the home of P^T (bf16 pairs, 32 columns) once L0^T has been read.
-constexpr uint32_t kColST = 0, kColDPT = 64, kColL0T = 128, kColDV = 192, kColDK = 256, kColDK0 = 320, kColDQ = 384,
-                   kColDQ0 = 448;
+// TMEM columns
+constexpr uint32_t kColK = 0, kColV = 32, kColDV = 64, kColDK = 128, kColDK0 = 192, kColZ = 256, kColX = 320, kColY = 384,
+                   kColDQ = 448;
 
 // Writes 8 consecutive bf16 (query columns c0 .. c0 + 7 of key row `row`) of a [128][128] matrix kept
 // as two 64-column tiles.
@@ -79,47 +87,61 @@ __device__ __forceinline__ void put8(uint8_t* base, int row, int c0, const float
   *reinterpret_cast<uint4*>(base + (c0 >> 6) * kRowTile + swz_off(row, (c0 & 63) >> 3)) = w;
 }
 
-struct HalfCtx {
-  uint8_t* smem;
-  uint32_t lane_base;
-  int row;                 // key row of this thread inside the tile (its TMEM lane)
-  int wg;                  // warpgroup: which 16-column chunk of the half
-  int hf;                  // which half of the query tile
-  bool selectable;         // key >= exempt
-  float cnl;               // log2(e) * selection received through the END of this query tile
-  float c1;                // scale * log2(e)
-  const float* lse_s;      // -lse2 of the tile's queries (padded queries: -inf)
-  const float* dbar_s;     // -dbar
-  float (*sel_tot)[kTile];
-  float (*dz_tot)[kTile];
-  uint64_t* bar_early;     // arrived once per half when P^T and dz are in place and the score columns are free
-  bool drain_reduce;       // first half of a tile: the previous tile's reduce-adds still read the dz / g buffers
+__device__ __forceinline__ void put_words(uint8_t* base, int row, int c0, const uint32_t* w) {
+  *reinterpret_cast<uint4*>(base + (c0 >> 6) * kRowTile + swz_off(row, (c0 & 63) >> 3)) = make_uint4(w[0], w[1], w[2], w[3]);
+}
+
+struct HalfState {
+  float negon[16];     // -1 where the (query, key) pair is selected, else 0
+  float lx[16];        // exclusive suffix sums of dz inside this thread's chunk
+  float dz[16];        // one head per selector only: dz, which the g pass adds to g before the products
 };
 
-// One 64-query half of a (key tile, query tile) pair; this thread handles 16 of its query columns for
-// its key row.  The two running sums run from the last query to the first; a chunk computes them
-// locally (two independent chains of 8) and picks up the totals of the chunks to its right, and the
-// carried state, through shared memory.
-template <bool DIAG, bool SELF>
-__device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state, float& dz_state) {
-  using L = BwdSmem;
-  const int colw = c.wg * kChunk;
-  const int col0 = c.hf * 64 + colw;
-  uint32_t r[16];
-  float negon[16], ls[16], p[16], lx[16];
+struct Ctx {
+  uint8_t* smem;
+  uint32_t tmem, lane_base;
+  int row, wg;
+  bool selectable;
+  float c1;
+  const float* lse_s;
+  const float* dbar_s;
+  float (*sel_tot)[kTile];
+  float (*dz_tot)[kTile];
+  WaitCtx status;
+};
 
-  tmem_ld16(c.lane_base + (SELF ? kColST : kColL0T) + colw, r);
+// First part of a half: selection pass, probabilities, dz.  Leaves P^T and dz^T in this thread's columns of Y (bf16
+// pairs), the dz half tile in shared memory, and returns what the g pass needs.
+template <bool DIAG, bool SELF>
+__device__ __forceinline__ void half_scores(const Ctx& c, int hf, uint32_t phase, float cnl, float& sel_state,
+                                            HalfState& st, uint64_t* bar_l0, uint64_t* bar_sel, uint64_t* bar_s,
+                                            uint64_t* bar_dp, uint64_t* bar_early, bool drain_reduce) {
+  using L = Smem;
+  const int colw = c.wg * kChunk;
+  const int col0 = hf * 64 + colw;
+  uint32_t r[16];
+  float ls[16], p[16];
+
+  if (SELF) {                                               // the selection logits are the head's own: S^T serves both
+    mbar_wait(bar_s, phase, c.status, 416);
+    tc_fence_after_sync();
+    tmem_ld16(c.lane_base + kColY + colw, r);
+  } else {
+    mbar_wait(bar_l0, phase, c.status, 410);
+    tc_fence_after_sync();
+    tmem_ld16(c.lane_base + kColZ + colw, r);               // L0^T
+  }
   tmem_ld_wait();
 #pragma unroll
   for (int e = 0; e < 16; ++e) {
     const float l0 = __uint_as_float(r[e]);
     bool on = c.selectable && (l0 > 0.f);
-    if (DIAG) on = on && (c.row < col0 + e);          // key strictly before the query
-    negon[e] = on ? -1.f : 0.f;
+    if (DIAG) on = on && (c.row < col0 + e);                // key strictly before the query
+    st.negon[e] = on ? -1.f : 0.f;
     ls[e] = on ? l0 : 0.f;
   }
 #pragma unroll
-  for (int e = 6; e >= 0; --e) {                        // inclusive suffix sums, two chains
+  for (int e = 6; e >= 0; --e) {                            // inclusive suffix sums, two chains
     ls[e] += ls[e + 1];
     ls[e + 8] += ls[e + 9];
   }
@@ -127,9 +149,8 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   for (int e = 0; e < 8; ++e) ls[e] += ls[8];
   c.sel_tot[c.wg][c.row] = ls[0];
   tc_fence_before_sync();
-  if (c.drain_reduce && threadIdx.x == 0) bulk_wait_read();
-  named_barrier(kComputeBarrier, kComputeThreads);      // also: every thread has finished reading L0^T
-  tc_fence_after_sync();
+  named_barrier(kComputeBarrier, kComputeThreads);          // every thread has read L0^T
+  if (!SELF && threadIdx.x == 0) mbar_arrive(bar_sel);      // Z may now receive the next half's L0^T
   float later = 0.f, all = 0.f;
 #pragma unroll
   for (int w = 0; w < kGroups; ++w) {
@@ -138,39 +159,44 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
     if (w > c.wg) later += t;
   }
   // F * log2e = cnl - c1 * (sel_state + later + ls[e]);   z = S * c1 - F * log2e - lse
-  const float cb = c.cnl - c.c1 * (sel_state + later);
+  const float cb = cnl - c.c1 * (sel_state + later);
   sel_state += all;
 
-  tmem_ld16(c.lane_base + kColST + colw, r);
-  tmem_ld_wait();
-  // Packed fp32x2 arithmetic (two results per issue slot) for the elementwise parts.
+  if (!SELF) {
+    mbar_wait(bar_s, phase, c.status, 416);
+    tc_fence_after_sync();
+    tmem_ld16(c.lane_base + kColY + colw, r);               // S^T
+    tmem_ld_wait();
+  }
   const float2 cc = make_float2(c.c1, c.c1);
   const float2 ncb = make_float2(-cb, -cb);
 #pragma unroll
-  for (int e4 = 0; e4 < 16; e4 += 4) {                  // row statistics: one 16-byte broadcast load per 4 queries
+  for (int e4 = 0; e4 < 16; e4 += 4) {
     const float4 st4 = *reinterpret_cast<const float4*>(c.lse_s + col0 + e4);
-    const float2 st[2] = {make_float2(st4.x, st4.y), make_float2(st4.z, st4.w)};
+    const float2 sv[2] = {make_float2(st4.x, st4.y), make_float2(st4.z, st4.w)};
 #pragma unroll
     for (int k = 0; k < 2; ++k) {
       const int e = e4 + 2 * k;
-      const float2 t2 = __ffma2_rn(cc, make_float2(ls[e], ls[e + 1]), __fadd2_rn(st[k], ncb));     // c1 ls - (cb + lse)
+      const float2 t2 = __ffma2_rn(cc, make_float2(ls[e], ls[e + 1]), __fadd2_rn(sv[k], ncb));     // c1 ls - (cb + lse)
       const float2 x = __ffma2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])), cc, t2);
       p[e] = ex2(x.x);
       p[e + 1] = ex2(x.y);
-      if (DIAG) {                                       // key after the query
+      if (DIAG) {                                           // key after the query
         if (c.row > col0 + e) p[e] = 0.f;
         if (c.row > col0 + e + 1) p[e + 1] = 0.f;
       }
     }
   }
-  {                                                     // P^T as bf16 pairs into the (consumed) L0^T columns
+  {                                                         // P^T as bf16 pairs over the first half of this thread's S^T
     uint32_t w8[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) w8[e] = pack_bf16(p[2 * e], p[2 * e + 1]);
-    tmem_st8(c.lane_base + kColL0T + (colw >> 1), w8);
+    tmem_st8(c.lane_base + kColY + colw, w8);
   }
 
-  tmem_ld16(c.lane_base + kColDPT + colw, r);
+  mbar_wait(bar_dp, phase, c.status, 411);
+  tc_fence_after_sync();
+  tmem_ld16(c.lane_base + kColX + colw, r);                 // dP^T
   tmem_ld_wait();
 #pragma unroll
   for (int e4 = 0; e4 < 16; e4 += 4) {
@@ -183,29 +209,43 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
                                             make_float2(st4.z, st4.w)));
     p[e4] = d0.x; p[e4 + 1] = d0.y; p[e4 + 2] = d1.x; p[e4 + 3] = d1.y;
   }
-  if (!SELF) {
-    put8(c.smem + L::dz, c.row, col0, p);
-    put8(c.smem + L::dz, c.row, col0 + 8, p + 8);
+  if (SELF) {                                               // dz + g leaves in the g pass
+#pragma unroll
+    for (int e = 0; e < 16; ++e) st.dz[e] = p[e];
+  } else {                                                  // dz: bf16 once, to TMEM (A of dK) and shared memory (A of dQ)
+    uint32_t w8[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) w8[e] = pack_bf16(p[2 * e], p[2 * e + 1]);
+    tmem_st8(c.lane_base + kColY + colw + 8, w8);           //   over the second half of this thread's S^T
+    put_words(c.smem + L::dz, c.row, col0, w8);
+    put_words(c.smem + L::dz, c.row, col0 + 8, w8 + 4);
   }
 
-  lx[15] = 0.f;                                          // exclusive suffix sums of dz, two chains
-  lx[7] = 0.f;
+  st.lx[15] = 0.f;                                          // exclusive suffix sums of dz, two chains
+  st.lx[7] = 0.f;
 #pragma unroll
   for (int e = 6; e >= 0; --e) {
-    lx[e] = lx[e + 1] + p[e + 1];
-    lx[e + 8] = lx[e + 9] + p[e + 9];
+    st.lx[e] = st.lx[e + 1] + p[e + 1];
+    st.lx[e + 8] = st.lx[e + 9] + p[e + 9];
   }
-  const float tot_hi = lx[8] + p[8];
+  const float tot_hi = st.lx[8] + p[8];
 #pragma unroll
-  for (int e = 0; e < 8; ++e) lx[e] += tot_hi;
-  c.dz_tot[c.wg][c.row] = lx[0] + p[0];
-  fence_async_smem();                                    // dz tile half -> visible to the MMAs
-  tmem_st_wait();                                        // P^T in TMEM
+  for (int e = 0; e < 8; ++e) st.lx[e] += tot_hi;
+  c.dz_tot[c.wg][c.row] = st.lx[0] + p[0];
+  fence_async_smem();                                       // dz half tile -> visible to the MMAs
+  tmem_st_wait();                                           // P^T and dz^T in TMEM
   tc_fence_before_sync();
-  named_barrier(kComputeBarrier, kComputeThreads);      // every thread is done with S^T, dP^T and L0^T
-  if (threadIdx.x == 0) mbar_arrive(c.bar_early);
-  later = 0.f;
-  all = 0.f;
+  if (drain_reduce && threadIdx.x == 0) bulk_wait_read();   // the staging tile's last reduce-add has read it
+  named_barrier(kComputeBarrier, kComputeThreads);          // every thread is done with S^T and dP^T
+  if (threadIdx.x == 0) mbar_arrive(bar_early);
+}
+
+// Second part of a half: g = gate ? -(sum of dz over later queries, all in this head) : 0 into shared memory.
+template <bool SELF>
+__device__ __forceinline__ void half_gate(const Ctx& c, int hf, float& dz_state, HalfState& st) {
+  using L = Smem;
+  const int col0 = hf * 64 + c.wg * kChunk;
+  float later = 0.f, all = 0.f;
 #pragma unroll
   for (int w = 0; w < kGroups; ++w) {
     const float t = c.dz_tot[w][c.row];
@@ -215,24 +255,23 @@ __device__ __forceinline__ void process_half(const HalfCtx& c, float& sel_state,
   const float base = dz_state + later;
   dz_state += all;
   const float2 bb = make_float2(base, base);
-  if (SELF) {
 #pragma unroll
-    for (int e = 0; e < 16; e += 2) {                                                              // dz + g
-      const float2 x = __ffma2_rn(make_float2(negon[e], negon[e + 1]), __fadd2_rn(make_float2(lx[e], lx[e + 1]), bb),
-                                  make_float2(p[e], p[e + 1]));
-      lx[e] = x.x; lx[e + 1] = x.y;
-    }
-    put8(c.smem + L::dz, c.row, col0, lx);
-    put8(c.smem + L::dz, c.row, col0 + 8, lx + 8);
-  } else {
-#pragma unroll
-    for (int e = 0; e < 16; e += 2) {                                                              // g
-      const float2 x = __fmul2_rn(make_float2(negon[e], negon[e + 1]), __fadd2_rn(make_float2(lx[e], lx[e + 1]), bb));
-      lx[e] = x.x; lx[e + 1] = x.y;
-    }
-    put8(c.smem + L::g, c.row, col0, lx);
-    put8(c.smem + L::g, c.row, col0 + 8, lx + 8);
+  for (int e = 0; e < 16; e += 2) {
+    float2 x;
+    if (SELF)                                                    // dz + g: Q0 = Q and K0 = K, so the two gradient paths add
+      x = __ffma2_rn(make_float2(st.negon[e], st.negon[e + 1]), __fadd2_rn(make_float2(st.lx[e], st.lx[e + 1]), bb),
+                     make_float2(st.dz[e], st.dz[e + 1]));
+    else
+      x = __fmul2_rn(make_float2(st.negon[e], st.negon[e + 1]), __fadd2_rn(make_float2(st.lx[e], st.lx[e + 1]), bb));
+    st.lx[e] = x.x; st.lx[e + 1] = x.y;
   }
+  uint32_t w8[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) w8[e] = pack_bf16(st.lx[2 * e], st.lx[2 * e + 1]);
+  tmem_st8(c.lane_base + kColX + c.wg * kChunk, w8);             // g^T (or (dz + g)^T) over this thread's dP^T columns
+  put_words(c.smem + (SELF ? L::dz : L::g), c.row, col0, w8);    // g: A of dQ0 (dz + g: A of dQ)
+  put_words(c.smem + (SELF ? L::dz : L::g), c.row, col0 + 8, w8 + 4);
+  tmem_st_wait();
 }
 
 template <bool SELF>
@@ -244,17 +283,24 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     const float* __restrict__ lse2, const float* __restrict__ carry, const float* __restrict__ dbar,
     float* __restrict__ dk_acc, float* __restrict__ dk0, __nv_bfloat16* __restrict__ dv, int heads, int seq,
     int ntiles, int exempt, float scale, WaitCtx status, RowLayout dv_rows) {
-  using L = BwdSmem;
+  using L = Smem;
   constexpr int D = 64;
-  const int nrows = gridDim.x / ntiles;                  // batch * heads
-  const int nj = (int)(blockIdx.x / nrows);              // key tiles with the most query tiles first
-  const int n = blockIdx.x % nrows;
+  // One (batch, head) row after the other, and within a row the key tiles with the most query tiles first: the CTAs
+  // resident at one time belong to one or two rows and walk the same query tiles from the last one down, so every
+  // Q, Q0, dO tile is fetched from DRAM once and then served from L2 to the row's other CTAs.
+  const int n = (int)(blockIdx.x / ntiles);
+  const int nj = (int)(blockIdx.x % ntiles);
   const int b = n / heads, h = n - b * heads;
   const int n_iter = ntiles - nj;
+  const int n_half = 2 * n_iter;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-  __shared__ uint64_t bar_kv, bar_ld[2], bar_a, bar_b, bar_dq, bar_half[2], bar_early;
+  // Completion barriers (MMA commits and TMA loads) and arrival barriers (arithmetic warps).  bar_l0 .. bar_g complete
+  // one phase per half; each side reaches its next wait on one of them only after the other side has consumed the
+  // previous phase, so a poller can never see two phases complete between two polls.
+  __shared__ uint64_t bar_kv, bar_setup, bar_ld[kRing], bar_free[kRing], bar_l0, bar_s, bar_dp, bar_sel, bar_early, bar_g,
+      bar_dq, bar_dq0, bar_dqread, bar_dq0read, bar_fin;
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(16) float lse_s[kTile];
   __shared__ __align__(16) float dbar_s[kTile];
@@ -264,17 +310,22 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
     mbar_init(&bar_kv, 1);
-    mbar_init(&bar_ld[0], 1);
-    mbar_init(&bar_ld[1], 1);
-    mbar_init(&bar_a, 1);
-    mbar_init(&bar_b, 1);
-    mbar_init(&bar_dq, 1);
-    // bar_half: one per half, each used once per tile, so the waiter can never see one complete two phases between
-    // two of its polls.  bar_early needs no such split: each arrival needs scores that are issued after the
-    // previous arrival was observed.
-    mbar_init(&bar_half[0], kComputeThreads / 32);
-    mbar_init(&bar_half[1], kComputeThreads / 32);
+    for (int u = 0; u < kRing; ++u) {
+      mbar_init(&bar_ld[u], 1);
+      mbar_init(&bar_free[u], 1);
+    }
+    mbar_init(&bar_setup, kComputeThreads / 32);
+    mbar_init(&bar_l0, 1);
+    mbar_init(&bar_s, 1);
+    mbar_init(&bar_dp, 1);
+    mbar_init(&bar_sel, 1);
     mbar_init(&bar_early, 1);
+    mbar_init(&bar_g, kComputeThreads / 32);
+    mbar_init(&bar_dq, 1);
+    mbar_init(&bar_dq0, 1);
+    mbar_init(&bar_dqread, 1);
+    mbar_init(&bar_dq0read, 1);
+    mbar_init(&bar_fin, 1);
     mbar_init_fence();
   }
   if (warp == 0) tmem_alloc(&tmem_base_s, 512);
@@ -290,131 +341,153 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       const uint32_t idesc_t = instr_desc_bf16(128, 64, false, false);     // keys x 64 queries, K = D
       const uint32_t idesc_acc = instr_desc_bf16(128, 64, false, true);    // A K-major (keys x queries), B MN-major
       const uint32_t idesc_dq = instr_desc_bf16(128, 64, true, true);      // A MN-major (queries x keys), B MN-major
-      auto load_stage = [&](int it) {
-        const int mi = ntiles - 1 - it;
-        uint8_t* st = smem + L::stage + (it & 1) * 3 * kRowTile;
-        mbar_expect_tx(&bar_ld[it & 1], (SELF ? 2 : 3) * kRowTile);
-        tma_load_4d(st, &map_q, &bar_ld[it & 1], 0, mi * kTile, h, b);
-        if (!SELF) tma_load_4d(st + kRowTile, &map_q0, &bar_ld[it & 1], 0, mi * kTile, 0, b);
-        tma_load_4d(st + 2 * kRowTile, &map_do, &bar_ld[it & 1], 0, mi * kTile, n, 0);
+      // Half index hn counts from the last query half: tile it = hn / 2 (query tile ntiles - 1 - it), upper half of
+      // the tile first.  Its operands sit in ring slot hn % kRing.
+      auto load_half = [&](int hn) {
+        const int it = hn >> 1, hf = 1 - (hn & 1), slot = hn % kRing;
+        const int row0 = (ntiles - 1 - it) * kTile + hf * 64;
+        uint8_t* st = smem + L::ring + slot * 3 * kHalfTile;
+        mbar_expect_tx(&bar_ld[slot], (SELF ? 2 : 3) * kHalfTile);
+        tma_load_4d(st, &map_q, &bar_ld[slot], 0, row0, h, b);
+        if (!SELF) tma_load_4d(st + kHalfTile, &map_q0, &bar_ld[slot], 0, row0, 0, b);
+        tma_load_4d(st + 2 * kHalfTile, &map_do, &bar_ld[slot], 0, row0, n, 0);
       };
-      // Operand descriptors are built once; an MMA's descriptor is a base plus a byte offset / 16, so the
-      // issuing thread spends a couple of integer adds per MMA instead of rebuilding 64-bit descriptors.
       auto at = [](uint64_t desc, uint32_t byte_off) { return desc + (uint64_t)(byte_off >> 4); };
-      const uint64_t kK = smem_desc(sa + L::k, 16, 1024), kV = smem_desc(sa + L::v, 16, 1024),
-                     kK0 = smem_desc(sa + L::k0, 16, 1024);                                   // K-major A (scores)
+      const uint64_t kK0 = smem_desc(sa + L::k0, 16, 1024);                   // K-major A of L0^T
       const uint64_t mK = smem_desc(sa + L::k, kRowTile, 1024), mK0 = smem_desc(sa + L::k0, kRowTile, 1024);
-      const uint64_t kDZ = smem_desc(sa + L::dz, 16, 1024), kG = smem_desc(sa + L::g, 16, 1024);   // K-major A
       const uint64_t mDZ = smem_desc(sa + L::dz, kRowTile, 1024), mG = smem_desc(sa + L::g, kRowTile, 1024);
-      const uint64_t kStage = smem_desc(sa + L::stage, 16, 1024);            // Q, Q0, dO of stage 0, K-major B
-      const uint64_t mStage = smem_desc(sa + L::stage, kRowTile, 1024);      // the same tiles as "K rows" operands
-      // S^T, dP^T, L0^T of one 64-query half
-      auto issue_scores = [&](int it, int hf) {
-        const uint32_t st = (it & 1) * 3 * kRowTile + hf * 8192;                   // rows 64 hf .. 64 hf + 63
-        if (!SELF) {
+      const uint64_t kRingD = smem_desc(sa + L::ring, 16, 1024);             // Q, Q0, dO half tiles as K-major B
+      const uint64_t mRingD = smem_desc(sa + L::ring, kRowTile, 1024);       // the same tiles as "K rows" operands
+      auto ring_off = [](int hn) { return (uint32_t)((hn % kRing) * 3 * kHalfTile); };
+      auto issue_l0 = [&](int hn) {                                          // L0^T -> Z (both operands in shared memory)
+        const uint32_t st = ring_off(hn);
+        mbar_wait(&bar_ld[hn % kRing], (uint32_t)((hn / kRing) & 1), status, 401);
+        tc_fence_after_sync();
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)
-            mma_ss(tmem + kColL0T, at(kK0, ks * 32), at(kStage, st + kRowTile + ks * 32), idesc_t, ks > 0);
+        for (int ks = 0; ks < 4; ++ks)
+          mma_ss(tmem + kColZ, at(kK0, ks * 32), at(kRingD, st + kHalfTile + ks * 32), idesc_t, ks > 0);
+        mma_commit(&bar_l0);
+      };
+      auto issue_s = [&](int hn) {                                           // S^T -> Y (A = K from TMEM)
+        const uint32_t st = ring_off(hn);
+        if (SELF) {                                                          // (otherwise issue_l0 has waited for the slot)
+          mbar_wait(&bar_ld[hn % kRing], (uint32_t)((hn / kRing) & 1), status, 401);
+          tc_fence_after_sync();
         }
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColST, at(kK, ks * 32), at(kStage, st + ks * 32), idesc_t, ks > 0);
-#pragma unroll
-        for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColDPT, at(kV, ks * 32), at(kStage, st + 2 * kRowTile + ks * 32), idesc_t, ks > 0);
-        mma_commit(&bar_a);
+          mma_ts(tmem + kColY, tmem + kColK + ks * 8, at(kRingD, st + ks * 32), idesc_t, ks > 0);
+        mma_commit(&bar_s);
       };
-      // dV += P^T dO over the half's 64 queries, P^T from TMEM
-      auto issue_dv = [&](int it, int hf, bool first) {
-        const uint32_t st = (it & 1) * 3 * kRowTile + hf * 8192;
+      auto issue_dp = [&](int hn) {                                          // dP^T -> X (A = V from TMEM)
+        const uint32_t st = ring_off(hn);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ts(tmem + kColDV, tmem + kColL0T + ks * 8, at(mStage, st + 2 * kRowTile + ks * 2048), idesc_acc,
-                 (first && ks == 0) ? 0u : 1u);
+          mma_ts(tmem + kColX, tmem + kColV + ks * 8, at(kRingD, st + 2 * kHalfTile + ks * 32), idesc_t, ks > 0);
+        mma_commit(&bar_dp);
       };
-      // dK += dz^T Q and dK0 += g^T Q0 over the half's 64 queries
-      auto issue_dk_only = [&](int it, int hf, bool first) {
-        const uint32_t st = (it & 1) * 3 * kRowTile + hf * 8192;
+      // dV += P^T dO; dK += dz^T Q: A from TMEM, 16 queries = 8 packed columns at a stride of 16 columns
+      auto issue_dv_dk = [&](int hn) {
+        const uint32_t st = ring_off(hn);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColDK, at(kDZ, hf * kRowTile + ks * 32), at(mStage, st + ks * 2048), idesc_acc,
-                 (first && ks == 0) ? 0u : 1u);
+          mma_ts(tmem + kColDV, tmem + kColY + ks * 16, at(mRingD, st + 2 * kHalfTile + ks * 2048), idesc_acc,
+                 (hn == 0 && ks == 0) ? 0u : 1u);
+#pragma unroll
+        for (int ks = 0; ks < 4; ++ks)
+          mma_ts(tmem + kColDK, tmem + kColY + ks * 16 + 8, at(mRingD, st + ks * 2048), idesc_acc,
+                 (hn == 0 && ks == 0) ? 0u : 1u);
       };
-      auto issue_dk0_only = [&](int it, int hf, bool first) {
-        const uint32_t st = (it & 1) * 3 * kRowTile + hf * 8192;
+      auto issue_dk0 = [&](int hn) {                                         // dK0 += g^T Q0 (A from TMEM)
+        const uint32_t st = ring_off(hn);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)
-          mma_ss(tmem + kColDK0, at(kG, hf * kRowTile + ks * 32), at(mStage, st + kRowTile + ks * 2048), idesc_acc,
-                 (first && ks == 0) ? 0u : 1u);
+          mma_ts(tmem + kColDK0, tmem + kColX + ks * 16, at(mRingD, st + kHalfTile + ks * 2048), idesc_acc,
+                 (hn == 0 && ks == 0) ? 0u : 1u);
+        mma_commit(&bar_free[hn % kRing]);                                   // every MMA reading this ring slot is issued
+      };
+      auto issue_dq0 = [&](int it) {                                         // dQ0 = g K0 into the shared accumulator
+        mbar_wait(&bar_dqread, (uint32_t)(it & 1), status, 407);             // dQ of that tile has been read out
+        tc_fence_after_sync();
+#pragma unroll
+        for (int ks = 0; ks < 8; ++ks)
+          mma_ss(tmem + kColDQ, at(mG, ks * 2048), at(mK0, ks * 2048), idesc_dq, ks > 0);
+        mma_commit(&bar_dq0);
       };
 
       mbar_expect_tx(&bar_kv, (SELF ? 2 : 3) * kRowTile);
       tma_load_4d(smem + L::k, &map_k, &bar_kv, 0, nj * kTile, h, b);
       tma_load_4d(smem + L::v, &map_v, &bar_kv, 0, nj * kTile, h, b);
       if (!SELF) tma_load_4d(smem + L::k0, &map_k0, &bar_kv, 0, nj * kTile, 0, b);
-      load_stage(0);
-      if (n_iter > 1) load_stage(1);
-      mbar_wait(&bar_kv, 0, status, 400);
-      mbar_wait(&bar_ld[0], 0, status, 401);
+      for (int hn = 0; hn < kRing && hn < n_half; ++hn) load_half(hn);
+      mbar_wait(&bar_setup, 0, status, 400);                   // K and V are in TMEM
       tc_fence_after_sync();
-      issue_scores(0, 1);
+      if (!SELF) issue_l0(0);
+      issue_s(0);
+      issue_dp(0);
 
-      uint32_t early_phase = 0;
-      for (int it = 0; it < n_iter; ++it) {
-        // half 1: P^T and dz are ready and the score columns are free while the g pass still runs
-        const uint32_t ph = it & 1;
-        mbar_wait(&bar_early, early_phase, status, 402);
-        early_phase ^= 1;
-        tc_fence_after_sync();
-        issue_dv(it, 1, it == 0);                             // reads P^T before the next scores overwrite it
-        issue_scores(it, 0);
-        if (!SELF) issue_dk_only(it, 1, it == 0);
-        mbar_wait(&bar_half[1], ph, status, 403);            // half 1: g (SELF: dz + g) written
-        tc_fence_after_sync();
-        if (SELF) issue_dk_only(it, 1, it == 0);
-        else issue_dk0_only(it, 1, it == 0);
-        // half 0
-        mbar_wait(&bar_early, early_phase, status, 406);
-        early_phase ^= 1;
+      for (int hn = 0; hn < n_half; ++hn) {
+        const int second = hn & 1, it = hn >> 1;               // second: the lower half, which completes a query tile
+        const uint32_t ph = (uint32_t)(hn & 1);
+        const bool more = hn + 1 < n_half;
+        if (hn >= 1 && hn - 1 + kRing < n_half) {             // the slot of half hn - 1 is free once its last MMA is done
+          mbar_wait(&bar_free[(hn - 1) % kRing], (uint32_t)(((hn - 1) / kRing) & 1), status, 403);
+          load_half(hn - 1 + kRing);
+        }
+        if (!SELF) {
+          mbar_wait(&bar_sel, ph, status, 402);                // L0^T read by every thread: Z takes the next half's
+          tc_fence_after_sync();
+          if (more) issue_l0(hn + 1);
+          if (!second && it > 0) issue_dq0(it - 1);            // dQ0 of the previous tile (its dQ was read out at that tile's end)
+        }
+        mbar_wait(&bar_early, ph, status, 404);                // P^T (and dz^T) in place, S^T and dP^T read
         tc_fence_after_sync();
         if (SELF) {
-          issue_dv(it, 0, false);
-          if (it + 1 < n_iter) {                              // nothing else can run until the g pass ends
-            mbar_wait(&bar_ld[(it + 1) & 1], ((it + 1) >> 1) & 1, status, 404);
-            tc_fence_after_sync();
-            issue_scores(it + 1, 1);
-          }
-          mbar_wait(&bar_half[0], ph, status, 407);          // half 0: dz + g written
-          tc_fence_after_sync();
+          const uint32_t st = ring_off(hn);
 #pragma unroll
-          for (int ks = 0; ks < 8; ++ks)                      // dQ = (dz + g) K: A M-major, K = key index
-            mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
-          issue_dk_only(it, 0, false);
-          mma_commit(&bar_dq);
-          mma_commit(&bar_b);
+          for (int ks = 0; ks < 4; ++ks)                       // dV += P^T dO; dK waits for dz + g
+            mma_ts(tmem + kColDV, tmem + kColY + ks * 16, at(mRingD, st + 2 * kHalfTile + ks * 2048), idesc_acc,
+                   (hn == 0 && ks == 0) ? 0u : 1u);
         } else {
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks)                      // dQ = dz K: A M-major, K = key index
-            mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
-          issue_dk_only(it, 0, false);
-          mma_commit(&bar_dq);                                // dQ done and every MMA reading the dz tiles is done:
-          issue_dv(it, 0, false);                             //   its read-out overlaps the MMAs from here on
-          mbar_wait(&bar_half[0], ph, status, 407);          // half 0: g written
-          tc_fence_after_sync();
-          issue_dk0_only(it, 0, false);
-#pragma unroll
-          for (int ks = 0; ks < 8; ++ks)                      // dQ0 = g K0
-            mma_ss(tmem + kColDQ0, at(mG, ks * 2048), at(mK0, ks * 2048), idesc_dq, ks > 0);
-          mma_commit(&bar_b);
-          if (it + 1 < n_iter) {
-            mbar_wait(&bar_ld[(it + 1) & 1], ((it + 1) >> 1) & 1, status, 404);
-            tc_fence_after_sync();
-            issue_scores(it + 1, 1);
-          }
+          issue_dv_dk(hn);                                     // they read P^T and dz^T, which the next S^T overwrites
         }
-        mbar_wait(&bar_b, it & 1, status, 405);               // every MMA reading stage (it & 1) has completed
-        if (it + 2 < n_iter) load_stage(it + 2);
+        if (more) issue_s(hn + 1);
+        if (!SELF && second) {                                 // dQ = dz K over all 128 keys
+          if (it > 0) {
+            mbar_wait(&bar_dq0read, (uint32_t)((it - 1) & 1), status, 405);   // dQ0 of the previous tile has been read out
+            tc_fence_after_sync();
+          }
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
+          mma_commit(&bar_dq);
+        }
+        mbar_wait(&bar_g, ph, status, 406);                    // g^T and the g half written (one head per selector: dz + g)
+        tc_fence_after_sync();
+        if (SELF) {
+          const uint32_t st = ring_off(hn);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks)                       // dK += (dz + g)^T Q, A from TMEM (this thread's X columns)
+            mma_ts(tmem + kColDK, tmem + kColX + ks * 16, at(mRingD, st + ks * 2048), idesc_acc,
+                   (hn == 0 && ks == 0) ? 0u : 1u);
+          mma_commit(&bar_free[hn % kRing]);
+        } else {
+          issue_dk0(hn);                                       // it reads g^T, which the next dP^T overwrites
+        }
+        if (more) issue_dp(hn + 1);
+        if (SELF && second) {                                  // dQ = (dz + g) K over all 128 keys
+          if (it > 0) {
+            mbar_wait(&bar_dqread, (uint32_t)((it - 1) & 1), status, 407);    // dQ of the previous tile has been read out
+            tc_fence_after_sync();
+          }
+#pragma unroll
+          for (int ks = 0; ks < 8; ++ks)
+            mma_ss(tmem + kColDQ, at(mDZ, ks * 2048), at(mK, ks * 2048), idesc_dq, ks > 0);
+          mma_commit(&bar_dq);
+        }
       }
+      if (!SELF) issue_dq0(n_iter - 1);
+      mma_commit(&bar_fin);
     }
     __syncwarp();
   } else {
@@ -423,10 +496,10 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     const uint32_t lane_base = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // a warp reaches lanes 32 (warp % 4) ..
     const int j = nj * kTile + row;
     float dz_state = 0.f;            // sum of dz over the queries already visited (later queries), this key
-    uint32_t a_phase = 0;
 
-    HalfCtx ctx;
+    Ctx ctx;
     ctx.smem = smem;
+    ctx.tmem = tmem;
     ctx.lane_base = lane_base;
     ctx.row = row;
     ctx.wg = wg;
@@ -436,9 +509,8 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     ctx.dbar_s = dbar_s;
     ctx.sel_tot = sel_tot;
     ctx.dz_tot = dz_tot;
-    ctx.bar_early = &bar_early;
+    ctx.status = status;
 
-    // per-tile row statistics and carry, fetched one tile ahead
     auto fetch_lse = [&](int mi) {
       const int i = mi * kTile + tid;
       return (tid < kTile && i < seq) ? load_ahead(lse2 + (int64_t)n * seq + i) : INFINITY;   // +inf: P = 0 for padded queries
@@ -452,15 +524,62 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     };
     float next_lse = fetch_lse(ntiles - 1), next_dbar = fetch_dbar(ntiles - 1), next_carry = fetch_carry(ntiles - 1);
 
+    // K and V rows from their landing tiles into TMEM as bf16 pairs (A operands of the score products); warpgroup
+    // wg moves 16 of the 64 d columns = two 16-byte chunks = 8 packed columns of each matrix
+    mbar_wait(&bar_kv, 0, status, 409);
+    {
+      const int offs[2] = {L::k, L::v};
+      const uint32_t cols[2] = {kColK, kColV};
+#pragma unroll
+      for (int m = 0; m < 2; ++m) {
+        uint32_t w8[8];
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const uint4 v4 = *reinterpret_cast<const uint4*>(smem + offs[m] + swz_off(row, wg * 2 + c));
+          w8[4 * c] = v4.x; w8[4 * c + 1] = v4.y; w8[4 * c + 2] = v4.z; w8[4 * c + 3] = v4.w;
+        }
+        tmem_st8(lane_base + cols[m] + wg * 8, w8);
+      }
+      tmem_st_wait();
+      tc_fence_before_sync();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&bar_setup);
+    }
+
+    // The shared accumulator (here the lane is a QUERY row, columns are d) -> scaled fp32 staging tile -> TMA reduce-add.
+    auto read_out = [&](uint64_t* done_bar, const CUtensorMap* map, int i0, int row_index) {
+      const int c0 = wg * kChunk;
+      uint32_t r[16];
+      tmem_ld16(lane_base + kColDQ + c0, r);
+      tmem_ld_wait();
+      uint8_t* sq = smem + L::out + (wg >> 1) * kRowTile;     // [128 queries][32 floats] tiles, 128-byte swizzle
+#pragma unroll
+      for (int c = 0; c < 4; ++c)
+        *reinterpret_cast<float4*>(sq + swz_off(row, (wg & 1) * 4 + c)) =
+            make_float4(__uint_as_float(r[4 * c]) * scale, __uint_as_float(r[4 * c + 1]) * scale,
+                        __uint_as_float(r[4 * c + 2]) * scale, __uint_as_float(r[4 * c + 3]) * scale);
+      fence_async_smem();
+      tc_fence_before_sync();
+      named_barrier(kComputeBarrier, kComputeThreads);
+      if (tid == 0) {
+        mbar_arrive(done_bar);                                // the accumulator may be overwritten
+        tma_reduce_add_4d(map, smem + L::out, 0, i0, row_index, 0);
+        tma_reduce_add_4d(map, smem + L::out + kRowTile, 32, i0, row_index, 0);
+        bulk_commit();
+      }
+    };
+
+    HalfState st;
     for (int it = 0; it < n_iter; ++it) {
       const int mi = ntiles - 1 - it;
       const int i0 = mi * kTile;
       const bool diag = (mi == nj);
+      const uint32_t ph = (uint32_t)(it & 1);
       if (tid < kTile) {
         lse_s[tid] = -next_lse;                                // negated: both enter packed adds directly
         dbar_s[tid] = -next_dbar;
       }
-      ctx.cnl = next_carry * kLog2e;
+      const float cnl = next_carry * kLog2e;
       if (it + 1 < n_iter) {
         next_lse = fetch_lse(mi - 1);
         next_dbar = fetch_dbar(mi - 1);
@@ -470,55 +589,47 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 
 #pragma unroll 1
       for (int hf = 1; hf >= 0; --hf) {
-        mbar_wait(&bar_a, a_phase, status, 410);
-        a_phase ^= 1;
-        tc_fence_after_sync();
-        ctx.hf = hf;
-        ctx.drain_reduce = (hf == 1) && (it > 0);
-        if (diag) process_half<true, SELF>(ctx, sel_state, dz_state);
-        else process_half<false, SELF>(ctx, sel_state, dz_state);
-        fence_async_smem();                                    // g tile half -> visible to the MMAs
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&bar_half[hf]);
-      }
-
-      // ---- dQ, then dQ0, of this query tile: TMEM -> scaled fp32 staging in shared memory (the dz / g tiles,
-      // which no MMA reads any more) -> TMA reduce-add.  dQ is staged while the dK0 / dQ0 MMAs still run.
-      auto stage_tile = [&](uint32_t col, uint8_t* dst) {
-        const int c0 = wg * kChunk;                           // here the lane is a QUERY row, columns are d
-        uint32_t r[16];
-        tmem_ld16(lane_base + col + c0, r);
-        tmem_ld_wait();
-        uint8_t* sq = dst + (wg >> 1) * kRowTile;             // [128 queries][32 floats] tiles, 128-byte swizzle
-#pragma unroll
-        for (int c = 0; c < 4; ++c)
-          *reinterpret_cast<float4*>(sq + swz_off(row, (wg & 1) * 4 + c)) =
-              make_float4(__uint_as_float(r[4 * c]) * scale, __uint_as_float(r[4 * c + 1]) * scale,
-                          __uint_as_float(r[4 * c + 2]) * scale, __uint_as_float(r[4 * c + 3]) * scale);
-        fence_async_smem();
+        const uint32_t hp = (uint32_t)(1 - hf);               // parity of this half's barrier phases
+        // the staging tile is written next at the read-out that follows this half's dz pass (dQ0 of the previous
+        // tile after the upper half, dQ of this tile after the lower half): its last reduce-add must have read it
+        const bool drain = SELF ? (hf == 1 && it > 0) : ((it > 0) || (hf == 0));
+        if (diag) half_scores<true, SELF>(ctx, hf, hp, cnl, sel_state, st, &bar_l0, &bar_sel, &bar_s, &bar_dp, &bar_early, drain);
+        else half_scores<false, SELF>(ctx, hf, hp, cnl, sel_state, st, &bar_l0, &bar_sel, &bar_s, &bar_dp, &bar_early, drain);
+        if (hf == 1 && it > 0) {                               // the previous tile's last product, issued a half-tile ago:
+          if (SELF) {                                          //   dQ = (dz + g) K, or dQ0 = g K0
+            mbar_wait(&bar_dq, (uint32_t)((it - 1) & 1), status, 413);
+            tc_fence_after_sync();
+            read_out(&bar_dqread, &map_dq, i0 + kTile, n);
+          } else {
+            mbar_wait(&bar_dq0, (uint32_t)((it - 1) & 1), status, 412);
+            tc_fence_after_sync();
+            read_out(&bar_dq0read, &map_dq0, i0 + kTile, b);
+          }
+        }
+        half_gate<SELF>(ctx, hf, dz_state, st);
+        fence_async_smem();                                    // g half tile -> visible to the MMAs
         tc_fence_before_sync();
-        named_barrier(kComputeBarrier, kComputeThreads);
-      };
-      mbar_wait(&bar_dq, it & 1, status, 412);
-      tc_fence_after_sync();
-      stage_tile(kColDQ, smem + L::dz);
-      if (tid == 0) {
-        tma_reduce_add_4d(&map_dq, smem + L::dz, 0, i0, n, 0);
-        tma_reduce_add_4d(&map_dq, smem + L::dz + kRowTile, 32, i0, n, 0);
-        bulk_commit();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&bar_g);
       }
-      if (SELF) continue;                                      // dQ already carries the selection path
-      mbar_wait(&bar_b, it & 1, status, 411);
-      tc_fence_after_sync();
-      stage_tile(kColDQ0, smem + L::g);
-      if (tid == 0) {
-        tma_reduce_add_4d(&map_dq0, smem + L::g, 0, i0, b, 0);
-        tma_reduce_add_4d(&map_dq0, smem + L::g + kRowTile, 32, i0, b, 0);
-        bulk_commit();
+      if (!SELF) {
+        mbar_wait(&bar_dq, ph, status, 413);                   // dQ of this tile, issued before the last g pass
+        tc_fence_after_sync();
+        read_out(&bar_dqread, &map_dq, i0, n);
       }
+    }
+    {                                                          // the first query tile's last product, visited last
+      mbar_wait(SELF ? &bar_dq : &bar_dq0, (uint32_t)((n_iter - 1) & 1), status, 414);
+      tc_fence_after_sync();
+      if (tid == 0) bulk_wait_read();
+      named_barrier(kComputeBarrier, kComputeThreads);
+      if (SELF) read_out(&bar_dqread, &map_dq, nj * kTile, n);
+      else read_out(&bar_dq0read, &map_dq0, nj * kTile, b);
     }
 
     // ---- epilogue: dV, dK (this head) and this head's share of dK0 ------------------------------------------
+    mbar_wait(&bar_fin, 0, status, 415);
+    tc_fence_after_sync();
     {
       const int c0 = wg * kChunk;
       __nv_bfloat16* dv_row = dv + dv_rows.at(b, h, j) + c0;
@@ -545,9 +656,9 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
                           __uint_as_float(rk[e + 2]) * scale, __uint_as_float(rk[e + 3]) * scale);
           if (!SELF)
             asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dk0_row + e),
-                         "f"(__uint_as_float(r0[e]) * scale), "f"(__uint_as_float(r0[e + 1]) * scale),
-                         "f"(__uint_as_float(r0[e + 2]) * scale), "f"(__uint_as_float(r0[e + 3]) * scale)
-                         : "memory");
+                       "f"(__uint_as_float(r0[e]) * scale), "f"(__uint_as_float(r0[e + 1]) * scale),
+                       "f"(__uint_as_float(r0[e + 2]) * scale), "f"(__uint_as_float(r0[e + 3]) * scale)
+                       : "memory");
         }
       }
     }
@@ -560,50 +671,46 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 
 }  // namespace
 
-int backward_shared(const Problem& p, const float* lse2, const float* carry, const float* dbar, const void* d_out_bf16,
-                    float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv, cudaStream_t s);
-
 int backward(const Problem& p, const float* lse2, const float* carry, const float* dbar, const void* d_out_bf16,
              float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv, cudaStream_t s) {
   if (p.head_dim != 64) return SA_ERR_UNSUPPORTED;
-  // A selector shared by several heads (or given separately) has its own kernel (sa_tc_bwd_shared.cu); the kernel of
-  // this file runs the one-head-per-selector form.
-  const bool self = (p.heads == 1) && !p.external_selector;
-  if (!self) return backward_shared(p, lse2, carry, dbar, d_out_bf16, dq_acc, dk_acc, dq0, dk0, dv, s);
   const int ntiles = (p.seq + kTile - 1) / kTile;
   const int nrows = p.batch * p.heads;
-  CUtensorMap map_q, map_k, map_v, map_do, map_dq, map_dq0;
-  int st = make_map_16bit(&map_q, p.q.ptr, 64, p.seq, p.heads, p.batch, p.q.st, p.q.sh, p.q.sb, kTile);
+  CUtensorMap map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0;
+  int st = make_map_16bit(&map_q, p.q.ptr, 64, p.seq, p.heads, p.batch, p.q.st, p.q.sh, p.q.sb, 64);
   if (st != SA_OK) return st;
   st = make_map_16bit(&map_k, p.k.ptr, 64, p.seq, p.heads, p.batch, p.k.st, p.k.sh, p.k.sb, kTile);
   if (st != SA_OK) return st;
   st = make_map_16bit(&map_v, p.v.ptr, 64, p.seq, p.heads, p.batch, p.v.st, p.v.sh, p.v.sb, kTile);
   if (st != SA_OK) return st;
-  st = make_map_16bit(&map_do, d_out_bf16, 64, p.seq, nrows, 1, 64, (int64_t)p.seq * 64, (int64_t)nrows * p.seq * 64,
-                      kTile);
+  st = make_map_16bit(&map_do, d_out_bf16, 64, p.seq, nrows, 1, 64, (int64_t)p.seq * 64, (int64_t)nrows * p.seq * 64, 64);
   if (st != SA_OK) return st;
   st = make_map_f32_rows(&map_dq, dq_acc, p.seq, nrows);
   if (st != SA_OK) return st;
   st = make_map_f32_rows(&map_dq0, dq0, p.seq, p.batch);
   if (st != SA_OK) return st;
-  CUtensorMap map_q0, map_k0;                            // the selector's rows: (d, token, 1, batch)
-  st = make_map_16bit(&map_q0, p.q0.ptr, 64, p.seq, 1, p.batch, p.q0.st, 0, p.q0.sb, kTile);
+  st = make_map_16bit(&map_q0, p.q0.ptr, 64, p.seq, 1, p.batch, p.q0.st, 0, p.q0.sb, 64);
   if (st != SA_OK) return st;
   st = make_map_16bit(&map_k0, p.k0.ptr, 64, p.seq, 1, p.batch, p.k0.st, 0, p.k0.sb, kTile);
   if (st != SA_OK) return st;
   WaitCtx status;
   st = wait_ctx(&status);
   if (st != SA_OK) return st;
-  const int smem = BwdSmem::total + 1024;
-  // One head per selector (the per-head form): the selection logits are the head's own, and the kernel merges the
-  // two gradient paths before the MMAs.
+  const int smem = Smem::total + 1024;
+  const bool self = (p.heads == 1) && !p.external_selector;   // one head per selector: the selection logits are the head's own
   SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   {
     ProfileScope prof(SA_KERNEL_TC_BACKWARD, s);
     count_launch();
-    backward_kernel<true><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
-        map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
-        static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
+    if (self)
+      backward_kernel<true><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
+          map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
+          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
+    else
+      backward_kernel<false><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
+          map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
+          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
   }
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;
