@@ -7,6 +7,8 @@ namespace tc {
 int forward(const Problem& p, float* out, float* lse2, float* carry, float* total, cudaStream_t s);
 int backward(const Problem& p, const float* lse2, const float* carry, const float* dbar, const void* d_out_bf16,
              float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv, cudaStream_t s);
+int backward_wide(const Problem& p, const float* lse2, const float* carry, const float* dbar, const void* d_out_bf16,
+                  float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv, cudaStream_t s);
 }  // namespace tc
 
 int tc_available() { return 1; }
@@ -23,13 +25,12 @@ int tc_forward(const Problem& p, float* out, float* lse2, float* carry, float* t
 }
 
 int tc_backward_supported(const Problem& p) {
-  int st = tc_supported(p);
-  if (st != SA_OK) return st;
-  return p.head_dim == 64 ? SA_OK : SA_ERR_UNSUPPORTED;
+  return tc_supported(p);
 }
 
 int tc_backward(const Problem& p, const float* lse2, const float* carry, const float* dbar, const void* d_out_lowp,
                 float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv, cudaStream_t s) {
+  if (p.head_dim == 128) return tc::backward_wide(p, lse2, carry, dbar, d_out_lowp, dq_acc, dk_acc, dq0, dk0, dv, s);
   return tc::backward(p, lse2, carry, dbar, d_out_lowp, dq_acc, dk_acc, dq0, dk0, dv, s);
 }
 }  // namespace sa

@@ -323,11 +323,6 @@ def _backward_call(ctx, dout, dq0=None, dk0=None):
         dout = dout.float()
     dout = dout.contiguous()
     engine = ctx.engine
-    if engine == _lib.ENGINE_TCGEN05 and not lib.sa_engine_supports(engine, _DTYPE_CODE[q.dtype], q.shape[3], 1):
-        # The tensor-core forward ran, but this head_dim has no tensor-core backward: the CUDA-core backward takes
-        # the forward's out / lse and its own 32-query checkpoints from a selection pass of its own.
-        engine = _lib.ENGINE_SIMT
-        carry = _selection_carry32(q, k, sel, ctx.exempt, zero=False)
     prob = _problem(q, k, v, engine, ctx.exempt)
     need = lib.sa_backward_workspace_bytes(ctypes.byref(prob))
     workspace = torch.empty(max(need, 1), device=dev, dtype=torch.uint8)
@@ -447,9 +442,9 @@ def _tensor_struct(t: torch.Tensor) -> _lib.Tensor:
 
 def packed_supported(qkv: torch.Tensor) -> bool:
     """True when ``selective_attention_packed`` can take this fused projection output: bf16 on a CUDA device,
-    (B, T, 3, H, D) with D = 64, contiguous, and the library built."""
+    (B, T, 3, H, D) with D = 64 or 128, contiguous, and the library built."""
     return (HAS_KERNELS and qkv.is_cuda and qkv.dtype == torch.bfloat16 and qkv.dim() == 5 and qkv.shape[2] == 3
-            and qkv.shape[4] == 64 and qkv.is_contiguous() and os.environ.get("SA_B200_ENGINE", "") != "simt")
+            and qkv.shape[4] in (64, 128) and qkv.is_contiguous() and os.environ.get("SA_B200_ENGINE", "") != "simt")
 
 
 class _SelectiveAttentionPackedFn(torch.autograd.Function):
@@ -512,7 +507,7 @@ def selective_attention_packed(qkv: torch.Tensor, exempt: int = 1) -> torch.Tens
     heads.  Same arithmetic as ``selective_attention`` on the three (B, H, T, D) views; what is saved is every
     copy between the projections and the kernels."""
     if not packed_supported(qkv):
-        raise ValueError("qkv must be a contiguous bf16 CUDA tensor (B, T, 3, H, 64); use selective_attention otherwise")
+        raise ValueError("qkv must be a contiguous bf16 CUDA tensor (B, T, 3, H, 64 or 128); use selective_attention otherwise")
     return _SelectiveAttentionPackedFn.apply(qkv, exempt)
 
 

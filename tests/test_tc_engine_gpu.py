@@ -105,9 +105,12 @@ def _fwd_bwd(q, k, v, w, **kw):
 
 @pytest.mark.parametrize("seq", [1, 2, 64, 65, 128, 129, 300, 1000, 2049])
 @pytest.mark.parametrize("heads,scale", [(1, 1.0), (3, 1.0), (4, 0.3)])
-def test_backward_matches_oracle(seq, heads, scale):
-    q, k, v, w = _inputs(2, heads, seq, 64, seed=seq + heads, scale=scale)
+@pytest.mark.parametrize("dim", [64, 128])
+def test_backward_matches_oracle(seq, heads, scale, dim):
+    q, k, v, w = _inputs(2, heads, seq, dim, seed=seq + heads, scale=scale)
+    before = _lib.launch_count()
     got = _fwd_bwd(q, k, v, w)
+    assert _lib.launch_count() - before == 3 + 4          # colsum, scan, forward | dbar, backward, 2 x fold
     want = oracle.attention_grads(q.float(), k.float(), v.float(), w.float())
     for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
         assert a.dtype == (torch.float32 if name == "out" else torch.bfloat16)
@@ -136,16 +139,16 @@ def test_backward_exempt_prefix(exempt, heads):
         assert _rel(a, b) < 2e-2, (name, _rel(a, b))
 
 
-@pytest.mark.parametrize("seq", [129, 1000, 2049])
-def test_head_dim_128_training_keeps_the_tensor_core_forward(seq):
-    """head_dim 128 has a tensor-core forward but no tensor-core backward: under autograd the forward still runs on
-    the tensor cores (carry checkpoints every 128 queries) and the backward runs on the CUDA cores from the
-    forward's out / lse with 32-query checkpoints of its own."""
-    q, k, v, w = _inputs(1, 2, seq, 128, seed=9 + seq, scale=0.5)
-    before = _lib.launch_count()
-    got = _fwd_bwd(q, k, v, w)
-    assert _lib.launch_count() - before == 3 + 5          # colsum, scan, forward | dbar, carry, backward, 2 x fold
-    want = oracle.attention_grads(q.float(), k.float(), v.float(), w.float())
+@pytest.mark.parametrize("heads", [1, 3])
+def test_head_dim_128_backward_exempt_prefix_and_selection_only_gradient(heads):
+    """head_dim 128: two CTAs per (head, key tile), one per half of the head dimension; the query-side gradients
+    leave transposed.  An exempt prefix past the first key tile, and a cotangent that is zero on the selection head
+    so that its q / k gradients come only through the other heads' history terms."""
+    q, k, v, w = _inputs(1, heads, 333, 128, seed=50 + heads, scale=0.8)
+    if heads > 1:
+        w[:, 0] = 0
+    got = _fwd_bwd(q, k, v, w, exempt=140)
+    want = oracle.attention_grads(q.float(), k.float(), v.float(), w.float(), exempt=140)
     for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
         assert _rel(a, b) < 2e-2, (name, _rel(a, b))
 
@@ -163,12 +166,12 @@ def test_reference_layout_of_the_carry_on_request():
     assert (native["carry"][:, 0] == 0).all() and (aux["carry"][:, 0] == 0).all()
 
 
-@pytest.mark.parametrize("seq,heads", [(300, 3), (1000, 2), (129, 1)])
-def test_packed_projection_form_equals_the_plain_call(seq, heads):
+@pytest.mark.parametrize("seq,heads,d", [(300, 3, 64), (1000, 2, 64), (129, 1, 64), (300, 2, 128), (700, 1, 128)])
+def test_packed_projection_form_equals_the_plain_call(seq, heads, d):
     """The layout-fused entry (q, k, v read in place from a (B, T, 3, H, D) projection output, merged (B, T, H D)
     output and packed gradients written by the kernels) against the plain call on the three views, and the oracle."""
     g = torch.Generator("cpu").manual_seed(seq)
-    b, d = 2, 64
+    b = 2
     qkv = torch.randn(b, seq, 3, heads, d, generator=g).bfloat16().cuda()
     w = torch.randn(b, seq, heads * d, generator=g).bfloat16().cuda()
     assert kernels.packed_supported(qkv)
