@@ -1,8 +1,8 @@
 """Parity at the benchmark's own shapes against the oracle, with the oracle's dense torch ops run on the
 device (fp32, TF32 off) because a (T, T) tensor at T = 16384 is 1 GiB.
 
-* whole forward + backward of one sequence at T = 16384, D = 64, bf16: out, dq, dk, dv and the per-key totals,
-  shared selection (three heads) and one head per selector, unit-variance inputs and low-scale q, k;
+* whole forward + backward of one sequence at T = 16384, D = 64 and D = 128, bf16: out, dq, dk, dv and the per-key
+  totals, shared selection (three heads) and one head per selector, unit-variance inputs and low-scale q, k;
 * the reference's CPU case exactly (B = 2, H = 4, T = 1024, D = 64, fp32, seed 0) at the fp32 bar;
 * forward rows from a MIDDLE query tile and from the tail, at T = 16384 with all sixteen heads and two
   sequences, and at T = 131072.
@@ -48,10 +48,10 @@ class _ExactMatmul:
 
 
 @pytest.mark.parametrize("heads", [3, 1])                    # 3: head 0 selects for all; 1: the per-head kernels
-@pytest.mark.parametrize("scale_qk", [1.0, 0.15, 0.02])
-def test_forward_backward_at_16k_against_the_oracle(heads, scale_qk, achieved):
+@pytest.mark.parametrize("dim,scale_qk", [(64, 1.0), (64, 0.15), (64, 0.02), (128, 1.0), (128, 0.1)])
+def test_forward_backward_at_16k_against_the_oracle(heads, dim, scale_qk, achieved):
     seq = 16384
-    q, k, v, w = _inputs((1, heads, seq, 64), seed=1000 + heads, scale_qk=scale_qk)
+    q, k, v, w = _inputs((1, heads, seq, dim), seed=1000 + heads, scale_qk=scale_qk)
     qq, kk, vv = (t.cuda().requires_grad_(True) for t in (q, k, v))
     out, aux = None, None
     out = kernels.selective_attention(qq, kk, vv)
@@ -66,7 +66,7 @@ def test_forward_backward_at_16k_against_the_oracle(heads, scale_qk, achieved):
     got = (out.detach()[0], qq.grad[0], kk.grad[0], vv.grad[0])
     errs = {name: _rel(a, b) for name, a, b in zip(("out", "dq", "dk", "dv"), got, want)}
     total_err = float((aux["selected_total"][0] - want[4]).abs().max() / want[4].abs().max().clamp_min(1e-6))
-    achieved(f"fwd+bwd T=16384 H={heads} D=64 bf16 scale_qk={scale_qk}", total_max_rel=total_err, **errs)
+    achieved(f"fwd+bwd T=16384 H={heads} D={dim} bf16 scale_qk={scale_qk}", total_max_rel=total_err, **errs)
     for name, a in zip(("out", "dq", "dk", "dv"), got):
         assert torch.isfinite(a.float()).all(), name
     for name, e in errs.items():

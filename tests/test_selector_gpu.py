@@ -34,6 +34,7 @@ def _split_call(q, k, v, w, head_slices, precision):
     (torch.float32, "ieee", 32, 300, 1e-4),       # CUDA-core engine
     (torch.bfloat16, None, 64, 700, 2e-2),        # tensor-core engine
     (torch.bfloat16, None, 64, 2049, 2e-2),
+    (torch.bfloat16, None, 128, 1000, 2e-2),      # head_dim 128: the split-head-dimension backward with an outside selector
 ])
 def test_two_head_halves_with_a_replicated_selector_equal_the_unsplit_call(dtype, precision, dim, seq, tol, achieved):
     g = torch.Generator("cpu").manual_seed(seq)
