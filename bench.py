@@ -47,6 +47,8 @@ WORKLOADS = {
     # name: (batch, heads, seq, dim, per_head selection, backward?)
     "c2": dict(batch=4, heads=16, seq=16384, dim=64, per_head=False, backward=True),
     "c3": dict(batch=4, heads=16, seq=16384, dim=64, per_head=True, backward=True),
+    # the counted FLOPs of c2 at head_dim 128 (eight heads)
+    "c2d128": dict(batch=4, heads=8, seq=16384, dim=128, per_head=False, backward=True),
     "c4": dict(batch=1, heads=16, seq=131072, dim=64, per_head=False, backward=False),
     # one cached decode step against a 131,071-token cache (the serving continuation of c4)
     "decode": dict(batch=1, heads=16, seq=131072, dim=64, per_head=False, backward=False),
@@ -388,7 +390,7 @@ def run_ours(args, w, rank, world, device):
     # ---- end-to-end arm: host buffers in, host buffers out ------------------------------------------------
     # Whole sequences with a shared selector go through the layer-facing call: one packed (B, T, 3, H, D) projection
     # output and one (B, T, H D) cotangent in, the merged output and the packed gradient out (the same bytes).
-    packed = w["backward"] and not w["per_head"] and not sel_h and w["dim"] == 64 and args.e2e_call == "packed"
+    packed = w["backward"] and not w["per_head"] and not sel_h and w["dim"] in (64, 128) and args.e2e_call == "packed"
     if packed:
         q_h, k_h, v_h, do_h = (t.transpose(1, 2) for t in (q_h, k_h, v_h, do_h))       # (B, T, H, D)
         qkv_h = torch.stack([q_h, k_h, v_h], dim=2).contiguous()                       # (B, T, 3, H, D)
@@ -506,7 +508,7 @@ def run_ours(args, w, rank, world, device):
     achieved = kflops / (kernel_avg_ms * 1e-3) / 1e12 if kernel_ms else None
     ntile = math.ceil(w["seq"] / 128)
     head_tiles = len(plan["seqs"]) * len(plan["heads"]) * (ntile * (ntile + 1) // 2)
-    per_tile = captured_traffic_per_head_tile(dominant)
+    per_tile = captured_traffic_per_head_tile(dominant if w["dim"] == 64 else f"{dominant}_d{w['dim']}")
     step_flops = (flops["forward"] + flops["backward"]) * (world if plan["scaling"] == "weak" else 1)
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
