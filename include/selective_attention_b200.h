@@ -84,7 +84,7 @@ typedef struct sa_selector {
  * (batch, seq, 3, heads, head_dim) projection gradient. */
 typedef struct sa_tensor {
   void* ptr;             /* 16-byte aligned                                                            */
-  int32_t dtype;         /* sa_dtype; must equal p->dtype                                              */
+  int32_t dtype;         /* sa_dtype; p->dtype unless the entry point says otherwise                   */
   int32_t reserved;      /* 0                                                                          */
   int64_t stride[3];     /* batch, head, token strides in elements; each a multiple of 16 bytes        */
 } sa_tensor;
@@ -226,7 +226,8 @@ int sa_backward_selector(const sa_problem* p, const void* q, const void* k, cons
                          void* workspace, size_t workspace_bytes, void* stream);
 
 /* Layout-fused backward (tensor-core engine).  As sa_backward_selector, with the cotangent read from, and the
- * three gradients written to, tensors in the caller's layout (element type p->dtype): d_out is typically the
+ * three gradients written to, tensors in the caller's layout (gradients: element type p->dtype; the cotangent:
+ * any supported element type): d_out is typically the
  * (batch, seq, heads, head_dim) view of the gradient of the merged activation, dq / dk / dv the three slots of
  * the fused projection's gradient.  Replaces the `.contiguous()` copy of the cotangent
  * (src/selective_attention/kernels.py:632-635) and the copies autograd makes to scatter dq / dk / dv back through
@@ -237,6 +238,33 @@ int sa_backward_fused(const sa_problem* p, const void* q, const void* k, const v
                       const sa_tensor* d_out,
                       const sa_tensor* dq, const sa_tensor* dk, const sa_tensor* dv, float* dq0, float* dk0,
                       void* workspace, size_t workspace_bytes, void* stream);
+
+/* Leaving out dead tiles (tensor-core engine, bf16, head_dim 64 / 128, seq <= 131072; optional).  The history term of
+ * a (query, key) pair never decreases with the query index, so for keys that many later queries have selected
+ * against, whole 128 x 128 tiles of far queries have probabilities that the exponential flushes to exactly zero:
+ * they add nothing to the output or to any gradient.  The reference computes every causal tile
+ * (src/selective_attention/kernels.py:100-160, :196-268); with a tile table the forward decides after its selection
+ * pass, from a rigorous bound (largest row norms of the q / k tiles, smallest running selection sum of the key tile,
+ * a margin of 24 binades beyond the flush threshold), which tiles are dead, records the live ones in the table and
+ * leaves the dead ones out; the backward of the same call is given the same table and starts each key tile's walk at
+ * its last live query tile.  Results are those of the plain calls (bit-identical forward; gradients equal up to the
+ * order of the fp32 reductions).  What is saved depends on the data: nothing when the selection is weak, most of the
+ * tiles at long context when it is strong.
+ *   sa_tile_table_bytes     size of the table for a problem; 0 when leaving out tiles is not offered for it.
+ *   sa_forward_live_tiles   sa_forward_fused plus the table (256-byte aligned device memory; contents undefined on
+ *                           entry; NULL: identical to sa_forward_fused).
+ *   sa_backward_live_tiles  sa_backward_fused plus the table the forward filled (NULL: identical to it). */
+size_t sa_tile_table_bytes(const sa_problem* p);
+int sa_forward_live_tiles(const sa_problem* p, const void* q, const void* k, const void* v,
+                          const sa_selector* sel,
+                          float* out, const sa_tensor* out_lowp, float* lse2, float* carry, float* total,
+                          void* tile_table, size_t tile_table_bytes, void* stream);
+int sa_backward_live_tiles(const sa_problem* p, const void* q, const void* k, const void* v,
+                           const sa_selector* sel,
+                           const float* out, const float* lse2, const float* carry,
+                           const sa_tensor* d_out,
+                           const sa_tensor* dq, const sa_tensor* dk, const sa_tensor* dv, float* dq0, float* dk0,
+                           void* workspace, size_t workspace_bytes, const void* tile_table, void* stream);
 
 /* Bytes of scratch sa_decode_step needs: per-split partial sums, the step's new selection values and the
  * tickets with which the last CTA of a row / key range is found.  Contents undefined on entry and exit; two

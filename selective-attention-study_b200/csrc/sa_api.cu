@@ -76,6 +76,7 @@ int to_problem(const sa_problem* in, const void* q, const void* k, const void* v
   p->q_offset = 0;
   p->carry_init = nullptr;
   p->carry_init_stride = 0;
+  p->tile_table = nullptr;
   p->out_lowp = nullptr;
   p->out_lowp_rows = contiguous_rows(in->heads, in->seq, in->head_dim);
   p->dv_rows = contiguous_rows(in->heads, in->seq, in->head_dim);
@@ -118,7 +119,7 @@ using namespace sa;
 
 extern "C" {
 
-int sa_abi_version(void) { return 2; }
+int sa_abi_version(void) { return 3; }
 
 const char* sa_status_string(int status) {
   switch (status) {
@@ -189,10 +190,29 @@ int sa_forward_selector(const sa_problem* in, const void* q, const void* k, cons
 
 int sa_forward_fused(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
                      float* out, const sa_tensor* out_lowp, float* lse2, float* carry, float* total, void* stream) {
+  return sa_forward_live_tiles(in, q, k, v, sel, out, out_lowp, lse2, carry, total, nullptr, 0, stream);
+}
+
+size_t sa_tile_table_bytes(const sa_problem* in) {
+  Problem p;
+  if (to_problem(in, nullptr, nullptr, nullptr, nullptr, &p) != SA_OK || in->engine != SA_ENGINE_TCGEN05) return 0;
+  return tc::tile_table_bytes(p);
+}
+
+int sa_forward_live_tiles(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
+                          float* out, const sa_tensor* out_lowp, float* lse2, float* carry, float* total,
+                          void* tile_table, size_t tile_table_bytes, void* stream) {
   Problem p;
   int st = to_problem(in, q, k, v, sel, &p);
   if (st != SA_OK) return st;
   if (!q || !k || !v || !out || !lse2 || !carry || !total) return SA_ERR_BAD_ARGUMENT;
+  if (tile_table != nullptr) {
+    const size_t need = (in->engine == SA_ENGINE_TCGEN05) ? tc::tile_table_bytes(p) : 0;
+    if (need == 0) return SA_ERR_UNSUPPORTED;
+    if (tile_table_bytes < need) return SA_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(tile_table) & 255) != 0) return SA_ERR_ALIGNMENT;
+    p.tile_table = tile_table;
+  }
   if (out_lowp != nullptr) {
     if (in->engine != SA_ENGINE_TCGEN05) return SA_ERR_UNSUPPORTED;
     st = rows_of(out_lowp, in->dtype, &p.out_lowp_rows);
@@ -302,7 +322,7 @@ int backward_common(const sa_problem* in, const void* q, const void* k, const vo
                     const float* out, const float* lse2, const float* carry, const void* d_out, int d_out_dtype,
                     const RowLayout* d_out_rows, void* dq, void* dk, void* dv, const RowLayout* dq_rows,
                     const RowLayout* dk_rows, const RowLayout* dv_rows, float* dq0_out, float* dk0_out, void* workspace,
-                    size_t workspace_bytes, void* stream);
+                    size_t workspace_bytes, const void* tile_table, void* stream);
 }  // namespace
 
 int sa_backward_selector(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
@@ -310,22 +330,31 @@ int sa_backward_selector(const sa_problem* in, const void* q, const void* k, con
                          void* dq, void* dk, void* dv, float* dq0_out, float* dk0_out, void* workspace,
                          size_t workspace_bytes, void* stream) {
   return backward_common(in, q, k, v, sel, out, lse2, carry, d_out, d_out_dtype, nullptr, dq, dk, dv, nullptr, nullptr,
-                         nullptr, dq0_out, dk0_out, workspace, workspace_bytes, stream);
+                         nullptr, dq0_out, dk0_out, workspace, workspace_bytes, nullptr, stream);
 }
 
 int sa_backward_fused(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
                       const float* out, const float* lse2, const float* carry, const sa_tensor* d_out,
                       const sa_tensor* dq, const sa_tensor* dk, const sa_tensor* dv, float* dq0_out, float* dk0_out,
                       void* workspace, size_t workspace_bytes, void* stream) {
+  return sa_backward_live_tiles(in, q, k, v, sel, out, lse2, carry, d_out, dq, dk, dv, dq0_out, dk0_out, workspace,
+                                workspace_bytes, nullptr, stream);
+}
+
+int sa_backward_live_tiles(const sa_problem* in, const void* q, const void* k, const void* v, const sa_selector* sel,
+                           const float* out, const float* lse2, const float* carry, const sa_tensor* d_out,
+                           const sa_tensor* dq, const sa_tensor* dk, const sa_tensor* dv, float* dq0_out, float* dk0_out,
+                           void* workspace, size_t workspace_bytes, const void* tile_table, void* stream) {
   if (in == nullptr || in->engine != SA_ENGINE_TCGEN05) return in ? SA_ERR_UNSUPPORTED : SA_ERR_BAD_ARGUMENT;
   RowLayout r_do, r_dq, r_dk, r_dv;
-  int st = rows_of(d_out, in->dtype, &r_do);
+  if (d_out == nullptr || !dtype_ok(d_out->dtype)) return SA_ERR_BAD_ARGUMENT;
+  int st = rows_of(d_out, d_out->dtype, &r_do);        // the cotangent may be of any supported element type
   if (st == SA_OK) st = rows_of(dq, in->dtype, &r_dq);
   if (st == SA_OK) st = rows_of(dk, in->dtype, &r_dk);
   if (st == SA_OK) st = rows_of(dv, in->dtype, &r_dv);
   if (st != SA_OK) return st;
   return backward_common(in, q, k, v, sel, out, lse2, carry, d_out->ptr, d_out->dtype, &r_do, dq->ptr, dk->ptr, dv->ptr,
-                         &r_dq, &r_dk, &r_dv, dq0_out, dk0_out, workspace, workspace_bytes, stream);
+                         &r_dq, &r_dk, &r_dv, dq0_out, dk0_out, workspace, workspace_bytes, tile_table, stream);
 }
 
 namespace {
@@ -333,11 +362,15 @@ int backward_common(const sa_problem* in, const void* q, const void* k, const vo
                     const float* out, const float* lse2, const float* carry, const void* d_out, int d_out_dtype,
                     const RowLayout* d_out_rows, void* dq, void* dk, void* dv, const RowLayout* dq_rows,
                     const RowLayout* dk_rows, const RowLayout* dv_rows, float* dq0_out, float* dk0_out, void* workspace,
-                    size_t workspace_bytes, void* stream) {
+                    size_t workspace_bytes, const void* tile_table, void* stream) {
   Problem p;
   int st = to_problem(in, q, k, v, sel, &p);
   if (st != SA_OK) return st;
   if (dv_rows != nullptr) p.dv_rows = *dv_rows;
+  if (tile_table != nullptr) {                         // the table the forward of this call filled
+    if (in->engine != SA_ENGINE_TCGEN05 || tc::tile_table_bytes(p) == 0) return SA_ERR_UNSUPPORTED;
+    p.tile_table = const_cast<void*>(tile_table);
+  }
   if (!q || !k || !v || !out || !lse2 || !carry || !d_out || !dq || !dk || !dv || !workspace) return SA_ERR_BAD_ARGUMENT;
   if (sel != nullptr && (!dq0_out || !dk0_out)) return SA_ERR_BAD_ARGUMENT;
   if (!dtype_ok(d_out_dtype) || in->damp != SA_DAMP_NONE) return SA_ERR_BAD_ARGUMENT;

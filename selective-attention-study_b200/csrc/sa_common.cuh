@@ -60,6 +60,9 @@ struct Problem {
   void* out_lowp;        // null: not requested
   RowLayout out_lowp_rows;
   RowLayout dv_rows;     // where dv rows go (default: contiguous (batch, heads, seq, head_dim))
+  // Tensor-core engine, optional: the table of live (query tile, key tile) pairs (sa_tc_skip.cu).  The forward
+  // fills it after its selection pass and leaves out the dead tiles; the backward of the same call reads it.
+  void* tile_table;      // null: every causal tile is computed
 };
 
 // ---- engine entry points (host) -------------------------------------------------------------------
@@ -68,6 +71,11 @@ int simt_carry(const Problem& p, float* carry, float* total, cudaStream_t s);
 int simt_backward(const Problem& p, const float* lse2, const float* carry, const float* dbar,
                   const float* d_out, float* dq_acc, float* dk_acc, float* dq0, float* dk0, void* dv,
                   cudaStream_t s);
+
+namespace tc {
+size_t tile_table_bytes(const Problem& p);                                     // 0: not offered for this problem
+int build_tile_table(const Problem& p, const float* carry, cudaStream_t s);
+}  // namespace tc
 
 int tc_available();
 int tc_supported(const Problem& p);

@@ -68,17 +68,15 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     const __grid_constant__ CUtensorMap map_q0, const __grid_constant__ CUtensorMap map_k0,
     const float* __restrict__ lse2, const float* __restrict__ carry, const float* __restrict__ dbar,
     float* __restrict__ dk_acc, float* __restrict__ dk0, __nv_bfloat16* __restrict__ dv, int heads, int seq,
-    int ntiles, int exempt, float scale, WaitCtx status, RowLayout dv_rows) {
+    int ntiles, int exempt, float scale, WaitCtx status, RowLayout dv_rows, const uint8_t* __restrict__ alive) {
   using L = Smem;
   constexpr int D = 64;
   // One (batch, head) row after the other, and within a row the key tiles with the most query tiles first: the CTAs
   // resident at one time belong to one or two rows and walk the same query tiles from the last one down, so every
   // Q, Q0, dO tile is fetched from DRAM once and then served from L2 to the row's other CTAs.
-  const int n = (int)(blockIdx.x / ntiles);
-  const int nj = (int)(blockIdx.x % ntiles);
+  int n, nj;
+  tile_of_block(blockIdx.x, ntiles, gridDim.x / ntiles, alive != nullptr, n, nj);
   const int b = n / heads, h = n - b * heads;
-  const int n_iter = ntiles - nj;
-  const int n_half = 2 * n_iter;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -94,6 +92,8 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
   __shared__ float dz_tot[kGroups][kTile];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  __shared__ int top_s;
+  if (warp == 1) find_top_tile(alive, n, nj, ntiles, lane, &top_s);
   if (tid == 0) {
     mbar_init(&bar_kv, 1);
     for (int u = 0; u < kRing; ++u) {
@@ -120,6 +120,9 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
   tc_fence_after_sync();
   const uint32_t tmem = tmem_base_s;
   const uint32_t sa = smem_u32(smem);
+  const int mi_top = top_s;                 // the walk starts at the last query tile, or at the last live one
+  const int n_iter = mi_top - nj + 1;
+  const int n_half = 2 * n_iter;
 
   if (warp == kComputeThreads / 32) {
     // =============================== control warp: TMA loads and MMA issue ===============================
@@ -127,11 +130,11 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       const uint32_t idesc_t = instr_desc_bf16(128, 64, false, false);     // keys x 64 queries, K = D
       const uint32_t idesc_acc = instr_desc_bf16(128, 64, false, true);    // A K-major (keys x queries), B MN-major
       const uint32_t idesc_dq = instr_desc_bf16(128, 64, true, true);      // A MN-major (queries x keys), B MN-major
-      // Half index hn counts from the last query half: tile it = hn / 2 (query tile ntiles - 1 - it), upper half of
+      // Half index hn counts from the last query half: tile it = hn / 2 (query tile mi_top - it), upper half of
       // the tile first.  Its operands sit in ring slot hn % kRing.
       auto load_half = [&](int hn) {
         const int it = hn >> 1, hf = 1 - (hn & 1), slot = hn % kRing;
-        const int row0 = (ntiles - 1 - it) * kTile + hf * 64;
+        const int row0 = (mi_top - it) * kTile + hf * 64;
         uint8_t* st = smem + L::ring + slot * 3 * kHalfTile;
         mbar_expect_tx(&bar_ld[slot], (SELF ? 2 : 3) * kHalfTile);
         tma_load_4d(st, &map_q, &bar_ld[slot], 0, row0, h, b);
@@ -309,7 +312,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     auto fetch_carry = [&](int mi) {
       return (j < seq) ? load_ahead(carry + ((int64_t)b * (ntiles + 1) + mi + 1) * seq + j) : 0.f;
     };
-    float next_lse = fetch_lse(ntiles - 1), next_dbar = fetch_dbar(ntiles - 1), next_carry = fetch_carry(ntiles - 1);
+    float next_lse = fetch_lse(mi_top), next_dbar = fetch_dbar(mi_top), next_carry = fetch_carry(mi_top);
 
     // K and V rows from their landing tiles into TMEM as bf16 pairs (A operands of the score products); warpgroup
     // wg moves 16 of the 64 d columns = two 16-byte chunks = 8 packed columns of each matrix
@@ -358,7 +361,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 
     HalfState st;
     for (int it = 0; it < n_iter; ++it) {
-      const int mi = ntiles - 1 - it;
+      const int mi = mi_top - it;
       const int i0 = mi * kTile;
       const bool diag = (mi == nj);
       const uint32_t ph = (uint32_t)(it & 1);
@@ -493,11 +496,13 @@ int backward(const Problem& p, const float* lse2, const float* carry, const floa
     if (self)
       backward_kernel<true><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
           map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
+          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows,
+          static_cast<const uint8_t*>(p.tile_table));
     else
       backward_kernel<false><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
           map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
+          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows,
+          static_cast<const uint8_t*>(p.tile_table));
   }
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;

@@ -31,6 +31,43 @@ __device__ __forceinline__ float load_ahead(const float* p) {
   return v;
 }
 
+// Which (row n = batch x head, key tile nj) a CTA takes.  Dense: one row after the other, key tile 0 (the longest
+// walk) first.  With a table of live tiles most walks are a few tiles long, except those of the key tiles that hold an
+// exempt key, which stay live for every query tile: all rows' key tile 0 go first so that the long walks start together.
+__device__ __forceinline__ void tile_of_block(unsigned block, int ntiles, int nrows, bool sparse, int& n, int& nj) {
+  if (!sparse) {
+    n = (int)(block / ntiles);
+    nj = (int)(block % ntiles);
+  } else if ((int)block < nrows) {
+    n = (int)block;
+    nj = 0;
+  } else {
+    const unsigned r = block - nrows;
+    n = (int)(r / (ntiles - 1));
+    nj = 1 + (int)(r % (ntiles - 1));
+  }
+}
+
+// The last query tile from which key tile nj of row n gets anything: ntiles - 1, or with a table of live tiles
+// (alive[n][mi][nj], sa_tc_skip.cu) the largest live mi; the diagonal tile is always live.  One warp.
+__device__ __forceinline__ void find_top_tile(const uint8_t* alive, int n, int nj, int ntiles, int lane, int* top) {
+  int found = ntiles - 1;
+  if (alive != nullptr) {
+    const uint8_t* col = alive + (int64_t)n * ntiles * ntiles + nj;
+    found = nj;
+    for (int base = ntiles - 1; base >= nj; base -= 32) {
+      const int mi = base - lane;
+      const bool f = mi >= nj && col[(int64_t)mi * ntiles] != 0;
+      const unsigned m = __ballot_sync(0xffffffffu, f);
+      if (m != 0) {
+        found = base - (__ffs(m) - 1);
+        break;
+      }
+    }
+  }
+  if (lane == 0) *top = found;
+}
+
 // TMEM columns of the three score-shaped tiles (the same in both kernels)
 constexpr uint32_t kColZ = 256, kColX = 320, kColY = 384;
 

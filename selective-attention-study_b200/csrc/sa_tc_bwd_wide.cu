@@ -54,18 +54,16 @@ __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
     const float* __restrict__ lse2, const float* __restrict__ carry, const float* __restrict__ dbar,
     float* __restrict__ dq_acc, float* __restrict__ dq0, float* __restrict__ dk_acc, float* __restrict__ dk0,
     __nv_bfloat16* __restrict__ dv, int heads, int seq, int ntiles, int exempt, float scale, WaitCtx status,
-    RowLayout dv_rows) {
+    RowLayout dv_rows, const uint8_t* __restrict__ alive) {
   using L = Layout<SELF>;
   constexpr int D = 128;
   constexpr int kRingQD = L::ring_qd;
   // Consecutive CTAs: the two halves of the head dimension of one (row, key tile), then the row's next key tile, so
   // the CTAs resident at one time walk the same query tiles and share them through L2.
   const int dh = (int)(blockIdx.x & 1);
-  const int n = (int)((blockIdx.x >> 1) / ntiles);
-  const int nj = (int)((blockIdx.x >> 1) % ntiles);
+  int n, nj;
+  tile_of_block(blockIdx.x >> 1, ntiles, (gridDim.x >> 1) / ntiles, alive != nullptr, n, nj);
   const int b = n / heads, h = n - b * heads;
-  const int n_iter = ntiles - nj;
-  const int n_half = 2 * n_iter;
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -80,6 +78,8 @@ __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
   __shared__ float dz_tot[kGroups][kTile];
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  __shared__ int top_s;
+  if (warp == 1) find_top_tile(alive, n, nj, ntiles, lane, &top_s);
   if (tid == 0) {
     mbar_init(&bar_kv, 1);
     for (int u = 0; u < 3; ++u) {
@@ -107,6 +107,9 @@ __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
   tc_fence_after_sync();
   const uint32_t tmem = tmem_base_s;
   const uint32_t sa = smem_u32(smem);
+  const int mi_top = top_s;                 // the walk starts at the last query tile, or at the last live one
+  const int n_iter = mi_top - nj + 1;
+  const int n_half = 2 * n_iter;
   // One head per selector: this CTA computes dQ^T of the halves whose index (counted from the last) has its parity.
   auto owns = [&](int hn) { return !SELF || ((hn & 1) == dh); };
 
@@ -116,9 +119,9 @@ __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
       const uint32_t idesc_t = instr_desc_bf16(128, 64, false, false);     // keys x 64 queries, K = d
       const uint32_t idesc_acc = instr_desc_bf16(128, 64, false, true);    // A K-major (keys x queries), B MN-major
       const uint32_t idesc_dq = instr_desc_bf16(128, 64, true, true);      // A MN-major (d x keys), B MN-major (keys x queries)
-      // Half index hn counts from the last query half: tile it = hn / 2 (query tile ntiles - 1 - it), upper half of
+      // Half index hn counts from the last query half: tile it = hn / 2 (query tile mi_top - it), upper half of
       // the tile first.
-      auto row_of = [&](int hn) { return (ntiles - 1 - (hn >> 1)) * kTile + (1 - (hn & 1)) * 64; };
+      auto row_of = [&](int hn) { return (mi_top - (hn >> 1)) * kTile + (1 - (hn & 1)) * 64; };
       auto qd_off = [](int hn) { return (uint32_t)(L::qd + (hn % kRingQD) * 2 * kOpTile); };
       auto q0_off = [](int hn) { return (uint32_t)(L::q0 + (hn % kRing0) * kOpTile); };
       auto load_qd = [&](int hn) {
@@ -292,7 +295,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
     auto fetch_carry = [&](int mi) {
       return (j < seq) ? load_ahead(carry + ((int64_t)b * (ntiles + 1) + mi + 1) * seq + j) : 0.f;
     };
-    float next_lse = fetch_lse(ntiles - 1), next_dbar = fetch_dbar(ntiles - 1), next_carry = fetch_carry(ntiles - 1);
+    float next_lse = fetch_lse(mi_top), next_dbar = fetch_dbar(mi_top), next_carry = fetch_carry(mi_top);
 
     // V rows from the landing tile into TMEM as bf16 pairs; warpgroup wg moves 32 of the 128 d columns = four
     // 16-byte chunks of box wg / 2 = 16 packed columns
@@ -316,7 +319,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
     // is 32 consecutive floats of the fp32 gradient row
     float* const grad_rows = (SELF || dh == 0) ? dq_acc + (int64_t)n * seq * D : dq0 + (int64_t)b * seq * D;
     auto read_out = [&](int hn) {
-      const int i_first = (ntiles - 1 - (hn >> 1)) * kTile + (1 - (hn & 1)) * 64 + wg * kChunk;
+      const int i_first = (mi_top - (hn >> 1)) * kTile + (1 - (hn & 1)) * 64 + wg * kChunk;
       uint32_t r[16];
       tmem_ld16(lane_base + kColDQT + wg * kChunk, r);
       tmem_ld_wait();
@@ -328,7 +331,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
 
     HalfState st;
     for (int it = 0; it < n_iter; ++it) {
-      const int mi = ntiles - 1 - it;
+      const int mi = mi_top - it;
       const bool diag = (mi == nj);
       if (tid < kTile) {
         lse_s[tid] = -next_lse;                                // negated: both enter packed adds directly
@@ -447,11 +450,13 @@ int backward_wide(const Problem& p, const float* lse2, const float* carry, const
     if (self)
       backward_wide_kernel<true><<<grid, kThreads, smem, s>>>(
           map_q, map_k, map_v, map_do, map_q0, map_k0, lse2, carry, dbar, dq_acc, dq0, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
+          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows,
+          static_cast<const uint8_t*>(p.tile_table));
     else
       backward_wide_kernel<false><<<grid, kThreads, smem, s>>>(
           map_q, map_k, map_v, map_do, map_q0, map_k0, lse2, carry, dbar, dq_acc, dq0, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows);
+          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows,
+          static_cast<const uint8_t*>(p.tile_table));
   }
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;

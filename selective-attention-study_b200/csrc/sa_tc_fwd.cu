@@ -213,6 +213,7 @@ struct WideSmem {
 constexpr int kWideCompute = 512;                      // four warpgroups: 32 of a step's 128 key columns, D / 4 of the d each
 constexpr int kWideThreads = kWideCompute + 32;        // + the control warp: one lane issues every TMA load and MMA
 constexpr int kWideBarrier = 1;                        // hardware barrier id of the arithmetic warps
+constexpr int kMaxLiveTiles = 1024;                    // key tiles of a sequence when dead tiles are left out (sa_tc_skip.cu)
 
 template <int D, bool SELF>
 __global__ void __launch_bounds__(kWideThreads, 1)
@@ -221,7 +222,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
                         const __grid_constant__ CUtensorMap map_k0, const float* __restrict__ carry,
                         float* __restrict__ out, float* __restrict__ lse2, int heads, int seq, int ntiles, int exempt,
                         float scale, WaitCtx status, __nv_bfloat16* __restrict__ out_lowp, RowLayout out_lowp_rows,
-                        int q_offset) {
+                        int q_offset, const uint8_t* __restrict__ alive) {
   using L = WideSmem<D>;
   constexpr int DK = D / 64, DH = D / 4, NC = 32, ST = L::kStages;
   // TMEM columns: S and L0 (fp32, 128 each), the output accumulator (D), Q and Q0 as bf16 pairs (D / 2 each)
@@ -236,7 +237,6 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   const int n = blockIdx.x % nrows;
   const int b = n / heads, h = n - b * heads;
   const int i0 = mi * kTile;
-  const int steps = mi + 1;                                   // 128-key steps up to and including the diagonal tile
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -247,8 +247,22 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   __shared__ uint32_t tmem_base_s;
   __shared__ __align__(16) float carry_s[2][kTile];
   __shared__ float rmax_s[4][kTile];
+  __shared__ uint16_t live_s[kMaxLiveTiles + 1];              // with a table of live tiles: this query tile's key tiles,
+  __shared__ int live_count_s;                                //   nearest first
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (alive != nullptr && warp == 1) {
+    const uint8_t* live_row = alive + ((int64_t)n * ntiles + mi) * ntiles;
+    int cnt = 0;
+    for (int base = mi; base >= 0; base -= 32) {
+      const int nj = base - lane;
+      const bool f = nj >= 0 && live_row[nj] != 0;
+      const unsigned m = __ballot_sync(0xffffffffu, f);
+      if (f) live_s[cnt + __popc(m & ((1u << lane) - 1u))] = (uint16_t)nj;
+      cnt += __popc(m);
+    }
+    if (lane == 0) live_count_s = cnt;
+  }
   if (tid == 0) {
     mbar_init(&bar_q, 1);
     for (int u = 0; u < 2; ++u) {
@@ -271,11 +285,14 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   tc_fence_after_sync();
   const uint32_t tmem = tmem_base_s;
   const uint32_t sa = smem_u32(smem);
+  // 128-key steps: every key tile up to and including the diagonal one, or the live ones only.  Step index `it`
+  // counts from the diagonal (it = 0) back towards key 0; key_tile(it) is the tile it covers.
+  const int steps = (alive != nullptr) ? live_count_s : mi + 1;
+  auto key_tile = [&](int it) { return (alive != nullptr) ? (it < steps ? (int)live_s[it] : 0) : steps - 1 - it; };
 
   if (warp == kWideCompute / 32) {
     // =============================== control warp: TMA loads and MMA issue ===============================
     if (lane == 0) {
-      // Step index `it` counts from the diagonal (it = 0) back to key 0; its keys start at 128 (steps - 1 - it).
       // A tile of step it lives in stage slot(it); the j-th fill of a stage completes its barrier's phase j.
       auto slot = [](int it) { return ST == 2 ? (it & 1) : 0; };
       auto fill = [](int it) { return (uint32_t)((ST == 2 ? (it >> 1) : it) & 1); };
@@ -283,7 +300,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         uint64_t* bar = &bars[slot(it)];
         mbar_expect_tx(bar, L::kTileBytes);
         for (int s2 = 0; s2 < DK; ++s2)
-          tma_load_4d(smem + off + slot(it) * L::kTileBytes + s2 * kRowTile, map, bar, s2 * 64, (steps - 1 - it) * kTile, head, b);
+          tma_load_4d(smem + off + slot(it) * L::kTileBytes + s2 * kRowTile, map, bar, s2 * 64, key_tile(it) * kTile, head, b);
       };
       auto load_k = [&](int it) { load_tile(L::k, &map_k, bar_k, it, h); };
       auto load_k0 = [&](int it) { if (!SELF) load_tile(L::k0, &map_k0, bar_k0, it, 0); };   // SELF: K0 is K
@@ -439,13 +456,13 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     // The carry of a step's keys is fetched from global memory a step before it is staged, so the load's latency
     // is spent under the exponentials of the step before.
     auto fetch_carry = [&](int it) {
-      const int j = (steps - 1 - it) * kTile + tid;
+      const int j = key_tile(it) * kTile + tid;
       return (tid < kTile && it < steps && j < seq) ? load_ahead(carry_row + j) : 0.f;
     };
     // selection relu(L0) under the mask of step `it` -> bf16 tile, in two halves of 16 columns; also stages the
     // step's carry (scaled) for the logits pass
     auto selection = [&](int it, float carry_value) {
-      const int j0 = (steps - 1 - it) * kTile;
+      const int j0 = key_tile(it) * kTile;
       if (tid < kTile) carry_s[it & 1][tid] = -carry_value * kLog2e;   // negated: the logits pass adds it in an FMA
       mbar_wait(&bar_l0, it & 1, status, 313);
       tc_fence_after_sync();
@@ -480,7 +497,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     selection(0, fetch_carry(0));
     float next_carry = fetch_carry(1);
     for (int it = 0; it < steps; ++it) {
-      const int j0 = (steps - 1 - it) * kTile;
+      const int j0 = key_tile(it) * kTile;
       // ---- logits z = (S * scale - carry) * log2(e) after S -= TRI x selection, and the row maximum -----------
       mbar_wait(&bar_tri, it & 1, status, 314);
       tc_fence_after_sync();
@@ -638,6 +655,12 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   }
   SA_CUDA_CHECK(cudaGetLastError());
 
+  const uint8_t* alive = nullptr;                        // dead tiles are left out only when a whole sequence is computed
+  if (p.tile_table != nullptr && p.q_offset == 0 && ntiles <= kMaxLiveTiles) {
+    st = build_tile_table(p, carry, s);
+    if (st != SA_OK) return st;
+    alive = static_cast<const uint8_t*>(p.tile_table);
+  }
   const unsigned grid = (unsigned)(ntiles - mi_first) * p.batch * p.heads;
   const bool self = (p.heads == 1) && !p.external_selector;   // one head per selector: the selection logits are the head's own
   {
@@ -650,11 +673,11 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
       if (self)
         forward_wide_kernel<D, true><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2,
                                                                             p.heads, p.seq, ntiles, p.exempt, p.scale, status,
-                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows, p.q_offset);
+                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows, p.q_offset, alive);
       else
         forward_wide_kernel<D, false><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2,
                                                                              p.heads, p.seq, ntiles, p.exempt, p.scale, status,
-                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows, p.q_offset);
+                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows, p.q_offset, alive);
     }
     SA_CUDA_CHECK(cudaGetLastError());
     return SA_OK;

@@ -234,7 +234,8 @@ def _selection_carry32(q, k, sel, exempt: int, zero: bool):
     return carry
 
 
-def _forward(q, k, v, lowp: bool, exempt: int, damp: int, train_len: int, selector=None, zero_carry: bool = False):
+def _forward(q, k, v, lowp: bool, exempt: int, damp: int, train_len: int, selector=None, zero_carry: bool = False,
+             live_tiles: bool = False):
     lib = _lib.load()
     b, h, t, d = q.shape
     engine = _engine(lowp, d, False)
@@ -252,11 +253,18 @@ def _forward(q, k, v, lowp: bool, exempt: int, damp: int, train_len: int, select
     total = torch.empty(b, t, device=dev, dtype=torch.float32)
     prob = _problem(q, k, v, engine, exempt, damp, train_len)
     sel_ref = ctypes.byref(_selector_struct(*sel)) if sel is not None else None
+    table = None
+    if live_tiles and tc:
+        need = lib.sa_tile_table_bytes(ctypes.byref(prob))
+        if need:
+            table = torch.empty(need, device=dev, dtype=torch.uint8)
     with torch.cuda.device(dev):
-        st = lib.sa_forward_selector(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), sel_ref,
-                                     out.data_ptr(), lse2.data_ptr(), carry.data_ptr(), total.data_ptr(), _stream(dev))
+        st = lib.sa_forward_live_tiles(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), sel_ref,
+                                       out.data_ptr(), None, lse2.data_ptr(), carry.data_ptr(), total.data_ptr(),
+                                       table.data_ptr() if table is not None else None,
+                                       table.numel() if table is not None else 0, _stream(dev))
     _lib.check("sa_forward", st)
-    return out, lse2, carry, total, (q, k, v), sel, engine, carry_m
+    return out, lse2, carry, total, (q, k, v), sel, engine, carry_m, table
 
 
 def selective_attention_forward(
@@ -276,6 +284,7 @@ def selective_attention_forward(
     train_len: int = 0,
     selector=None,
     carry_rows: int | None = None,
+    skip_dead_tiles: bool = False,
 ):
     """Forward without autograd: fp32 (B, H, T, D).  With ``return_aux`` also a dict with ``rmax``
     (the row log-sum-exp in log2 units), ``rden`` (ones), ``carry``, ``carry_m`` and
@@ -289,7 +298,9 @@ def selective_attention_forward(
     rows, (B, T, D), from outside q / k (for a call that holds only some heads of each sequence);
     ``carry_rows=32`` (or the environment variable SA_B200_CARRY_ROWS=32) returns ``aux["carry"]`` with the
     reference's checkpoint every 32 queries whichever engine ran (an extra selection pass on the CUDA
-    cores); by default the spacing is the engine's own, reported in ``aux["carry_m"]``."""
+    cores); by default the spacing is the engine's own, reported in ``aux["carry_m"]``; ``skip_dead_tiles=True``
+    leaves out the (query tile, key tile) pairs whose probabilities are all exactly zero (see
+    ``selective_attention``)."""
     check_inputs(q, k, v)
     exempt = _check_exempt(exempt)
     lowp = _lowp(dot_precision, q.dtype)
@@ -300,8 +311,9 @@ def selective_attention_forward(
         raise ValueError("damp needs train_len (the trained context length)")
     selector = _check_selector(selector, q)
     carry_rows = _carry_rows_request(carry_rows) if return_aux else None
-    out, lse2, carry, total, operands, sel, _, carry_m = _forward(
-        q, k, v, lowp, exempt, _lib.DAMP_CODES[damp], train_len, selector=selector, zero_carry=return_aux)
+    out, lse2, carry, total, operands, sel, _, carry_m, table = _forward(
+        q, k, v, lowp, exempt, _lib.DAMP_CODES[damp], train_len, selector=selector, zero_carry=return_aux,
+        live_tiles=skip_dead_tiles)
     if not return_aux:
         return out
     b, h, t, _ = q.shape
@@ -311,6 +323,9 @@ def selective_attention_forward(
         carry, carry_m = _selection_carry32(operands[0], operands[1], sel, exempt, zero=True), 32
     aux = dict(rmax=lse2.view(b * h, t), rden=torch.ones(b * h, t, device=q.device, dtype=torch.float32),
                carry=carry[:, :(t + carry_m - 1) // carry_m], carry_m=carry_m, selected_total=total)
+    if table is not None:       # [row, query tile, key tile] != 0 where the tile was computed (entries above the diagonal unused)
+        nt = (t + 127) // 128
+        aux["live_tiles"] = table[: b * h * nt * nt].view(b * h, nt, nt)
     return out, aux
 
 
@@ -328,13 +343,23 @@ def _backward_call(ctx, dout, dq0=None, dk0=None):
     workspace = torch.empty(max(need, 1), device=dev, dtype=torch.uint8)
     dq, dk, dv = (torch.empty(q.shape, device=dev, dtype=q.dtype) for _ in range(3))
     sel_ref = ctypes.byref(_selector_struct(*sel)) if sel is not None else None
+    table = getattr(ctx, "tile_table", None)
     with torch.cuda.device(dev):
-        st = lib.sa_backward_selector(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), sel_ref,
-                                      out.data_ptr(), lse2.data_ptr(), carry.data_ptr(), dout.data_ptr(),
-                                      _DTYPE_CODE[dout.dtype], dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
-                                      dq0.data_ptr() if dq0 is not None else None,
-                                      dk0.data_ptr() if dk0 is not None else None, workspace.data_ptr(), need,
-                                      _stream(dev))
+        if table is not None:           # the forward left out dead tiles: the backward walks the same live ones
+            descs = [_tensor_struct(x) for x in (dout, dq, dk, dv)]
+            st = lib.sa_backward_live_tiles(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), sel_ref,
+                                            out.data_ptr(), lse2.data_ptr(), carry.data_ptr(),
+                                            *(ctypes.byref(x) for x in descs),
+                                            dq0.data_ptr() if dq0 is not None else None,
+                                            dk0.data_ptr() if dk0 is not None else None, workspace.data_ptr(), need,
+                                            table.data_ptr(), _stream(dev))
+        else:
+            st = lib.sa_backward_selector(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), sel_ref,
+                                          out.data_ptr(), lse2.data_ptr(), carry.data_ptr(), dout.data_ptr(),
+                                          _DTYPE_CODE[dout.dtype], dq.data_ptr(), dk.data_ptr(), dv.data_ptr(),
+                                          dq0.data_ptr() if dq0 is not None else None,
+                                          dk0.data_ptr() if dk0 is not None else None, workspace.data_ptr(), need,
+                                          _stream(dev))
     _lib.check("sa_backward", st)
     return dq, dk, dv
 
@@ -342,14 +367,15 @@ def _backward_call(ctx, dout, dq0=None, dk0=None):
 class _SelectiveAttentionFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, q, k, v, dot_precision, block_m, block_n, num_warps, bwd_block_n, bwd_num_warps,
-                bwd_num_stages, group, bwd_group, num_stages, exempt):
+                bwd_num_stages, group, bwd_group, num_stages, exempt, skip_dead_tiles=False):
         check_inputs(q, k, v)
         exempt = _check_exempt(exempt)
         lowp = _lowp(dot_precision, q.dtype)
         _check_blocks(block_m, block_n)
-        out, lse2, carry, _, operands, _, engine, _ = _forward(q, k, v, lowp, exempt, 0, 0)
+        out, lse2, carry, _, operands, _, engine, _, table = _forward(q, k, v, lowp, exempt, 0, 0,
+                                                                      live_tiles=skip_dead_tiles)
         ctx.save_for_backward(*operands, out, lse2, carry)
-        ctx.engine, ctx.exempt, ctx.bwd_group = engine, exempt, bwd_group
+        ctx.engine, ctx.exempt, ctx.bwd_group, ctx.tile_table = engine, exempt, bwd_group, table
         ctx.grad_dtypes = (q.dtype, k.dtype, v.dtype)
         return out
 
@@ -359,7 +385,7 @@ class _SelectiveAttentionFn(torch.autograd.Function):
         _check_bwd_group(ctx.bwd_group)
         grads = _backward_call(ctx, dout)
         grads = tuple(g if g.dtype == want else g.to(want) for g, want in zip(grads, ctx.grad_dtypes))
-        return grads + (None,) * 11
+        return grads + (None,) * 12
 
 
 class _SelectiveAttentionSelectorFn(torch.autograd.Function):
@@ -369,14 +395,15 @@ class _SelectiveAttentionSelectorFn(torch.autograd.Function):
     share a sequence sum these partial gradients (all-reduce) like any replicated parameter's."""
 
     @staticmethod
-    def forward(ctx, q, k, v, q0, k0, dot_precision, exempt):
+    def forward(ctx, q, k, v, q0, k0, dot_precision, exempt, skip_dead_tiles=False):
         check_inputs(q, k, v)
         exempt = _check_exempt(exempt)
         lowp = _lowp(dot_precision, q.dtype)
         selector = _check_selector((q0, k0), q)
-        out, lse2, carry, _, operands, sel, engine, _ = _forward(q, k, v, lowp, exempt, 0, 0, selector=selector)
+        out, lse2, carry, _, operands, sel, engine, _, table = _forward(q, k, v, lowp, exempt, 0, 0, selector=selector,
+                                                                        live_tiles=skip_dead_tiles)
         ctx.save_for_backward(*operands, out, lse2, carry, *sel)
-        ctx.engine, ctx.exempt = engine, exempt
+        ctx.engine, ctx.exempt, ctx.tile_table = engine, exempt, table
         ctx.grad_dtypes = (q.dtype, k.dtype, v.dtype)
         ctx.sel_shapes = (q0.shape, k0.shape, q0.dtype, k0.dtype)
         return out
@@ -391,7 +418,7 @@ class _SelectiveAttentionSelectorFn(torch.autograd.Function):
         grads = _backward_call(ctx, dout, dq0, dk0)
         grads = tuple(g if g.dtype == want else g.to(want) for g, want in zip(grads, ctx.grad_dtypes))
         q0_shape, k0_shape, q0_dtype, k0_dtype = ctx.sel_shapes
-        return grads + (dq0.reshape(q0_shape).to(q0_dtype), dk0.reshape(k0_shape).to(k0_dtype), None, None)
+        return grads + (dq0.reshape(q0_shape).to(q0_dtype), dk0.reshape(k0_shape).to(k0_dtype), None, None, None)
 
 
 def selective_attention(
@@ -411,6 +438,7 @@ def selective_attention(
     exempt: int = 1,
     *,
     selector=None,
+    skip_dead_tiles: bool = False,
 ) -> torch.Tensor:
     """Differentiable Selective Attention.  q / k / v: (B, H, T, D) CUDA tensors (fp16, bf16 or fp32;
     D in 16, 32, 64, 128; any strides).  Returns fp32 (B, H, T, D); gradients come back in the input
@@ -420,14 +448,21 @@ def selective_attention(
 
     ``selector=(q0, k0)`` (keyword-only, beyond the reference's signature) shards the heads of a sequence:
     q / k / v hold any subset of its heads and q0 / k0, (B, T, D), are a replica of the selection head's rows.
-    Gradients flow to q0 / k0 as this call's partial sums; sum them over the calls that share the selector."""
+    Gradients flow to q0 / k0 as this call's partial sums; sum them over the calls that share the selector.
+
+    ``skip_dead_tiles=True`` (keyword-only, beyond the reference, tensor-core engine, T <= 131072): after the selection
+    pass, 128 x 128 (query tile, key tile) pairs in which every probability is exactly zero -- far queries of keys that
+    many later queries have selected against; decided by a rigorous bound, never by a threshold on the result -- are
+    left out of the forward and the backward.  The results are those of the full computation (the forward bit for
+    bit); the time saved depends on how strongly the data selects."""
     if selector is not None:
         _check_blocks(block_m, block_n)
         _check_bwd_group(bwd_group)
         q0, k0 = selector
-        return _SelectiveAttentionSelectorFn.apply(q, k, v, q0, k0, dot_precision, exempt)
+        return _SelectiveAttentionSelectorFn.apply(q, k, v, q0, k0, dot_precision, exempt, bool(skip_dead_tiles))
     return _SelectiveAttentionFn.apply(q, k, v, dot_precision, block_m, block_n, num_warps, bwd_block_n,
-                                       bwd_num_warps, bwd_num_stages, group, bwd_group, num_stages, exempt)
+                                       bwd_num_warps, bwd_num_stages, group, bwd_group, num_stages, exempt,
+                                       bool(skip_dead_tiles))
 
 
 # ---- layout-fused form for a model's attention layer -------------------------------------------------

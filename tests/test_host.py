@@ -26,7 +26,7 @@ def test_library_exports_every_declared_symbol():
     assert set(_lib.EXPORTS) <= set(declared) and len(declared) >= 9
     for name in declared:
         assert hasattr(lib, name), name
-    assert lib.sa_abi_version() == 2
+    assert lib.sa_abi_version() == 3
     assert lib.sa_carry_rows(_lib.ENGINE_SIMT) == 32 and lib.sa_carry_rows(_lib.ENGINE_TCGEN05) == 128
     assert lib.sa_status_string(2) == b"unsupported shape, dtype or engine"
 

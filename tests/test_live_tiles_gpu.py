@@ -1,0 +1,117 @@
+"""Leaving out dead tiles (``skip_dead_tiles=True``): (query tile, key tile) pairs whose probabilities are all exactly
+zero are not computed.  The results must be those of the full computation: the forward bit for bit, the gradients up
+to the order of the fp32 reductions, and both within the usual bar of the oracle."""
+
+import pytest
+import torch
+
+import selective_oracle as oracle
+from selective_attention_b200 import _lib, kernels
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(batch, heads, seq, dim, seed, scale_qk=1.0):
+    g = torch.Generator("cpu").manual_seed(seed)
+    q, k, v, w = (torch.randn(batch, heads, seq, dim, generator=g) for _ in range(4))
+    return (q * scale_qk).bfloat16(), (k * scale_qk).bfloat16(), v.bfloat16(), w.bfloat16()
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-30))
+
+
+def _lower(live):
+    """The entries of the table that mean something: key tile <= query tile."""
+    nt = live.shape[-1]
+    mask = torch.tril(torch.ones(nt, nt, dtype=torch.bool, device=live.device))
+    return live[:, mask]
+
+
+def _run(q, k, v, w, skip, exempt=1):
+    qq, kk, vv = (t.cuda().requires_grad_(True) for t in (q, k, v))
+    out = kernels.selective_attention(qq, kk, vv, exempt=exempt, skip_dead_tiles=skip)
+    out.backward(w.cuda().float())
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    return out.detach(), qq.grad, kk.grad, vv.grad
+
+
+@pytest.mark.parametrize("heads,dim,seq", [(3, 64, 2049), (1, 64, 1500), (2, 128, 2049), (1, 128, 1300)])
+def test_results_equal_the_full_computation_when_most_far_tiles_are_dead(heads, dim, seq, achieved):
+    q, k, v, w = _inputs(2, heads, seq, dim, seed=seq + heads)
+    with torch.no_grad():
+        full, aux_full = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda(), return_aux=True)
+        before = _lib.launch_count()
+        lean, aux = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda(), return_aux=True, skip_dead_tiles=True)
+        assert _lib.launch_count() - before == 5          # colsum, scan, tile norms, tile table, forward
+    live = _lower(aux["live_tiles"])
+    nt = (seq + 127) // 128
+    frac = float((live != 0).float().mean())
+    achieved(f"live tiles T={seq} H={heads} D={dim} N(0,1)", live_fraction=frac)
+    assert frac < 0.9                                      # unit-variance q, k: keys ~500 positions back are dead
+    assert bool((aux["live_tiles"][:, torch.arange(nt), torch.arange(nt)] != 0).all())   # the diagonal is always computed
+    assert bool((aux["live_tiles"][:, :, 0] != 0).all())  # key tile 0 holds the exempt <BOS> key: never dead
+    assert torch.equal(lean, full)
+    assert torch.equal(aux["rmax"], aux_full["rmax"]) and torch.equal(aux["selected_total"], aux_full["selected_total"])
+
+    got = _run(q, k, v, w, skip=True)
+    ref = _run(q, k, v, w, skip=False)
+    assert torch.equal(got[0], ref[0])
+    for name, a, b in zip(("dq", "dk", "dv"), got[1:], ref[1:]):
+        assert _rel(a, b) < 2e-3, (name, _rel(a, b))       # the order of the fp32 reductions only
+    want = oracle.attention_grads(q.float(), k.float(), v.float(), w.float())
+    for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
+        assert _rel(a.cpu(), b) < 2e-2, (name, _rel(a.cpu(), b))
+
+
+def test_nothing_is_left_out_when_the_selection_is_weak():
+    q, k, v, w = _inputs(1, 2, 1500, 64, seed=5, scale_qk=0.05)
+    with torch.no_grad():
+        full = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda())
+        lean, aux = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda(), return_aux=True, skip_dead_tiles=True)
+    assert bool((_lower(aux["live_tiles"]) != 0).all())
+    assert torch.equal(lean, full)
+
+
+def test_exempt_prefix_keeps_its_key_tiles_alive():
+    q, k, v, w = _inputs(1, 2, 2049, 64, seed=6)
+    with torch.no_grad():
+        _, aux = kernels.selective_attention_forward(q.cuda(), k.cuda(), v.cuda(), return_aux=True, exempt=200,
+                                                     skip_dead_tiles=True)
+    live = aux["live_tiles"]
+    assert bool((live[:, :, 0] != 0).all())
+    assert bool((live[:, 1:, 1] != 0).all())               # keys 128..199 are exempt too
+    assert not bool((_lower(live) != 0).all())
+    got = _run(q, k, v, w, skip=True, exempt=200)
+    want = oracle.attention_grads(q.float(), k.float(), v.float(), w.float(), exempt=200)
+    for name, a, b in zip(("out", "dq", "dk", "dv"), got, want):
+        assert _rel(a.cpu(), b) < 2e-2, (name, _rel(a.cpu(), b))
+
+
+def test_head_halves_with_a_replicated_selector():
+    q, k, v, w = _inputs(1, 4, 1800, 64, seed=8)
+    ref = _run(q, k, v, w, skip=False)
+    outs, dqs = [], []
+    q0 = q[:, 0].cuda().requires_grad_(True)
+    k0 = k[:, 0].cuda().requires_grad_(True)
+    for hs in (slice(0, 2), slice(2, 4)):
+        qq, kk, vv = (t[:, hs].cuda().requires_grad_(True) for t in (q, k, v))
+        out = kernels.selective_attention(qq, kk, vv, selector=(q0, k0), skip_dead_tiles=True)
+        out.backward(w[:, hs].cuda().float())
+        outs.append(out.detach())
+        dqs.append(qq.grad)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert torch.equal(torch.cat(outs, 1), ref[0])
+    dq = torch.cat(dqs, 1).float()
+    dq[:, 0] += q0.grad.float()
+    assert _rel(dq, ref[1]) < 1e-2
+
+
+def test_unsupported_engines_ignore_the_request():
+    g = torch.Generator("cpu").manual_seed(1)
+    q, k, v = (torch.randn(1, 2, 200, 32, generator=g).cuda() for _ in range(3))
+    a = kernels.selective_attention_forward(q, k, v, skip_dead_tiles=True)
+    b = kernels.selective_attention_forward(q, k, v)
+    assert torch.equal(a, b)
