@@ -305,8 +305,10 @@ def run_ours(args, w, rank, world, device):
             if ranks == plan["group"]:
                 group = g
 
+    skip = bool(args.skip_dead_tiles)
+
     def operator(q, k, v, sel):
-        return kernels.selective_attention(q, k, v, selector=sel) if sel else kernels.selective_attention(q, k, v)
+        return kernels.selective_attention(q, k, v, selector=sel or None, skip_dead_tiles=skip)
 
     def reduce_selector_grads(sel, record=None):
         """The ranks that share a sequence sum their partial gradients of the replicated selector rows."""
@@ -339,7 +341,7 @@ def run_ours(args, w, rank, world, device):
             q.grad = k.grad = v.grad = None
         else:
             with torch.no_grad():
-                kernels.selective_attention_forward(q, k, v, return_aux=True, selector=sel or None)
+                kernels.selective_attention_forward(q, k, v, return_aux=True, selector=sel or None, skip_dead_tiles=skip)
             ev[1].record(); ev[2].record(); ev[3].record()
         ev[4].record()
         if record is not None:
@@ -390,7 +392,8 @@ def run_ours(args, w, rank, world, device):
     # ---- end-to-end arm: host buffers in, host buffers out ------------------------------------------------
     # Whole sequences with a shared selector go through the layer-facing call: one packed (B, T, 3, H, D) projection
     # output and one (B, T, H D) cotangent in, the merged output and the packed gradient out (the same bytes).
-    packed = w["backward"] and not w["per_head"] and not sel_h and w["dim"] in (64, 128) and args.e2e_call == "packed"
+    packed = (w["backward"] and not w["per_head"] and not sel_h and w["dim"] in (64, 128) and args.e2e_call == "packed"
+              and not skip)
     if packed:
         q_h, k_h, v_h, do_h = (t.transpose(1, 2) for t in (q_h, k_h, v_h, do_h))       # (B, T, H, D)
         qkv_h = torch.stack([q_h, k_h, v_h], dim=2).contiguous()                       # (B, T, 3, H, D)
@@ -457,7 +460,8 @@ def run_ours(args, w, rank, world, device):
                 results += [flat[:half].to(torch.bfloat16).view(sd[0].shape), flat[half:].to(torch.bfloat16).view(sd[1].shape)]
         else:
             with torch.no_grad():
-                results = [kernels.selective_attention_forward(qd, kd, vd, selector=sd or None).to(torch.bfloat16)]
+                results = [kernels.selective_attention_forward(qd, kd, vd, selector=sd or None,
+                                                               skip_dead_tiles=skip).to(torch.bfloat16)]
         consumed[slot].record(s_comp)
         done = torch.cuda.Event()
         done.record(s_comp)
@@ -503,13 +507,25 @@ def run_ours(args, w, rank, world, device):
     value = whole_job_tokens_per_second(tokens, ms_per_step)
     peak, peak_kind = measured_peaks()
     share = (len(plan["seqs"]) * len(plan["heads"])) / (w["batch"] * w["heads"])      # this rank's part of the batch
-    kflops = (flops["backward"] if w["backward"] else flops["forward"]) * share
+    live_fraction = None
+    if skip:                                 # the share of the causal tiles that was computed (this rank's shard)
+        with torch.no_grad():
+            _, aux = kernels.selective_attention_forward(q, k, v, return_aux=True, selector=sel or None, skip_dead_tiles=True)
+        live = aux.get("live_tiles")
+        if live is not None:
+            lower = torch.tril(torch.ones(live.shape[-1], live.shape[-1], dtype=torch.bool, device=live.device))
+            live_fraction = float((live[:, lower] != 0).float().mean())
+    kflops = (flops["backward"] if w["backward"] else flops["forward"]) * share * (live_fraction if live_fraction else 1.0)
     kernel_avg_ms = sum(kernel_ms) / max(len(kernel_ms), 1)
     achieved = kflops / (kernel_avg_ms * 1e-3) / 1e12 if kernel_ms else None
     ntile = math.ceil(w["seq"] / 128)
     head_tiles = len(plan["seqs"]) * len(plan["heads"]) * (ntile * (ntile + 1) // 2)
     per_tile = captured_traffic_per_head_tile(dominant if w["dim"] == 64 else f"{dominant}_d{w['dim']}")
     step_flops = (flops["forward"] + flops["backward"]) * (world if plan["scaling"] == "weak" else 1)
+    dense_step_flops = step_flops
+    if live_fraction:                        # rates below count the live tiles only
+        step_flops *= live_fraction
+        per_tile = None
     line = {
         "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": plan["scaling"],
@@ -520,11 +536,16 @@ def run_ours(args, w, rank, world, device):
                                f"{'whole batch per GPU' if plan['scaling'] == 'weak' else 'one batch over all GPUs'}",
                    "parallelism": plan["parallelism"],
                    "rank0_shard": f"sequences {plan['seqs'].start}..{plan['seqs'].stop - 1}, heads {plan['heads'].start}..{plan['heads'].stop - 1}",
+                   "tiles": ("every causal tile is computed" if not skip else
+                             "NOT the dense workload: (query tile, key tile) pairs whose probabilities are all exactly zero "
+                             f"are left out (results identical); live fraction {live_fraction}; the roofline's FLOPs are "
+                             "the algorithmic count times that fraction"),
                    "l2": "inputs (q, k, v, dO) of every rank exceed the 126 MB L2; no explicit flush",
                    "engine": "tcgen05", "fwd_ms": fwd_ms / args.steps, "bwd_ms": bwd_ms / args.steps,
                    "selector_grad_allreduce_ms": reduce_ms / args.steps if (sel and w["backward"]) else None,
                    "selector_grad_allreduce_bytes": (2 * sel[0].numel() * 4) if (sel and w["backward"]) else 0,
                    "algorithmic_tflop_per_step": step_flops / 1e12,
+                   "dense_workload_tflop_per_step": dense_step_flops / 1e12,
                    "attention_only_tflop_per_step": flops["attention_only"] * (world if plan["scaling"] == "weak" else 1) / 1e12,
                    "step_tflops_per_gpu": step_flops / world / (ms_per_step * 1e-3) / 1e12,
                    "frac_of_nominal_2250_per_gpu": step_flops / world / (ms_per_step * 1e-3) / 1e12 / NOMINAL_BF16_TFLOPS,
@@ -848,6 +869,8 @@ def main():
                     help="end-to-end arm: the layer-facing packed call (default where it applies) or the (B, H, T, D) call")
     ap.add_argument("--no-reference-gpu", action="store_true",
                     help="--impl reference: skip timing the reference's Triton kernels on the GPU")
+    ap.add_argument("--skip-dead-tiles", action="store_true",
+                    help="a separate row, not the headline: leave out tiles whose probabilities are all exactly zero")
     ap.add_argument("--replicas", action="store_true",
                     help="N > 1: every rank runs its own full batch (weak scaling) instead of a shard of one batch")
     args = ap.parse_args()
