@@ -119,6 +119,28 @@ def test_new_entry_points_check_their_arguments_before_any_launch():
     assert lib.sa_launch_count() >= 0
 
 
+def test_live_tile_entry_points_check_their_arguments_before_any_launch():
+    """The table of live tiles: its size, and the refusals that need no GPU."""
+    lib = _lib.load()
+    p = _lib.Problem()
+    p.struct_bytes = ctypes.sizeof(_lib.Problem)
+    p.dtype, p.engine, p.batch, p.heads, p.seq, p.head_dim, p.exempt = 1, 1, 2, 3, 1000, 64, 1
+    nt, rows = 8, 6
+    table = (rows * nt * nt + 255) // 256 * 256
+    assert lib.sa_tile_table_bytes(ctypes.byref(p)) == table + 2 * rows * nt * 4      # verdicts + the two norm arrays
+    p.seq = 131072 + 1                                           # more than 1024 key tiles: not offered
+    assert lib.sa_tile_table_bytes(ctypes.byref(p)) == 0
+    p.seq, p.head_dim = 1000, 32
+    assert lib.sa_tile_table_bytes(ctypes.byref(p)) == 0        # tensor-core shapes only
+    p.head_dim, p.engine = 64, 0
+    assert lib.sa_tile_table_bytes(ctypes.byref(p)) == 0        # CUDA-core engine
+    args = (16, 16, 16, None, 16, None, 16, 16, 16)
+    assert lib.sa_forward_live_tiles(ctypes.byref(p), *args, 256, 1 << 20, None) == 2
+    p.engine = 1
+    assert lib.sa_forward_live_tiles(ctypes.byref(p), *args, 256, 16, None) == 4      # table too small
+    assert lib.sa_forward_live_tiles(ctypes.byref(p), *args, 16, 1 << 20, None) == 3  # table not 256-byte aligned
+
+
 def test_selector_and_packed_arguments_are_validated_in_python():
     q = torch.randn(1, 2, 64, 64)
     with pytest.raises(ValueError, match="CUDA"):
