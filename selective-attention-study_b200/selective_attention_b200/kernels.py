@@ -489,7 +489,7 @@ class _SelectiveAttentionPackedFn(torch.autograd.Function):
     and dq, dk, dv are written by the backward's kernels into one (B, T, 3, H, D) gradient."""
 
     @staticmethod
-    def forward(ctx, qkv, exempt):
+    def forward(ctx, qkv, exempt, skip_dead_tiles=False):
         exempt = _check_exempt(exempt)
         lib = _lib.load()
         b, t, _, h, d = qkv.shape
@@ -503,12 +503,17 @@ class _SelectiveAttentionPackedFn(torch.autograd.Function):
         total = torch.empty(b, t, device=dev, dtype=torch.float32)
         prob = _problem(q, k, v, engine, exempt)
         low = _tensor_struct(merged.view(b, t, h, d).transpose(1, 2))
+        table = None
+        need = lib.sa_tile_table_bytes(ctypes.byref(prob)) if skip_dead_tiles else 0
+        if need:
+            table = torch.empty(need, device=dev, dtype=torch.uint8)
         with torch.cuda.device(dev):
-            st = lib.sa_forward_fused(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), None, out.data_ptr(),
-                                      ctypes.byref(low), lse2.data_ptr(), carry.data_ptr(), total.data_ptr(), _stream(dev))
+            st = lib.sa_forward_live_tiles(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), None,
+                                           out.data_ptr(), ctypes.byref(low), lse2.data_ptr(), carry.data_ptr(),
+                                           total.data_ptr(), table.data_ptr() if need else None, need, _stream(dev))
         _lib.check("sa_forward_fused", st)
         ctx.save_for_backward(qkv, out, lse2, carry)
-        ctx.exempt = exempt
+        ctx.exempt, ctx.tile_table = exempt, table
         return merged
 
     @staticmethod
@@ -528,22 +533,24 @@ class _SelectiveAttentionPackedFn(torch.autograd.Function):
         need = lib.sa_backward_workspace_bytes(ctypes.byref(prob))
         workspace = torch.empty(max(need, 1), device=dev, dtype=torch.uint8)
         descs = [_tensor_struct(x) for x in (d_merged.view(b, t, h, d).transpose(1, 2), dq, dk, dv)]
+        table = ctx.tile_table
         with torch.cuda.device(dev):
-            st = lib.sa_backward_fused(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), None, out.data_ptr(),
-                                       lse2.data_ptr(), carry.data_ptr(), *(ctypes.byref(x) for x in descs), None, None,
-                                       workspace.data_ptr(), need, _stream(dev))
+            st = lib.sa_backward_live_tiles(ctypes.byref(prob), q.data_ptr(), k.data_ptr(), v.data_ptr(), None,
+                                            out.data_ptr(), lse2.data_ptr(), carry.data_ptr(),
+                                            *(ctypes.byref(x) for x in descs), None, None, workspace.data_ptr(), need,
+                                            table.data_ptr() if table is not None else None, _stream(dev))
         _lib.check("sa_backward_fused", st)
-        return d_qkv, None
+        return d_qkv, None, None
 
 
-def selective_attention_packed(qkv: torch.Tensor, exempt: int = 1) -> torch.Tensor:
+def selective_attention_packed(qkv: torch.Tensor, exempt: int = 1, *, skip_dead_tiles: bool = False) -> torch.Tensor:
     """Differentiable Selective Attention on a fused projection output.  qkv: (B, T, 3, H, D) bf16, contiguous
     (``packed_supported``); returns (B, T, H * D) bf16, ready for the output projection.  Head 0 selects for all
     heads.  Same arithmetic as ``selective_attention`` on the three (B, H, T, D) views; what is saved is every
-    copy between the projections and the kernels."""
+    copy between the projections and the kernels.  ``skip_dead_tiles``: as in ``selective_attention``."""
     if not packed_supported(qkv):
         raise ValueError("qkv must be a contiguous bf16 CUDA tensor (B, T, 3, H, 64 or 128); use selective_attention otherwise")
-    return _SelectiveAttentionPackedFn.apply(qkv, exempt)
+    return _SelectiveAttentionPackedFn.apply(qkv, exempt, bool(skip_dead_tiles))
 
 
 # ---- cached decode ------------------------------------------------------------------------------------

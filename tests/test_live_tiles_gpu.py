@@ -109,6 +109,23 @@ def test_head_halves_with_a_replicated_selector():
     assert _rel(dq, ref[1]) < 1e-2
 
 
+def test_packed_projection_form():
+    g = torch.Generator("cpu").manual_seed(11)
+    b, t, h, d = 1, 1700, 2, 64
+    qkv = torch.randn(b, t, 3, h, d, generator=g).bfloat16().cuda()
+    w = torch.randn(b, t, h * d, generator=g).bfloat16().cuda()
+    res = []
+    for skip in (True, False):
+        x = qkv.clone().requires_grad_(True)
+        y = kernels.selective_attention_packed(x, skip_dead_tiles=skip)
+        y.backward(w)
+        res.append((y.detach(), x.grad))
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert torch.equal(res[0][0], res[1][0])
+    assert _rel(res[0][1], res[1][1]) < 2e-3
+
+
 def test_unsupported_engines_ignore_the_request():
     g = torch.Generator("cpu").manual_seed(1)
     q, k, v = (torch.randn(1, 2, 200, 32, generator=g).cuda() for _ in range(3))
