@@ -215,7 +215,7 @@ constexpr int kWideThreads = kWideCompute + 32;        // + the control warp: on
 constexpr int kWideBarrier = 1;                        // hardware barrier id of the arithmetic warps
 constexpr int kMaxLiveTiles = 1024;                    // key tiles of a sequence when dead tiles are left out (sa_tc_skip.cu)
 
-template <int D, bool SELF>
+template <int D, bool SELF, bool LIVE>   // LIVE: a table of live key tiles is given and the dead ones are left out
 __global__ void __launch_bounds__(kWideThreads, 1)
     forward_wide_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_q0,
@@ -251,7 +251,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   __shared__ int live_count_s;                                //   nearest first
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  if (alive != nullptr && warp == 1) {
+  if (LIVE && warp == 1) {
     const uint8_t* live_row = alive + ((int64_t)n * ntiles + mi) * ntiles;
     int cnt = 0;
     for (int base = mi; base >= 0; base -= 32) {
@@ -287,8 +287,8 @@ __global__ void __launch_bounds__(kWideThreads, 1)
   const uint32_t sa = smem_u32(smem);
   // 128-key steps: every key tile up to and including the diagonal one, or the live ones only.  Step index `it`
   // counts from the diagonal (it = 0) back towards key 0; key_tile(it) is the tile it covers.
-  const int steps = (alive != nullptr) ? live_count_s : mi + 1;
-  auto key_tile = [&](int it) { return (alive != nullptr) ? (it < steps ? (int)live_s[it] : 0) : steps - 1 - it; };
+  const int steps = LIVE ? live_count_s : mi + 1;
+  auto key_tile = [&](int it) { return LIVE ? (it < steps ? (int)live_s[it] : 0) : steps - 1 - it; };
 
   if (warp == kWideCompute / 32) {
     // =============================== control warp: TMA loads and MMA issue ===============================
@@ -663,25 +663,21 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   }
   const unsigned grid = (unsigned)(ntiles - mi_first) * p.batch * p.heads;
   const bool self = (p.heads == 1) && !p.external_selector;   // one head per selector: the selection logits are the head's own
-  {
-    const int wide_smem = WideSmem<D>::total + 1024;
-    if (self) SA_CUDA_CHECK(cudaFuncSetAttribute(forward_wide_kernel<D, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
-    else SA_CUDA_CHECK(cudaFuncSetAttribute(forward_wide_kernel<D, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
-    {
-      ProfileScope prof(SA_KERNEL_TC_FORWARD, s);
-      count_launch();
-      if (self)
-        forward_wide_kernel<D, true><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2,
-                                                                            p.heads, p.seq, ntiles, p.exempt, p.scale, status,
-                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows, p.q_offset, alive);
-      else
-        forward_wide_kernel<D, false><<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2,
-                                                                             p.heads, p.seq, ntiles, p.exempt, p.scale, status,
-                                                                            static_cast<__nv_bfloat16*>(p.out_lowp), p.out_lowp_rows, p.q_offset, alive);
-    }
-    SA_CUDA_CHECK(cudaGetLastError());
+  const int wide_smem = WideSmem<D>::total + 1024;
+  auto launch = [&](auto kernel) -> int {
+    SA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, wide_smem));
+    ProfileScope prof(SA_KERNEL_TC_FORWARD, s);
+    count_launch();
+    kernel<<<grid, kWideThreads, wide_smem, s>>>(map_q, map_k128, map_v128, map_q0, map_k0, carry, out, lse2, p.heads, p.seq,
+                                                 ntiles, p.exempt, p.scale, status, static_cast<__nv_bfloat16*>(p.out_lowp),
+                                                 p.out_lowp_rows, p.q_offset, alive);
     return SA_OK;
-  }
+  };
+  if (alive != nullptr) st = self ? launch(forward_wide_kernel<D, true, true>) : launch(forward_wide_kernel<D, false, true>);
+  else st = self ? launch(forward_wide_kernel<D, true, false>) : launch(forward_wide_kernel<D, false, false>);
+  if (st != SA_OK) return st;
+  SA_CUDA_CHECK(cudaGetLastError());
+  return SA_OK;
 }
 
 }  // namespace
