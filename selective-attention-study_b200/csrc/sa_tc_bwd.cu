@@ -60,7 +60,7 @@ struct Smem {
 // TMEM columns (Z, X, Y: sa_tc_bwd_passes.cuh)
 constexpr uint32_t kColK = 0, kColV = 32, kColDV = 64, kColDK = 128, kColDK0 = 192, kColDQ = 448;
 
-template <bool SELF>
+template <bool SELF, bool LIVE>   // LIVE: a table of live tiles is given (sa_tc_skip.cu)
 __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -75,7 +75,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
   // resident at one time belong to one or two rows and walk the same query tiles from the last one down, so every
   // Q, Q0, dO tile is fetched from DRAM once and then served from L2 to the row's other CTAs.
   int n, nj;
-  tile_of_block(blockIdx.x, ntiles, gridDim.x / ntiles, alive != nullptr, n, nj);
+  tile_of_block(blockIdx.x, ntiles, gridDim.x / ntiles, LIVE, n, nj);
   const int b = n / heads, h = n - b * heads;
 
   extern __shared__ uint8_t smem_raw[];
@@ -93,7 +93,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   __shared__ int top_s;
-  if (warp == 1) find_top_tile(alive, n, nj, ntiles, lane, &top_s);
+  if (LIVE && warp == 1) find_top_tile(alive, n, nj, ntiles, lane, &top_s);
   if (tid == 0) {
     mbar_init(&bar_kv, 1);
     for (int u = 0; u < kRing; ++u) {
@@ -120,7 +120,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
   tc_fence_after_sync();
   const uint32_t tmem = tmem_base_s;
   const uint32_t sa = smem_u32(smem);
-  const int mi_top = top_s;                 // the walk starts at the last query tile, or at the last live one
+  const int mi_top = LIVE ? top_s : ntiles - 1;   // the walk starts at the last query tile, or at the last live one
   const int n_iter = mi_top - nj + 1;
   const int n_half = 2 * n_iter;
 
@@ -488,22 +488,19 @@ int backward(const Problem& p, const float* lse2, const float* carry, const floa
   if (st != SA_OK) return st;
   const int smem = Smem::total + 1024;
   const bool self = (p.heads == 1) && !p.external_selector;   // one head per selector: the selection logits are the head's own
-  SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  SA_CUDA_CHECK(cudaFuncSetAttribute(backward_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  {
+  const uint8_t* alive = static_cast<const uint8_t*>(p.tile_table);
+  auto launch = [&](auto kernel) -> int {
+    SA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     ProfileScope prof(SA_KERNEL_TC_BACKWARD, s);
     count_launch();
-    if (self)
-      backward_kernel<true><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
-          map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows,
-          static_cast<const uint8_t*>(p.tile_table));
-    else
-      backward_kernel<false><<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
-          map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows,
-          static_cast<const uint8_t*>(p.tile_table));
-  }
+    kernel<<<(unsigned)ntiles * nrows, kThreads, smem, s>>>(
+        map_q, map_k, map_v, map_do, map_dq, map_dq0, map_q0, map_k0, lse2, carry, dbar, dk_acc, dk0,
+        static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows, alive);
+    return SA_OK;
+  };
+  if (alive != nullptr) st = self ? launch(backward_kernel<true, true>) : launch(backward_kernel<false, true>);
+  else st = self ? launch(backward_kernel<true, false>) : launch(backward_kernel<false, false>);
+  if (st != SA_OK) return st;
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;
 }

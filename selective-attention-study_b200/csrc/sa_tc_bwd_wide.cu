@@ -46,7 +46,7 @@ struct Layout {
 // TMEM columns (Z, X, Y: sa_tc_bwd_passes.cuh)
 constexpr uint32_t kColV = 0, kColDV = 64, kColDK = 128, kColDK0 = 192, kColDQT = 448;
 
-template <bool SELF>
+template <bool SELF, bool LIVE>   // LIVE: a table of live tiles is given (sa_tc_skip.cu)
 __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
@@ -62,7 +62,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
   // the CTAs resident at one time walk the same query tiles and share them through L2.
   const int dh = (int)(blockIdx.x & 1);
   int n, nj;
-  tile_of_block(blockIdx.x >> 1, ntiles, (gridDim.x >> 1) / ntiles, alive != nullptr, n, nj);
+  tile_of_block(blockIdx.x >> 1, ntiles, (gridDim.x >> 1) / ntiles, LIVE, n, nj);
   const int b = n / heads, h = n - b * heads;
 
   extern __shared__ uint8_t smem_raw[];
@@ -79,7 +79,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   __shared__ int top_s;
-  if (warp == 1) find_top_tile(alive, n, nj, ntiles, lane, &top_s);
+  if (LIVE && warp == 1) find_top_tile(alive, n, nj, ntiles, lane, &top_s);
   if (tid == 0) {
     mbar_init(&bar_kv, 1);
     for (int u = 0; u < 3; ++u) {
@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_wide_kernel(
   tc_fence_after_sync();
   const uint32_t tmem = tmem_base_s;
   const uint32_t sa = smem_u32(smem);
-  const int mi_top = top_s;                 // the walk starts at the last query tile, or at the last live one
+  const int mi_top = LIVE ? top_s : ntiles - 1;   // the walk starts at the last query tile, or at the last live one
   const int n_iter = mi_top - nj + 1;
   const int n_half = 2 * n_iter;
   // One head per selector: this CTA computes dQ^T of the halves whose index (counted from the last) has its parity.
@@ -439,25 +439,20 @@ int backward_wide(const Problem& p, const float* lse2, const float* carry, const
   if (st != SA_OK) return st;
   const bool self = (p.heads == 1) && !p.external_selector;   // one head per selector: the selection logits are the head's own
   const int smem = (self ? Layout<true>::total : Layout<false>::total) + 1024;
-  SA_CUDA_CHECK(cudaFuncSetAttribute(backward_wide_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Layout<true>::total + 1024));
-  SA_CUDA_CHECK(cudaFuncSetAttribute(backward_wide_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     Layout<false>::total + 1024));
-  {
+  const uint8_t* alive = static_cast<const uint8_t*>(p.tile_table);
+  const unsigned grid = 2u * (unsigned)ntiles * (unsigned)nrows;
+  auto launch = [&](auto kernel) -> int {
+    SA_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     ProfileScope prof(SA_KERNEL_TC_BACKWARD, s);
     count_launch();
-    const unsigned grid = 2u * (unsigned)ntiles * (unsigned)nrows;
-    if (self)
-      backward_wide_kernel<true><<<grid, kThreads, smem, s>>>(
-          map_q, map_k, map_v, map_do, map_q0, map_k0, lse2, carry, dbar, dq_acc, dq0, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows,
-          static_cast<const uint8_t*>(p.tile_table));
-    else
-      backward_wide_kernel<false><<<grid, kThreads, smem, s>>>(
-          map_q, map_k, map_v, map_do, map_q0, map_k0, lse2, carry, dbar, dq_acc, dq0, dk_acc, dk0,
-          static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale, status, p.dv_rows,
-          static_cast<const uint8_t*>(p.tile_table));
-  }
+    kernel<<<grid, kThreads, smem, s>>>(map_q, map_k, map_v, map_do, map_q0, map_k0, lse2, carry, dbar, dq_acc, dq0, dk_acc,
+                                        dk0, static_cast<__nv_bfloat16*>(dv), p.heads, p.seq, ntiles, p.exempt, p.scale,
+                                        status, p.dv_rows, alive);
+    return SA_OK;
+  };
+  if (alive != nullptr) st = self ? launch(backward_wide_kernel<true, true>) : launch(backward_wide_kernel<false, true>);
+  else st = self ? launch(backward_wide_kernel<true, false>) : launch(backward_wide_kernel<false, false>);
+  if (st != SA_OK) return st;
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;
 }
