@@ -36,6 +36,8 @@
 //
 // Reference for the arithmetic: src/selective_attention/kernels.py:196-268 (one head), :271-364 (the shared
 // selection-gradient products).
+#include <type_traits>
+
 #include "sa_tc_bwd_passes.cuh"
 
 namespace sa {
@@ -215,6 +217,7 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       issue_s(0);
       issue_dp(0);
 
+#pragma unroll 2   // the half's parity becomes a constant in each copy (-1.2 %; by six, to fix the ring slot too: +8 %)
       for (int hn = 0; hn < n_half; ++hn) {
         const int second = hn & 1, it = hn >> 1;               // second: the lower half, which completes a query tile
         const uint32_t ph = (uint32_t)(hn & 1);
@@ -360,10 +363,12 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
     };
 
     HalfState st;
-    for (int it = 0; it < n_iter; ++it) {
+    // One query tile.  The diagonal tile (the only one that needs the causal mask inside the tile) is the LAST of the
+    // walk, so the loop runs the unmasked form only and the masked form follows it once.
+    auto tile = [&](int it, auto diag_tag) {
+      constexpr bool kDiag = decltype(diag_tag)::value;
       const int mi = mi_top - it;
       const int i0 = mi * kTile;
-      const bool diag = (mi == nj);
       const uint32_t ph = (uint32_t)(it & 1);
       if (tid < kTile) {
         lse_s[tid] = -next_lse;                                // negated: both enter packed adds directly
@@ -377,14 +382,13 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
       }
       float sel_state = 0.f;         // selection of the tile's queries already visited, this key (raw logit units)
 
-#pragma unroll 1
+#pragma unroll   // both halves inline: with the masked form out of the loop this is worth 4.5 % (7 % for one head per selector)
       for (int hf = 1; hf >= 0; --hf) {
         const uint32_t hp = (uint32_t)(1 - hf);               // parity of this half's barrier phases
         // the staging tile is written next at the read-out that follows this half's dz pass (dQ0 of the previous
         // tile after the upper half, dQ of this tile after the lower half): its last reduce-add must have read it
         const bool drain = SELF ? (hf == 1 && it > 0) : ((it > 0) || (hf == 0));
-        if (diag) half_scores<true, SELF>(ctx, hf, hp, cnl, sel_state, st, &bar_l0, &bar_sel, &bar_s, &bar_dp, &bar_early, drain, true);
-        else half_scores<false, SELF>(ctx, hf, hp, cnl, sel_state, st, &bar_l0, &bar_sel, &bar_s, &bar_dp, &bar_early, drain, true);
+        half_scores<kDiag, SELF>(ctx, hf, hp, cnl, sel_state, st, &bar_l0, &bar_sel, &bar_s, &bar_dp, &bar_early, drain, true);
         if (hf == 1 && it > 0) {                               // the previous tile's last product, issued a half-tile ago:
           if (SELF) {                                          //   dQ = (dz + g) K, or dQ0 = g K0
             mbar_wait(&bar_dq, (uint32_t)((it - 1) & 1), status, 413);
@@ -407,7 +411,9 @@ __global__ void __launch_bounds__(kThreads, 1) backward_kernel(
         tc_fence_after_sync();
         read_out(&bar_dqread, &map_dq, i0, n);
       }
-    }
+    };
+    for (int it = 0; it + 1 < n_iter; ++it) tile(it, std::false_type{});
+    tile(n_iter - 1, std::true_type{});
     {                                                          // the first query tile's last product, visited last
       mbar_wait(SELF ? &bar_dq : &bar_dq0, (uint32_t)((n_iter - 1) & 1), status, 414);
       tc_fence_after_sync();
