@@ -16,6 +16,8 @@
 //                   the exponentials.  head_dim 64 and 128.
 //
 // Reference for the arithmetic: src/selective_attention/kernels.py:100-194 (selection, carry, forward).
+#include <type_traits>
+
 #include "sa_tc_host.cuh"
 #include "sa_tc_ptx.cuh"
 
@@ -497,7 +499,10 @@ __global__ void __launch_bounds__(kWideThreads, 1)
     float run_max = -INFINITY, run_den = 0.f;                  // run_den: this warpgroup's share of the denominator
     selection(0, fetch_carry(0));
     float next_carry = fetch_carry(1);
-    for (int it = 0; it < steps; ++it) {
+    // One 128-key step.  The diagonal step (it = 0: causal mask inside the tile, nothing to wait for or rescale yet) is
+    // peeled off the loop.
+    auto step = [&](int it, auto first_tag) {
+      constexpr bool kFirst = decltype(first_tag)::value;
       const int j0 = key_tile(it) * kTile;
       // ---- logits z = (S * scale - carry) * log2(e) after S -= TRI x selection, and the row maximum -----------
       mbar_wait(&bar_tri, it & 1, status, 314);
@@ -518,7 +523,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
                                 make_float2(nc.x, nc.y));
           float2 b2 = __ffma2_rn(make_float2(__uint_as_float(r[4 * e4 + 2]), __uint_as_float(r[4 * e4 + 3])), cc,
                                  make_float2(nc.z, nc.w));
-          if (it == 0) {                                       // the diagonal tile
+          if (kFirst) {                                        // the diagonal tile
             const int jj = j0 + cw + 4 * e4;
             if (jj > i) a.x = -INFINITY;
             if (jj + 1 > i) a.y = -INFINITY;
@@ -552,7 +557,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
         rs = __fadd2_rn(rs, z[e]);
       }
       run_den = run_den * alpha + (rs.x + rs.y);
-      if (it > 0) {
+      if (!kFirst) {
         mbar_wait(&bar_pv, (it - 1) & 1, status, 323);         // P V of the previous step: P tile and O are free
         tc_fence_after_sync();
       }
@@ -569,7 +574,7 @@ __global__ void __launch_bounds__(kWideThreads, 1)
           *reinterpret_cast<uint4*>(smem + L::p + (wg >> 1) * kRowTile + swz_off(row, (wg & 1) * 4 + c)) = w;
         }
       }
-      if (it > 0 && __any_sync(0xffffffffu, alpha != 1.f)) {   // the accumulator follows the maximum while it moves
+      if (!kFirst && __any_sync(0xffffffffu, alpha != 1.f)) {  // the accumulator follows the maximum while it moves
         uint32_t r[DH];
         tmem_ld_n<DH>(lane_base + kColO + wg * DH, r);
         tmem_ld_wait();
@@ -579,7 +584,9 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       }
       tmem_st_wait();                                          // P (head_dim 64) and the rescaled accumulator are in TMEM
       arrive(&bar_p);
-    }
+    };
+    step(0, std::true_type{});
+    for (int it = 1; it < steps; ++it) step(it, std::false_type{});
     mbar_wait(&bar_fin, 0, status, 316);                       // the last P V
     tc_fence_after_sync();
 
