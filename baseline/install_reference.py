@@ -3,7 +3,7 @@
 against this repository's drop-in module (``tests/test_reference_suite_gpu.py``) and (b) time the reference's own
 code in ``bench.py --impl reference``.
 
-    python baseline/install_reference.py [/path/to/reference/checkout]
+    python baseline/install_reference.py /path/to/reference/checkout
 
 Nothing from the reference enters this repository's history: ``baseline/_ref/`` is listed in ``.gitignore``.
 The install is the offline pip recipe (no index, no build isolation) from a scratch copy of the checkout,
@@ -43,4 +43,6 @@ def install(checkout: str) -> str:
 
 
 if __name__ == "__main__":
-    print(install(sys.argv[1] if len(sys.argv) > 1 else "/root/reference"))
+    if len(sys.argv) != 2:
+        raise SystemExit("usage: python baseline/install_reference.py /path/to/reference/checkout")
+    print(install(sys.argv[1]))
