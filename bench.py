@@ -411,44 +411,30 @@ def run_ours(args, w, rank, world, device):
     h2d = sum(t.numel() * t.element_size() for t in pinned_in)
     d2h = sum(t.numel() * t.element_size() for t in pinned_out)
 
-    # Every step copies its own inputs in and its own results out; the copies of neighbouring steps run on
-    # their own streams, so step i's compute overlaps step i+1's upload and step i-1's download, as a serving
-    # or training loop that feeds the operator from host memory would arrange it.
+    # Every step copies its own inputs in and its own results out.  The copies run on their own streams and a step is
+    # fed sequence by sequence: sequence k + 1 of a step (and then the next step's first) is uploaded while sequence k
+    # is computed, and sequence k's results are downloaded under the next computation, as a training or serving loop
+    # that feeds the operator from host memory would arrange it.  Only the first upload and the last download of the
+    # timed region are not hidden.
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
     s_comp = torch.cuda.current_stream(device)
     dev_in = [[torch.empty_like(t, device=device) for t in pinned_in] for _ in range(2)]
-    uploaded = [torch.cuda.Event() for _ in range(2)]
+    n_chunks = pinned_in[0].shape[0]                          # this rank's sequences (every tensor has them on axis 0)
+    uploaded = [[torch.cuda.Event() for _ in range(n_chunks)] for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
     downloaded = torch.cuda.Event()
 
-    def e2e_step(i: int):
-        slot = i & 1
-        with torch.cuda.stream(s_in):
-            if i >= 2:
-                s_in.wait_event(consumed[slot])            # the compute of step i - 2 has read this slot
-            for dst, src in zip(dev_in[slot], pinned_in):
-                dst.copy_(src, non_blocking=True)
-            uploaded[slot].record(s_in)
-        s_comp.wait_event(uploaded[slot])
+    def e2e_compute(chunk):
+        """One sequence (all of this rank's heads) through the public call; returns what goes back to the host."""
         if packed:
-            xd = dev_in[slot][0].detach().requires_grad_(True)
+            xd = chunk[0].detach().requires_grad_(True)
             y = kernels.selective_attention_packed(xd)
-            y.backward(dev_in[slot][1])
-            results = [y.detach(), xd.grad]
-            consumed[slot].record(s_comp)
-            done = torch.cuda.Event()
-            done.record(s_comp)
-            with torch.cuda.stream(s_out):
-                s_out.wait_event(done)
-                for dst, src in zip(pinned_out, results):
-                    src.record_stream(s_out)
-                    dst.copy_(src, non_blocking=True)
-                downloaded.record(s_out)
-            return
-        qd, kd, vd = (t.detach() for t in dev_in[slot][:3])
-        sd = tuple(t.detach() for t in dev_in[slot][n_main:])
+            y.backward(chunk[1])
+            return [y.detach(), xd.grad]
+        qd, kd, vd = (t.detach() for t in chunk[:3])
+        sd = tuple(t.detach() for t in chunk[n_main:])
         if w["backward"]:
-            dd = dev_in[slot][3].float()
+            dd = chunk[3].float()
             for t in (qd, kd, vd) + sd:
                 t.requires_grad_(True)
             out = operator(qd, kd, vd, sd)
@@ -458,19 +444,32 @@ def run_ours(args, w, rank, world, device):
                 flat = reduce_selector_grads(sd)
                 half = flat.numel() // 2
                 results += [flat[:half].to(torch.bfloat16).view(sd[0].shape), flat[half:].to(torch.bfloat16).view(sd[1].shape)]
-        else:
-            with torch.no_grad():
-                results = [kernels.selective_attention_forward(qd, kd, vd, selector=sd or None,
-                                                               skip_dead_tiles=skip).to(torch.bfloat16)]
-        consumed[slot].record(s_comp)
-        done = torch.cuda.Event()
-        done.record(s_comp)
-        with torch.cuda.stream(s_out):
-            s_out.wait_event(done)
-            for dst, src in zip(pinned_out, results):
-                src.record_stream(s_out)
-                dst.copy_(src, non_blocking=True)
-            downloaded.record(s_out)
+            return results
+        with torch.no_grad():
+            return [kernels.selective_attention_forward(qd, kd, vd, selector=sd or None,
+                                                        skip_dead_tiles=skip).to(torch.bfloat16)]
+
+    def e2e_step(i: int):
+        slot = i & 1
+        for c in range(n_chunks):
+            with torch.cuda.stream(s_in):
+                if i >= 2 and c == 0:
+                    s_in.wait_event(consumed[slot])        # the compute of step i - 2 has read this slot
+                for dst, src in zip(dev_in[slot], pinned_in):
+                    dst[c:c + 1].copy_(src[c:c + 1], non_blocking=True)
+                uploaded[slot][c].record(s_in)
+            s_comp.wait_event(uploaded[slot][c])
+            results = e2e_compute([t[c:c + 1] for t in dev_in[slot]])
+            if c == n_chunks - 1:
+                consumed[slot].record(s_comp)
+            done = torch.cuda.Event()
+            done.record(s_comp)
+            with torch.cuda.stream(s_out):
+                s_out.wait_event(done)
+                for dst, src in zip(pinned_out, results):
+                    src.record_stream(s_out)
+                    dst[c:c + 1].copy_(src, non_blocking=True)
+                downloaded.record(s_out)
 
     for i in range(2):
         e2e_step(i)
@@ -553,6 +552,7 @@ def run_ours(args, w, rank, world, device):
         "e2e": {"value": whole_job_tokens_per_second(tokens, e2e_ms), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h, "ms_per_step": e2e_ms, "steps": args.steps,
                 "copies_alone_gbs": {"h2d": h2d_gbs, "d2h": d2h_gbs}, "bytes_are": "per rank",
+                "pipelining": f"{n_chunks} sequence(s) per step, one call each; uploads, computation and downloads on three streams",
                 "call": "selective_attention_packed (fused QKV layout in, merged output and packed gradient out)" if packed
                         else "selective_attention / selective_attention_forward on (B, H, T, D) tensors"},
         "gpu_launches": launches,
