@@ -76,8 +76,8 @@ __device__ __forceinline__ void put_words(uint8_t* base, int row, int c0, const 
 }
 
 struct HalfState {
-  float negon[16];     // -1 where the (query, key) pair is selected, else 0
-  float lx[16];        // exclusive suffix sums of dz inside this thread's chunk
+  float gate[16];      // 1 where the (query, key) pair is selected, else 0
+  float lx[16];        // NEGATED exclusive suffix sums of dz inside this thread's chunk (the g pass wants -U)
   float dz[16];        // one head per selector only: dz, which the g pass adds to g before the products
 };
 
@@ -118,12 +118,17 @@ __device__ __forceinline__ void half_scores(const Ctx& c, int hf, uint32_t phase
   }
   tmem_ld_wait();
 #pragma unroll
-  for (int e = 0; e < 16; ++e) {
+  for (int e = 0; e < 16; ++e) {                            // the gate as 1 / 0: one compare-and-set per element ...
     const float l0 = __uint_as_float(r[e]);
     bool on = c.selectable && (l0 > 0.f);
     if (DIAG) on = on && (c.row < col0 + e);                // key strictly before the query
-    st.negon[e] = on ? -1.f : 0.f;
-    ls[e] = on ? l0 : 0.f;
+    st.gate[e] = on ? 1.f : 0.f;
+  }
+#pragma unroll
+  for (int e = 0; e < 16; e += 2) {                         // ... and the selected logits as a packed product
+    const float2 v = __fmul2_rn(make_float2(__uint_as_float(r[e]), __uint_as_float(r[e + 1])),
+                                make_float2(st.gate[e], st.gate[e + 1]));
+    ls[e] = v.x; ls[e + 1] = v.y;
   }
 #pragma unroll
   for (int e = 6; e >= 0; --e) {                            // inclusive suffix sums, two chains
@@ -208,17 +213,17 @@ __device__ __forceinline__ void half_scores(const Ctx& c, int hf, uint32_t phase
     }
   }
 
-  st.lx[15] = 0.f;                                          // exclusive suffix sums of dz, two chains
+  st.lx[15] = 0.f;                                          // NEGATED exclusive suffix sums of dz, two chains
   st.lx[7] = 0.f;
 #pragma unroll
   for (int e = 6; e >= 0; --e) {
-    st.lx[e] = st.lx[e + 1] + p[e + 1];
-    st.lx[e + 8] = st.lx[e + 9] + p[e + 9];
+    st.lx[e] = st.lx[e + 1] - p[e + 1];
+    st.lx[e + 8] = st.lx[e + 9] - p[e + 9];
   }
-  const float tot_hi = st.lx[8] + p[8];
+  const float tot_hi = st.lx[8] - p[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) st.lx[e] += tot_hi;
-  c.dz_tot[c.wg][c.row] = st.lx[0] + p[0];
+  c.dz_tot[c.wg][c.row] = p[0] - st.lx[0];
   fence_async_smem();                                       // dz half tile -> visible to the MMAs
   tmem_st_wait();                                           // P^T and dz^T in TMEM
   tc_fence_before_sync();
@@ -241,15 +246,15 @@ __device__ __forceinline__ void half_gate(const Ctx& c, int hf, float& dz_state,
   }
   const float base = dz_state + later;
   dz_state += all;
-  const float2 bb = make_float2(base, base);
+  const float2 bb = make_float2(-base, -base);                   // lx holds negated sums: gate * (-(sum + base))
 #pragma unroll
   for (int e = 0; e < 16; e += 2) {
     float2 x;
     if (SELF)                                                    // dz + g: Q0 = Q and K0 = K, so the two gradient paths add
-      x = __ffma2_rn(make_float2(st.negon[e], st.negon[e + 1]), __fadd2_rn(make_float2(st.lx[e], st.lx[e + 1]), bb),
+      x = __ffma2_rn(make_float2(st.gate[e], st.gate[e + 1]), __fadd2_rn(make_float2(st.lx[e], st.lx[e + 1]), bb),
                      make_float2(st.dz[e], st.dz[e + 1]));
     else
-      x = __fmul2_rn(make_float2(st.negon[e], st.negon[e + 1]), __fadd2_rn(make_float2(st.lx[e], st.lx[e + 1]), bb));
+      x = __fmul2_rn(make_float2(st.gate[e], st.gate[e + 1]), __fadd2_rn(make_float2(st.lx[e], st.lx[e + 1]), bb));
     st.lx[e] = x.x; st.lx[e + 1] = x.y;
   }
   uint32_t w8[8];
