@@ -419,7 +419,8 @@ def run_ours(args, w, rank, world, device):
     s_in, s_out = torch.cuda.Stream(device), torch.cuda.Stream(device)
     s_comp = torch.cuda.current_stream(device)
     dev_in = [[torch.empty_like(t, device=device) for t in pinned_in] for _ in range(2)]
-    n_chunks = pinned_in[0].shape[0]                          # this rank's sequences (every tensor has them on axis 0)
+    n_chunks = len(plan["seqs"])                               # this rank's sequences; every tensor has their rows on axis 0
+    rows_per_chunk = pinned_in[0].shape[0] // n_chunks         #   (per-head form: the heads of a sequence are its rows)
     uploaded = [[torch.cuda.Event() for _ in range(n_chunks)] for _ in range(2)]
     consumed = [torch.cuda.Event() for _ in range(2)]
     downloaded = torch.cuda.Event()
@@ -452,14 +453,15 @@ def run_ours(args, w, rank, world, device):
     def e2e_step(i: int):
         slot = i & 1
         for c in range(n_chunks):
+            lo, hi = c * rows_per_chunk, (c + 1) * rows_per_chunk
             with torch.cuda.stream(s_in):
                 if i >= 2 and c == 0:
                     s_in.wait_event(consumed[slot])        # the compute of step i - 2 has read this slot
                 for dst, src in zip(dev_in[slot], pinned_in):
-                    dst[c:c + 1].copy_(src[c:c + 1], non_blocking=True)
+                    dst[lo:hi].copy_(src[lo:hi], non_blocking=True)
                 uploaded[slot][c].record(s_in)
             s_comp.wait_event(uploaded[slot][c])
-            results = e2e_compute([t[c:c + 1] for t in dev_in[slot]])
+            results = e2e_compute([t[lo:hi] for t in dev_in[slot]])
             if c == n_chunks - 1:
                 consumed[slot].record(s_comp)
             done = torch.cuda.Event()
@@ -468,7 +470,7 @@ def run_ours(args, w, rank, world, device):
                 s_out.wait_event(done)
                 for dst, src in zip(pinned_out, results):
                     src.record_stream(s_out)
-                    dst[c:c + 1].copy_(src, non_blocking=True)
+                    dst[lo:hi].copy_(src, non_blocking=True)
                 downloaded.record(s_out)
 
     for i in range(2):
