@@ -253,12 +253,18 @@ int sa_backward_fused(const sa_problem* p, const void* q, const void* k, const v
  *   sa_tile_table_bytes     size of the table for a problem; 0 when leaving out tiles is not offered for it.
  *   sa_forward_live_tiles   sa_forward_fused plus the table (256-byte aligned device memory; contents undefined on
  *                           entry; NULL: identical to sa_forward_fused).
- *   sa_backward_live_tiles  sa_backward_fused plus the table the forward filled (NULL: identical to it). */
+ *   sa_backward_live_tiles  sa_backward_fused plus the table the forward filled (NULL: identical to it).
+ *   sa_prefill_extend_live_tiles  sa_prefill_extend plus a table sized for the problem it is given (seq = cached + new
+ *                           tokens): a long prompt prefilled in chunks skips the dead part of the cache. */
 size_t sa_tile_table_bytes(const sa_problem* p);
 int sa_forward_live_tiles(const sa_problem* p, const void* q, const void* k, const void* v,
                           const sa_selector* sel,
                           float* out, const sa_tensor* out_lowp, float* lse2, float* carry, float* total,
                           void* tile_table, size_t tile_table_bytes, void* stream);
+int sa_prefill_extend_live_tiles(const sa_problem* p, int cached, const void* q_new, const void* k_cache,
+                                 const void* v_cache, const float* selected, int64_t selected_stride,
+                                 float* out, float* lse2, float* carry, float* total,
+                                 void* tile_table, size_t tile_table_bytes, void* stream);
 int sa_backward_live_tiles(const sa_problem* p, const void* q, const void* k, const void* v,
                            const sa_selector* sel,
                            const float* out, const float* lse2, const float* carry,

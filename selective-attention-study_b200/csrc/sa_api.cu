@@ -245,6 +245,14 @@ int sa_forward(const sa_problem* in, const void* q, const void* k, const void* v
 int sa_prefill_extend(const sa_problem* in, int cached, const void* q_new, const void* k_cache, const void* v_cache,
                       const float* selected, int64_t selected_stride, float* out, float* lse2, float* carry, float* total,
                       void* stream) {
+  return sa_prefill_extend_live_tiles(in, cached, q_new, k_cache, v_cache, selected, selected_stride, out, lse2, carry, total,
+                                      nullptr, 0, stream);
+}
+
+int sa_prefill_extend_live_tiles(const sa_problem* in, int cached, const void* q_new, const void* k_cache,
+                                 const void* v_cache, const float* selected, int64_t selected_stride, float* out,
+                                 float* lse2, float* carry, float* total, void* tile_table, size_t tile_table_bytes,
+                                 void* stream) {
   Problem p;
   int st = to_problem(in, q_new, k_cache, v_cache, nullptr, &p);
   if (st != SA_OK) return st;
@@ -254,6 +262,13 @@ int sa_prefill_extend(const sa_problem* in, int cached, const void* q_new, const
   st = tc_supported(p);
   if (st != SA_OK) return st;
   if (tc::timeout_pending()) return SA_ERR_DEVICE_TIMEOUT;
+  if (tile_table != nullptr) {
+    const size_t need = tc::tile_table_bytes(p);
+    if (need == 0) return SA_ERR_UNSUPPORTED;
+    if (tile_table_bytes < need) return SA_ERR_WORKSPACE;
+    if ((reinterpret_cast<uintptr_t>(tile_table) & 255) != 0) return SA_ERR_ALIGNMENT;
+    p.tile_table = tile_table;
+  }
   p.q_offset = cached;
   p.carry_init = selected;
   p.carry_init_stride = selected_stride;

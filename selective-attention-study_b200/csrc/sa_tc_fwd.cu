@@ -663,8 +663,8 @@ int forward_impl(const Problem& p, float* out, float* lse2, float* carry, float*
   }
   SA_CUDA_CHECK(cudaGetLastError());
 
-  const uint8_t* alive = nullptr;                        // dead tiles are left out only when a whole sequence is computed
-  if (p.tile_table != nullptr && p.q_offset == 0 && ntiles <= kMaxLiveTiles) {
+  const uint8_t* alive = nullptr;
+  if (p.tile_table != nullptr && ntiles <= kMaxLiveTiles) {
     st = build_tile_table(p, carry, s);
     if (st != SA_OK) return st;
     alive = static_cast<const uint8_t*>(p.tile_table);

@@ -29,18 +29,19 @@ constexpr int kTile = 128;
 constexpr float kDeadMargin = 150.f;
 
 // Largest row norm of each 128-row tile of q (z = 0) and k (z = 1): one block per (tile, row n, tensor), one thread
-// per token.
+// per token.  Tiles are counted in absolute positions; the query tensor starts at position q_offset (a prefill that
+// continues from a cache), the key tensor at 0.
 template <int D>
 __global__ void __launch_bounds__(kTile) tile_norms_kernel(const __nv_bfloat16* __restrict__ q, RowLayout q_rows,
                                                            const __nv_bfloat16* __restrict__ k, RowLayout k_rows,
-                                                           int heads, int seq, int ntiles, float* __restrict__ qn,
-                                                           float* __restrict__ kn) {
+                                                           int heads, int seq, int ntiles, int q_offset,
+                                                           float* __restrict__ qn, float* __restrict__ kn) {
   const int tile = blockIdx.x, n = blockIdx.y, which = blockIdx.z;
   const int b = n / heads, h = n - b * heads;
   const int t = tile * kTile + threadIdx.x;
   float ss = 0.f;
-  if (t < seq) {
-    const __nv_bfloat16* row = which == 0 ? q + q_rows.at(b, h, t) : k + k_rows.at(b, h, t);
+  if (t < seq && (which == 1 || t >= q_offset)) {
+    const __nv_bfloat16* row = which == 0 ? q + q_rows.at(b, h, t - q_offset) : k + k_rows.at(b, h, t);
 #pragma unroll
     for (int c = 0; c < D / 8; ++c) {
       const uint4 v = *reinterpret_cast<const uint4*>(row + c * 8);
@@ -62,12 +63,12 @@ __global__ void __launch_bounds__(kTile) tile_norms_kernel(const __nv_bfloat16* 
     (which == 0 ? qn : kn)[(int64_t)n * ntiles + tile] = fmaxf(fmaxf(part[0], part[1]), fmaxf(part[2], part[3]));
 }
 
-// alive[n][mi][nj] for nj <= mi: one block per (query tile mi, sequence b); a warp takes every fourth key tile, finds
-// the smallest carry over its 128 keys, and its lanes write the verdict for the heads of the sequence.
+// alive[n][mi][nj] for nj <= mi: one block per (query tile mi >= mi_first, sequence b); a warp takes every fourth key
+// tile, finds the smallest carry over its 128 keys, and its lanes write the verdict for the heads of the sequence.
 __global__ void __launch_bounds__(kTile) tile_table_kernel(const float* __restrict__ carry, const float* __restrict__ qn,
                                                            const float* __restrict__ kn, int heads, int seq, int ntiles,
-                                                           float c1, uint8_t* __restrict__ alive) {
-  const int mi = blockIdx.x, b = blockIdx.y;
+                                                           int mi_first, float c1, uint8_t* __restrict__ alive) {
+  const int mi = mi_first + blockIdx.x, b = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const float* carry_row = carry + ((int64_t)b * (ntiles + 1) + mi) * seq;
   for (int nj = warp; nj <= mi; nj += 4) {
@@ -99,7 +100,6 @@ size_t tile_table_bytes(const Problem& p) {
   return (size_t)(table + 2 * nrows * ntiles * 4);
 }
 
-uint8_t* tile_table_alive(const Problem& p) { return static_cast<uint8_t*>(p.tile_table); }
 
 int build_tile_table(const Problem& p, const float* carry, cudaStream_t s) {
   const int ntiles = (p.seq + kTile - 1) / kTile;
@@ -114,14 +114,16 @@ int build_tile_table(const Problem& p, const float* carry, cudaStream_t s) {
   if (p.head_dim == 64)
     tile_norms_kernel<64><<<gn, kTile, 0, s>>>(static_cast<const __nv_bfloat16*>(p.q.ptr), q_rows,
                                                static_cast<const __nv_bfloat16*>(p.k.ptr), k_rows, p.heads, p.seq, ntiles,
-                                               qn, kn);
+                                               p.q_offset, qn, kn);
   else
     tile_norms_kernel<128><<<gn, kTile, 0, s>>>(static_cast<const __nv_bfloat16*>(p.q.ptr), q_rows,
                                                 static_cast<const __nv_bfloat16*>(p.k.ptr), k_rows, p.heads, p.seq, ntiles,
-                                                qn, kn);
+                                                p.q_offset, qn, kn);
   SA_CUDA_CHECK(cudaGetLastError());
   count_launch();
-  tile_table_kernel<<<dim3(ntiles, p.batch), kTile, 0, s>>>(carry, qn, kn, p.heads, p.seq, ntiles, p.scale * kLog2e, alive);
+  const int mi_first = p.q_offset / kTile;                // a continued prefill computes the query tiles from here on
+  tile_table_kernel<<<dim3(ntiles - mi_first, p.batch), kTile, 0, s>>>(carry, qn, kn, p.heads, p.seq, ntiles, mi_first,
+                                                                       p.scale * kLog2e, alive);
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;
 }

@@ -24,7 +24,7 @@ EXPORTS = ("sa_abi_version", "sa_status_string", "sa_last_cuda_error", "sa_engin
            "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step", "sa_device_status", "sa_selftest_tcgen05", "sa_profile_enable",
            "sa_profile_collect", "sa_static_scratch_floats", "sa_forward_static_scratch", "sa_forward_selector",
            "sa_backward_selector", "sa_forward_fused", "sa_backward_fused", "sa_prefill_extend", "sa_selection_carry", "sa_launch_count", "sa_selftest_wait_timeout",
-           "sa_tile_table_bytes", "sa_forward_live_tiles", "sa_backward_live_tiles")
+           "sa_tile_table_bytes", "sa_forward_live_tiles", "sa_backward_live_tiles", "sa_prefill_extend_live_tiles")
 
 
 class Problem(ctypes.Structure):
@@ -99,6 +99,8 @@ def load() -> ctypes.CDLL:
     lib.sa_forward_live_tiles.argtypes = [pp, vp, vp, vp, sp, f32p, tp, f32p, f32p, f32p, vp, sz, vp]
     lib.sa_backward_live_tiles.restype = i32
     lib.sa_backward_live_tiles.argtypes = [pp, vp, vp, vp, sp, f32p, f32p, f32p, tp, tp, tp, tp, f32p, f32p, vp, sz, vp, vp]
+    lib.sa_prefill_extend_live_tiles.restype = i32
+    lib.sa_prefill_extend_live_tiles.argtypes = [pp, i32, vp, vp, vp, f32p, ctypes.c_int64, f32p, f32p, f32p, f32p, vp, sz, vp]
     lib.sa_prefill_extend.restype = i32
     lib.sa_prefill_extend.argtypes = [pp, i32, vp, vp, vp, f32p, ctypes.c_int64, f32p, f32p, f32p, f32p, vp]
     lib.sa_selection_carry.restype = i32

@@ -555,7 +555,8 @@ def selective_attention_packed(qkv: torch.Tensor, exempt: int = 1, *, skip_dead_
 
 # ---- cached decode ------------------------------------------------------------------------------------
 
-def prefill_extend(cache: dict, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, exempt: int = 1) -> torch.Tensor:
+def prefill_extend(cache: dict, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, exempt: int = 1, *,
+                   skip_dead_tiles: bool = False) -> torch.Tensor:
     """Continues a prefill: appends a chunk of new tokens to the cache and returns their outputs, (B, H, Tn, D)
     fp32, as the full forward over cached + new tokens would give them; ``cache["selected"]`` and ``cache["len"]``
     move on to the new length.  (The reference prefills from position 0 only and then decodes token by token,
@@ -563,7 +564,8 @@ def prefill_extend(cache: dict, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
 
     cache: {"k", "v": (B, H, capacity, D) contiguous bf16, "len": int, "selected": (B, G, capacity) fp32} with G = 1
     (head 0 selects) or G = H (every head its own selector).  q, k, v: (B, H, Tn, D).  bf16 operands on the
-    tensor-core engine only (head_dim 64 or 128)."""
+    tensor-core engine only (head_dim 64 or 128).  ``skip_dead_tiles``: as in ``selective_attention``; the part of
+    the cache whose probabilities are all exactly zero for the new queries is not read."""
     lib = _lib.load()
     exempt = _check_exempt(exempt)
     kc, vc, selected = cache["k"], cache["v"], cache["selected"]
@@ -600,10 +602,13 @@ def prefill_extend(cache: dict, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     total = torch.empty(bb, total_len, device=dev, dtype=torch.float32)
     prob = _problem(qn, kv, vv, engine, exempt)
     prob.seq = total_len
+    need = lib.sa_tile_table_bytes(ctypes.byref(prob)) if skip_dead_tiles else 0
+    table = torch.empty(need, device=dev, dtype=torch.uint8) if need else None
     with torch.cuda.device(dev):
-        st = lib.sa_prefill_extend(ctypes.byref(prob), cached, qn.data_ptr(), kv.data_ptr(), vv.data_ptr(),
-                                   selected.data_ptr(), cap, out.data_ptr(), lse2.data_ptr(), carry.data_ptr(),
-                                   total.data_ptr(), _stream(dev))
+        st = lib.sa_prefill_extend_live_tiles(ctypes.byref(prob), cached, qn.data_ptr(), kv.data_ptr(), vv.data_ptr(),
+                                              selected.data_ptr(), cap, out.data_ptr(), lse2.data_ptr(),
+                                              carry.data_ptr(), total.data_ptr(),
+                                              table.data_ptr() if need else None, need, _stream(dev))
     _lib.check("sa_prefill_extend", st)
     selected.view(bb, cap)[:, :total_len] = total
     cache["len"] = total_len

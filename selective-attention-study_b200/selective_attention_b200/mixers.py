@@ -80,10 +80,11 @@ class SelectiveAttentionSlot:
         cache["selected"] = selected
         return y, cache
 
-    def extend_cache(self, q, k, v, cache: dict):
+    def extend_cache(self, q, k, v, cache: dict, skip_dead_tiles: bool = False):
         """A further chunk of prompt tokens: (B, H, Tn, D) outputs in v's dtype; appends to the cache and moves
-        ``selected`` on.  Equals the rows a single prefill over all tokens would produce."""
-        return kernels.prefill_extend(cache, q, k, v, self.exempt).to(v.dtype)
+        ``selected`` on.  Equals the rows a single prefill over all tokens would produce.  ``skip_dead_tiles``: the
+        part of the cache whose probabilities are all exactly zero for these queries is not read (same rows)."""
+        return kernels.prefill_extend(cache, q, k, v, self.exempt, skip_dead_tiles=skip_dead_tiles).to(v.dtype)
 
     def step_cache(self, q1, k1, v1, cache: dict):
         """One token: (B, H, 1, D) in q1's dtype; appends to the cache and updates ``selected``."""

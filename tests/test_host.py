@@ -139,6 +139,9 @@ def test_live_tile_entry_points_check_their_arguments_before_any_launch():
     p.engine = 1
     assert lib.sa_forward_live_tiles(ctypes.byref(p), *args, 256, 16, None) == 4      # table too small
     assert lib.sa_forward_live_tiles(ctypes.byref(p), *args, 16, 1 << 20, None) == 3  # table not 256-byte aligned
+    cont = (128, 16, 16, 16, 16, 1000, 16, 16, 16, 16)
+    assert lib.sa_prefill_extend_live_tiles(ctypes.byref(p), *cont, 256, 16, None) == 4   # table too small
+    assert lib.sa_prefill_extend_live_tiles(ctypes.byref(p), *cont, 16, 1 << 20, None) == 3
 
 
 def test_selector_and_packed_arguments_are_validated_in_python():

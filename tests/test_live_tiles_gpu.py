@@ -126,6 +126,26 @@ def test_packed_projection_form():
     assert _rel(res[0][1], res[1][1]) < 2e-3
 
 
+@pytest.mark.parametrize("first,second,per_head", [(1536, 700, False), (1300, 1000, False), (1100, 900, True)])
+def test_chunked_prefill_skips_the_dead_part_of_the_cache(first, second, per_head):
+    """A continued prefill with the option on returns the rows and the per-key selection of one without, bit for bit."""
+    from selective_attention_b200 import mixers
+    g = torch.Generator("cpu").manual_seed(first + second)
+    total, heads = first + second, 2
+    q, k, v = (torch.randn(1, heads, total, 64, generator=g).bfloat16().cuda() for _ in range(3))
+    rows, sels = [], []
+    for skip in (False, True):
+        slot = mixers.SelectiveAttentionSlot(n_heads=heads, context_length=total + 8, per_head=per_head)
+        _, cache = slot.begin_cache(q[:, :, :first], k[:, :, :first], v[:, :, :first])
+        before = _lib.launch_count()
+        rows.append(slot.extend_cache(q[:, :, first:], k[:, :, first:], v[:, :, first:], cache, skip_dead_tiles=skip))
+        assert _lib.launch_count() - before == (5 if skip else 3)      # + tile norms, tile table
+        sels.append(cache["selected"].clone())
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert torch.equal(rows[0], rows[1]) and torch.equal(sels[0], sels[1])
+
+
 def test_unsupported_engines_ignore_the_request():
     g = torch.Generator("cpu").manual_seed(1)
     q, k, v = (torch.randn(1, 2, 200, 32, generator=g).cuda() for _ in range(3))
