@@ -293,6 +293,19 @@ int sa_decode_step(int dtype, int batch, int heads, int groups, int length, int 
                    void* k_cache, void* v_cache, float* selected, float* y,
                    void* workspace, size_t workspace_bytes, void* stream);
 
+/* The same step, leaving out the dead part of the cache (optional).  The history term of a key only grows, so in a
+ * long context most keys end up with a weight below 2^-150 for every new query: they add nothing to sums of order
+ * one.  With per-key norms the step first marks, from 8 bytes per key, the 64-key stages that hold a key whose bound
+ *   scale log2e |q| |k_j| - log2e selected[j]  >=  (logit of the newest key) - 150
+ * and streams K and V of those stages only; the heads that select stay dense (their new selection is needed for
+ * every key).  The reference reads the whole cache (mixers.py:119-129).
+ *   key_norms        (batch, heads, capacity) fp32: |k_j| of every cached key; the step stores the new key's.
+ *                    NULL: identical to sa_decode_step. */
+int sa_decode_step_live_keys(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim,
+                             int exempt, const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
+                             float* selected, float* key_norms, float* y, void* workspace, size_t workspace_bytes,
+                             void* stream);
+
 /* Per-kernel device timing for benchmarks.  sa_profile_enable(id) makes every later launch of that
  * kernel record a CUDA event pair on its stream (id 0 disables); sa_profile_collect waits for the
  * recorded pairs, writes their durations in milliseconds (launch order) to ms_host, forgets them and

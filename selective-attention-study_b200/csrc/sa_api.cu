@@ -499,6 +499,14 @@ size_t sa_decode_workspace_bytes(int batch, int heads, int groups, int length, i
 int sa_decode_step(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim, int exempt,
                    const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache, float* selected,
                    float* y, void* workspace, size_t workspace_bytes, void* stream) {
+  return sa_decode_step_live_keys(dtype, batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, k_cache,
+                                  v_cache, selected, nullptr, y, workspace, workspace_bytes, stream);
+}
+
+int sa_decode_step_live_keys(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim,
+                             int exempt, const void* q1, const void* k1, const void* v1, void* k_cache, void* v_cache,
+                             float* selected, float* key_norms, float* y, void* workspace, size_t workspace_bytes,
+                             void* stream) {
   if (!dtype_ok(dtype) || batch < 1 || heads < 1 || groups < 1 || heads % groups != 0 || length < 0 || exempt < 1)
     return SA_ERR_BAD_ARGUMENT;
   if (!dim_ok(head_dim)) return SA_ERR_UNSUPPORTED;
@@ -510,7 +518,7 @@ int sa_decode_step(int dtype, int batch, int heads, int groups, int length, int 
   if (workspace_bytes < sa_decode_workspace_bytes(batch, heads, groups, length, head_dim)) return SA_ERR_WORKSPACE;
   if (tc::timeout_pending()) return SA_ERR_DEVICE_TIMEOUT;
   return decode_step(dtype, batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, k_cache, v_cache,
-                     selected, y, static_cast<float*>(workspace), static_cast<cudaStream_t>(stream));
+                     selected, y, static_cast<float*>(workspace), key_norms, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

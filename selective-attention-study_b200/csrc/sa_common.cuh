@@ -99,7 +99,7 @@ int launch_fold_cast(const float* acc, const float* acc0, void* dst, int dtype, 
 size_t decode_workspace_floats(int batch, int heads, int groups, int length, int head_dim);
 int decode_step(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim, int exempt,
                 const void* q1, const void* k1, const void* v1, void* kc, void* vc, float* selected, float* y,
-                float* ws, cudaStream_t s);
+                float* ws, float* knorm, cudaStream_t s);   // knorm: per-key norms, or null (every key is read)
 
 void set_last_cuda_error(int code);
 void count_launch();   // every kernel launch of the library calls this once (sa_launch_count)

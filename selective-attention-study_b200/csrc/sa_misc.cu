@@ -121,12 +121,21 @@ static int decode_split_keys(int t, int rows) {
 }
 
 // Writes the new key and value into the cache and clears the tickets the attend kernel counts CTAs with.
+// With `knorm` (the per-key norms a decode that leaves out dead keys relies on) also stores the new key's norm.
 template <typename T>
 __global__ void append_kernel(const T* __restrict__ k1, const T* __restrict__ v1, T* __restrict__ kc,
                               T* __restrict__ vc, int rows, int capacity, int length, int D,
-                              unsigned int* __restrict__ tickets, int n_tickets) {
+                              unsigned int* __restrict__ tickets, int n_tickets, float* __restrict__ knorm) {
   int idx = blockIdx.x * blockDim.x + threadIdx.x;
   if (idx < n_tickets) tickets[idx] = 0u;
+  if (knorm != nullptr && idx < rows) {
+    float ss = 0.f;
+    for (int d = 0; d < D; ++d) {
+      const float x = to_float<T>(k1[(int64_t)idx * D + d]);
+      ss = fmaf(x, x, ss);
+    }
+    knorm[(int64_t)idx * capacity + length] = sqrtf(ss);
+  }
   if (idx >= rows * D) return;
   int n = idx / D, d = idx - n * D;
   int64_t dst = ((int64_t)n * capacity + length) * D + d;
@@ -167,6 +176,8 @@ __device__ __forceinline__ void bulk_load(void* smem_dst, const void* gmem_src, 
 constexpr int kDecStages = 3;                   // stages of 8 KB of K + 8 KB of V
 constexpr int kDecStageBytes = 8192;            // per tensor
 constexpr size_t kDecSmemBytes = (size_t)kDecStages * 2 * kDecStageBytes + 128;
+constexpr int kDecMaxLive = 512;                // stages (of 8 KB) of a CTA's key range when dead stages are left out
+constexpr float kDecDeadMargin = 150.f;         // binades below the newest key's logit at which a key counts as dead
 
 // Merges the per-split partial softmaxes of one query row; called by all 128 threads of a CTA.  The global
 // maximum is found first so that the weighted sums over splits have no serial dependence: warp w folds splits
@@ -216,11 +227,19 @@ __device__ __forceinline__ void decode_combine_row(const float* prow, float* yro
 // depend on how the arithmetic is scheduled.  A group of D / 8 lanes owns every (128 / lanes)-th key of a stage
 // and keeps its own running maximum, denominator and weighted sum (one pass, rescaled when its maximum grows);
 // the groups are merged at the end.
-template <typename T, int D>
+//
+// LIVE (optional, needs the per-key norms `knorm`): the history term of a key only grows, so most of a long cache
+// can be dead for the new query -- its weight exp2(z - m) is below 2^-150 and adds nothing to fp32 sums of order one.
+// A key is dead when  c1 |q| |k_j| - log2e selected[j]  <  z_new - 150, z_new being the logit of the newest key (its
+// history term is zero, and the row maximum is at least that).  A CTA first marks the 64-key stages of its range that
+// hold a live key (it reads 8 bytes per key for that instead of the 2 x 128 or 256 of K and V) and then streams
+// only those.  The CTAs of a selecting head stay dense: the new query's selection is needed for every key.
+template <typename T, int D, bool LIVE>
 __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
     const T* __restrict__ q1, const T* __restrict__ kc, const T* __restrict__ vc, float* selected,
     float* __restrict__ partial, float* __restrict__ sel_new, int heads, int groups, int t, int capacity,
-    int exempt, float scale, int split_keys, tc::WaitCtx status, float* __restrict__ y, unsigned int* __restrict__ row_tickets, unsigned int* __restrict__ split_tickets, int splits) {
+    int exempt, float scale, int split_keys, tc::WaitCtx status, float* __restrict__ y, unsigned int* __restrict__ row_tickets, unsigned int* __restrict__ split_tickets, int splits,
+    const float* __restrict__ knorm) {
   constexpr int kLanes = D / 8;                                   // lanes per key
   constexpr int kGroups = kDecThreads / kLanes;                   // keys the CTA covers per step
   constexpr int kRowBytes = D * (int)sizeof(T);
@@ -235,6 +254,9 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
   __shared__ float accs[kGroups][D];
   __shared__ float part[4][128 + 1];
   __shared__ unsigned int ticket_s[2];
+  __shared__ uint16_t live_s[LIVE ? kDecMaxLive : 1];             // LIVE: the stages of this CTA's range that hold a live key
+  __shared__ unsigned int live_bits[LIVE ? kDecMaxLive / 32 : 1];
+  __shared__ int live_n_s;
 
   const int n = (int)(blockIdx.x / (unsigned)splits), split = (int)(blockIdx.x % (unsigned)splits);
   const int b = n / heads, h = n - b * heads;
@@ -246,8 +268,11 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
   const uint8_t* kb = reinterpret_cast<const uint8_t*>(kc + (int64_t)n * capacity * D);
   const uint8_t* vb = reinterpret_cast<const uint8_t*>(vc + (int64_t)n * capacity * D);
 
-  auto issue = [&](int st) {                                      // thread 0 only
-    const int j0 = c0 + st * kStageKeys;
+  const bool sparse = LIVE && !selector;                          // this CTA leaves out dead stages
+  auto stage_of = [&](int it) { return sparse ? (int)live_s[it] : it; };
+  auto issue = [&](int it) {                                      // thread 0 only; `it` counts the stages this CTA streams
+    const int st = it;
+    const int j0 = c0 + stage_of(it) * kStageKeys;
     const uint32_t bytes = (uint32_t)(min(kStageKeys, c1 - j0) * kRowBytes);
     uint8_t* dst = ring + (size_t)(st % kDecStages) * 2 * kDecStageBytes;
     uint64_t* bar = &full[st % kDecStages];
@@ -255,23 +280,82 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
     bulk_load(dst, kb + (int64_t)j0 * kRowBytes, bytes, bar);
     bulk_load(dst + kDecStageBytes, vb + (int64_t)j0 * kRowBytes, bytes, bar);
   };
-  if (threadIdx.x == 0) {
-    for (int st = 0; st < kDecStages; ++st) tc::mbar_init(&full[st], 1);
-    tc::mbar_init_fence();
-    for (int st = 0; st < min(kDecStages - 1, n_stages); ++st) issue(st);
-  }
-
   float qv[8];
   load8<T>(q1 + (int64_t)n * D + lane * 8, qv);
   const float* selb = selected + ((int64_t)b * groups + g) * capacity;
   float* selnb = sel_new + ((int64_t)b * groups + g) * t;
+  int n_iter = n_stages;
+  if (sparse) {
+    // |q| and the newest key's logit, by every group of lanes (each holds the whole of q between its lanes)
+    float kx[8], ss = 0.f, dot = 0.f;
+    load8<T>(kc + ((int64_t)n * capacity + (t - 1)) * D + lane * 8, kx);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      ss = fmaf(qv[e], qv[e], ss);
+      dot = fmaf(qv[e], kx[e], dot);
+    }
+#pragma unroll
+    for (int sft = kLanes / 2; sft > 0; sft >>= 1) {
+      ss += __shfl_xor_sync(0xffffffffu, ss, sft);
+      dot += __shfl_xor_sync(0xffffffffu, dot, sft);
+    }
+    const float thr = (dot * scale - selb[t - 1]) * kLog2e - kDecDeadMargin;
+    const float cq = scale * kLog2e * sqrtf(ss);
+    const float* kn = knorm + (int64_t)n * capacity;
+    for (int w = threadIdx.x; w < (n_stages + 31) / 32; w += kDecThreads) live_bits[w] = 0u;
+    __syncthreads();
+    constexpr int kAhead = 4;                                      // independent loads in flight per thread
+    for (int base = c0 + threadIdx.x; base < c1; base += kDecThreads * kAhead) {
+      float nrm[kAhead], sel[kAhead];
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        const int j = base + u * kDecThreads;
+        nrm[u] = (j < c1) ? __ldg(kn + j) : 0.f;
+        sel[u] = (j < c1) ? __ldcg(selb + j) : 0.f;
+      }
+#pragma unroll
+      for (int u = 0; u < kAhead; ++u) {
+        const int j = base + u * kDecThreads;
+        if (j < c1 && cq * nrm[u] - kLog2e * sel[u] >= thr) {
+          const int st = (j - c0) / kStageKeys;
+          atomicOr(&live_bits[st >> 5], 1u << (st & 31));
+        }
+      }
+    }
+    __syncthreads();
+    if (threadIdx.x < 32) {                                        // compact the marked stages, in order
+      int count = 0;
+      for (int w0 = 0; w0 < (n_stages + 31) / 32; w0 += 32) {
+        const int w = w0 + threadIdx.x;
+        const unsigned int bits = (w < (n_stages + 31) / 32) ? live_bits[w] : 0u;
+        int mine = __popc(bits), before = mine;
+#pragma unroll
+        for (int sft = 1; sft < 32; sft <<= 1) {
+          const int v = __shfl_up_sync(0xffffffffu, before, sft);
+          if ((int)threadIdx.x >= sft) before += v;
+        }
+        const int total = __shfl_sync(0xffffffffu, before, 31);
+        int pos = count + before - mine;
+        for (unsigned int rest = bits; rest != 0u; rest &= rest - 1u) live_s[pos++] = (uint16_t)(w * 32 + __ffs(rest) - 1);
+        count += total;
+      }
+      if (threadIdx.x == 0) live_n_s = count;
+    }
+    __syncthreads();
+    n_iter = live_n_s;
+  }
+  if (threadIdx.x == 0) {
+    for (int st = 0; st < kDecStages; ++st) tc::mbar_init(&full[st], 1);
+    tc::mbar_init_fence();
+    for (int st = 0; st < min(kDecStages - 1, n_iter); ++st) issue(st);
+  }
   __syncthreads();                                                // barriers initialised before anyone waits
 
   float m = -INFINITY, den = 0.f, acc[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-  for (int st = 0; st < n_stages; ++st) {
-    const int j0 = c0 + st * kStageKeys;
+  for (int st = 0; st < n_iter; ++st) {
+    const int j0 = c0 + stage_of(st) * kStageKeys;
     float sv[kPer];
 #pragma unroll
     for (int u = 0; u < kPer; ++u) {                              // the history sums arrive while the stage is awaited
@@ -279,7 +363,7 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
       sv[u] = (j < c1) ? selb[j] : 0.f;
     }
     // the slot that stage st + kDecStages - 1 uses was read in iteration st - 1; every thread is past it
-    if (threadIdx.x == 0 && st + kDecStages - 1 < n_stages) issue(st + kDecStages - 1);
+    if (threadIdx.x == 0 && st + kDecStages - 1 < n_iter) issue(st + kDecStages - 1);
     tc::mbar_wait(&full[st % kDecStages], (st / kDecStages) & 1, status, 600);
     const uint8_t* ks = ring + (size_t)(st % kDecStages) * 2 * kDecStageBytes;
     const uint8_t* vs = ks + kDecStageBytes;
@@ -397,9 +481,11 @@ __global__ void __launch_bounds__(kDecThreads) decode_attend_kernel(
 template <typename T>
 int decode_impl(int batch, int heads, int groups, int length, int capacity, int D, int exempt, const void* q1,
                 const void* k1, const void* v1, void* kc, void* vc, float* selected, float* y, float* ws,
-                cudaStream_t s) {
+                float* knorm, cudaStream_t s) {
   const int rows = batch * heads, t = length + 1;
-  const int split_keys = decode_split_keys(t, rows);
+  // With key norms most CTAs find nothing to stream and only the selecting heads stay dense: short key ranges (1024
+  // keys; 512 and 2048 measured slower) then spread those heads over the whole GPU.
+  const int split_keys = (knorm != nullptr) ? 2 * kDecSplitMin : decode_split_keys(t, rows);
   const int splits = (t + split_keys - 1) / split_keys;
   float* partial = ws;
   float* sel_new = partial + (size_t)rows * splits * (D + 2);
@@ -411,7 +497,7 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
   count_launch();
   append_kernel<T><<<(append_threads + 255) / 256, 256, 0, s>>>(
       static_cast<const T*>(k1), static_cast<const T*>(v1), static_cast<T*>(kc), static_cast<T*>(vc), rows, capacity,
-      length, D, row_tickets, n_tickets);
+      length, D, row_tickets, n_tickets, knorm);
   SA_CUDA_CHECK(cudaGetLastError());
   const unsigned grid = (unsigned)rows * (unsigned)splits;
   const float scale = 1.0f / sqrtf((float)D);
@@ -420,14 +506,21 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
   const T* vv = static_cast<const T*>(vc);
   tc::WaitCtx status;
   if (int st = tc::wait_ctx(&status)) return st;
+  // dead stages are left out when the norms are given and a CTA's range fits the stage list
+  const bool live = knorm != nullptr && split_keys / (kDecStageBytes / (D * (int)sizeof(T))) <= kDecMaxLive;
+#define SA_DECODE_LAUNCH_ONE(DIM, LIVE_)                                                                           \
+  do {                                                                                                             \
+    SA_CUDA_CHECK(cudaFuncSetAttribute(decode_attend_kernel<T, DIM, LIVE_>,                                        \
+                                       cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kDecSmemBytes));          \
+    count_launch();                                                                                                \
+    decode_attend_kernel<T, DIM, LIVE_><<<grid, kDecThreads, kDecSmemBytes, s>>>(                                  \
+        q, kk, vv, selected, partial, sel_new, heads, groups, t, capacity, exempt, scale, split_keys, status,      \
+        y, row_tickets, split_tickets, splits, knorm);                                                            \
+  } while (0)
 #define SA_DECODE_LAUNCH(DIM)                                                                                      \
   do {                                                                                                             \
-    SA_CUDA_CHECK(cudaFuncSetAttribute(decode_attend_kernel<T, DIM>, cudaFuncAttributeMaxDynamicSharedMemorySize,  \
-                                       (int)kDecSmemBytes));                                                       \
-    count_launch();                                                                                                \
-    decode_attend_kernel<T, DIM><<<grid, kDecThreads, kDecSmemBytes, s>>>(                                         \
-        q, kk, vv, selected, partial, sel_new, heads, groups, t, capacity, exempt, scale, split_keys, status,      \
-        y, row_tickets, split_tickets, splits);                                                                   \
+    if (live) SA_DECODE_LAUNCH_ONE(DIM, true);                                                                     \
+    else SA_DECODE_LAUNCH_ONE(DIM, false);                                                                         \
   } while (0)
   switch (D) {
     case 16: SA_DECODE_LAUNCH(16); break;
@@ -437,6 +530,7 @@ int decode_impl(int batch, int heads, int groups, int length, int capacity, int 
     default: return SA_ERR_UNSUPPORTED;
   }
 #undef SA_DECODE_LAUNCH
+#undef SA_DECODE_LAUNCH_ONE
   SA_CUDA_CHECK(cudaGetLastError());
   return SA_OK;
 }
@@ -489,17 +583,17 @@ size_t decode_workspace_floats(int batch, int heads, int groups, int length, int
 
 int decode_step(int dtype, int batch, int heads, int groups, int length, int capacity, int head_dim, int exempt,
                 const void* q1, const void* k1, const void* v1, void* kc, void* vc, float* selected, float* y,
-                float* ws, cudaStream_t s) {
+                float* ws, float* knorm, cudaStream_t s) {
   switch (dtype) {
     case SA_F32:
       return decode_impl<float>(batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, kc, vc, selected,
-                                y, ws, s);
+                                y, ws, knorm, s);
     case SA_BF16:
       return decode_impl<__nv_bfloat16>(batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, kc, vc,
-                                        selected, y, ws, s);
+                                        selected, y, ws, knorm, s);
     case SA_F16:
       return decode_impl<__half>(batch, heads, groups, length, capacity, head_dim, exempt, q1, k1, v1, kc, vc, selected,
-                                 y, ws, s);
+                                 y, ws, knorm, s);
   }
   return SA_ERR_BAD_ARGUMENT;
 }

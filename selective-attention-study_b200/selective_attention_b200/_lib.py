@@ -24,7 +24,7 @@ EXPORTS = ("sa_abi_version", "sa_status_string", "sa_last_cuda_error", "sa_engin
            "sa_backward_workspace_bytes", "sa_backward", "sa_decode_workspace_bytes", "sa_decode_step", "sa_device_status", "sa_selftest_tcgen05", "sa_profile_enable",
            "sa_profile_collect", "sa_static_scratch_floats", "sa_forward_static_scratch", "sa_forward_selector",
            "sa_backward_selector", "sa_forward_fused", "sa_backward_fused", "sa_prefill_extend", "sa_selection_carry", "sa_launch_count", "sa_selftest_wait_timeout",
-           "sa_tile_table_bytes", "sa_forward_live_tiles", "sa_backward_live_tiles", "sa_prefill_extend_live_tiles")
+           "sa_tile_table_bytes", "sa_forward_live_tiles", "sa_backward_live_tiles", "sa_prefill_extend_live_tiles", "sa_decode_step_live_keys")
 
 
 class Problem(ctypes.Structure):
@@ -116,6 +116,8 @@ def load() -> ctypes.CDLL:
     lib.sa_decode_workspace_bytes.argtypes = [i32] * 5
     lib.sa_decode_step.restype = i32
     lib.sa_decode_step.argtypes = [i32] * 8 + [vp] * 8 + [sz, vp]
+    lib.sa_decode_step_live_keys.restype = i32
+    lib.sa_decode_step_live_keys.argtypes = [i32] * 8 + [vp] * 9 + [sz, vp]
     lib.sa_device_status.restype = i32
     lib.sa_device_status.argtypes = [ctypes.POINTER(ctypes.c_uint), i32]
     lib.sa_selftest_tcgen05.restype = i32

@@ -586,6 +586,8 @@ def prefill_extend(cache: dict, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
         raise ValueError("the cache is empty: use selective_attention_forward(return_aux=True) for the first chunk")
     kc[:, :, cached:total_len] = k
     vc[:, :, cached:total_len] = v
+    if cache.get("key_norms") is not None:
+        cache["key_norms"][:, :, cached:total_len] = key_norms(k.to(kc.dtype))
     qn = q.to(torch.bfloat16)
     if groups == h and h > 1:             # every head is its own one-head sequence
         qn = qn.reshape(b * h, 1, tn, d)
@@ -615,6 +617,11 @@ def prefill_extend(cache: dict, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     return out.view(b, h, tn, d)
 
 
+def key_norms(k: torch.Tensor) -> torch.Tensor:
+    """|k_j| of every key, fp32, for a decode cache that leaves out dead keys (``cache["key_norms"]``)."""
+    return k.float().norm(dim=-1)
+
+
 def decode_step(cache: dict, q1: torch.Tensor, k1: torch.Tensor, v1: torch.Tensor, exempt: int = 1) -> torch.Tensor:
     """One cached decode step on the device (the reference does this with PyTorch ops,
     ``mixers.py:115-130`` and ``model.py:86-93``).
@@ -622,7 +629,11 @@ def decode_step(cache: dict, q1: torch.Tensor, k1: torch.Tensor, v1: torch.Tenso
     cache: {"k", "v": (B, H, capacity, D) contiguous, "len": int, "selected": (B, G, capacity) fp32}.
     q1, k1, v1: (B, H, 1, D).  Appends k1 / v1 at ``len``, returns y (B, H, 1, D) fp32 and then adds the
     new query's own selection to ``selected`` in place.  G selectors: heads in G contiguous runs, the
-    first head of a run selects."""
+    first head of a run selects.
+
+    When the cache also holds ``"key_norms"`` (B, H, capacity) fp32 (``key_norms(k)`` of the cached keys; the slot's
+    ``begin_cache(..., live_keys=True)`` creates it), the step leaves out the part of the cache whose weights are
+    below 2^-150 for this query and keeps the norms up to date."""
     lib = _lib.load()
     exempt = _check_exempt(exempt)
     kc, vc, selected = cache["k"], cache["v"], cache["selected"]
@@ -642,10 +653,15 @@ def decode_step(cache: dict, q1: torch.Tensor, k1: torch.Tensor, v1: torch.Tenso
     y = torch.empty(b, h, 1, d, device=dev, dtype=torch.float32)
     need = lib.sa_decode_workspace_bytes(b, h, groups, length, d)
     ws = torch.empty(max(need, 1), device=dev, dtype=torch.uint8)
+    norms = cache.get("key_norms")
+    if norms is not None and not (norms.is_cuda and norms.dtype == torch.float32 and norms.is_contiguous()
+                                  and tuple(norms.shape) == (b, h, cap)):
+        raise ValueError("cache['key_norms'] must be a contiguous fp32 CUDA tensor (B, H, capacity)")
     with torch.cuda.device(dev):
-        st = lib.sa_decode_step(_DTYPE_CODE[kc.dtype], b, h, groups, length, cap, d, exempt, q1.data_ptr(),
-                                k1.data_ptr(), v1.data_ptr(), kc.data_ptr(), vc.data_ptr(), selected.data_ptr(),
-                                y.data_ptr(), ws.data_ptr(), need, _stream(dev))
+        st = lib.sa_decode_step_live_keys(_DTYPE_CODE[kc.dtype], b, h, groups, length, cap, d, exempt, q1.data_ptr(),
+                                          k1.data_ptr(), v1.data_ptr(), kc.data_ptr(), vc.data_ptr(),
+                                          selected.data_ptr(), norms.data_ptr() if norms is not None else None,
+                                          y.data_ptr(), ws.data_ptr(), need, _stream(dev))
     _lib.check("sa_decode_step", st)
     cache["len"] = length + 1
     return y

@@ -67,8 +67,9 @@ class SelectiveAttentionSlot:
             logits, total = kernels.selective_logits(q, k, self.exempt)
             return (logits.softmax(dim=-1) @ v.float()).to(v.dtype), total
 
-    def begin_cache(self, q, k, v, capacity: int | None = None):
-        """Prefill: outputs plus the decode cache {"k", "v", "len", "selected"}."""
+    def begin_cache(self, q, k, v, capacity: int | None = None, live_keys: bool = False):
+        """Prefill: outputs plus the decode cache {"k", "v", "len", "selected"}.  ``live_keys`` adds ``"key_norms"``,
+        with which the decode steps leave out the part of the cache that no longer carries weight."""
         b, h, t, d = k.shape
         y, total = self.attend(q, k, v, want_total=True)
         capacity = max(capacity if capacity is not None else self.context_length, t)
@@ -78,6 +79,10 @@ class SelectiveAttentionSlot:
         selected = torch.zeros(b, self.groups, capacity, device=k.device, dtype=torch.float32)
         selected[:, :, :t] = total.float()
         cache["selected"] = selected
+        if live_keys:
+            norms = torch.zeros(b, h, capacity, device=k.device, dtype=torch.float32)
+            norms[:, :, :t] = kernels.key_norms(k)
+            cache["key_norms"] = norms
         return y, cache
 
     def extend_cache(self, q, k, v, cache: dict, skip_dead_tiles: bool = False):

@@ -139,6 +139,8 @@ def test_live_tile_entry_points_check_their_arguments_before_any_launch():
     p.engine = 1
     assert lib.sa_forward_live_tiles(ctypes.byref(p), *args, 256, 16, None) == 4      # table too small
     assert lib.sa_forward_live_tiles(ctypes.byref(p), *args, 16, 1 << 20, None) == 3  # table not 256-byte aligned
+    # the decode step with key norms refuses what the plain step refuses (here: a full cache)
+    assert lib.sa_decode_step_live_keys(0, 1, 2, 1, 8, 8, 32, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1, 1 << 20, None) == 1
     cont = (128, 16, 16, 16, 16, 1000, 16, 16, 16, 16)
     assert lib.sa_prefill_extend_live_tiles(ctypes.byref(p), *cont, 256, 16, None) == 4   # table too small
     assert lib.sa_prefill_extend_live_tiles(ctypes.byref(p), *cont, 16, 1 << 20, None) == 3

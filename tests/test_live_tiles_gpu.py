@@ -146,6 +146,41 @@ def test_chunked_prefill_skips_the_dead_part_of_the_cache(first, second, per_hea
     assert torch.equal(rows[0], rows[1]) and torch.equal(sels[0], sels[1])
 
 
+@pytest.mark.parametrize("heads,per_head,dim", [(4, False, 64), (2, False, 128), (3, True, 64)])
+def test_decode_leaves_out_the_dead_part_of_the_cache(heads, per_head, dim):
+    """Decode steps on a cache with key norms (dead 64-key stages are not read) against the same steps without:
+    outputs and the history vector must be identical.  With one selector per head every CTA stays dense."""
+    import math
+    from selective_attention_b200 import mixers
+    g = torch.Generator("cpu").manual_seed(17 + heads)
+    t0, steps = 6000, 5
+    q, k, v = (torch.randn(1, heads, t0 + steps, dim, generator=g).bfloat16().cuda() for _ in range(3))
+    outs, sels = [], []
+    for live in (False, True):
+        slot = mixers.SelectiveAttentionSlot(n_heads=heads, context_length=t0 + 16, per_head=per_head)
+        _, cache = slot.begin_cache(q[:, :, :t0], k[:, :, :t0], v[:, :, :t0], live_keys=live)
+        if live and not per_head:                     # the case must have something to leave out: head 1, first step
+            sel = cache["selected"][0, 0, :t0].float()
+            kn = cache["key_norms"][0, 1, :t0]
+            q1 = q[0, 1, t0].float()
+            c1 = math.log2(math.e) / math.sqrt(dim)
+            z_new = float((q1 * k[0, 1, t0].float()).sum()) * c1
+            alive = c1 * q1.norm() * kn - math.log2(math.e) * sel >= z_new - 150
+            stages = alive[: t0 // 64 * 64].view(-1, 64).any(dim=1)
+            assert float(stages.float().mean()) < 0.5
+        ys = [slot.step_cache(q[:, :, t0 + s:t0 + s + 1], k[:, :, t0 + s:t0 + s + 1], v[:, :, t0 + s:t0 + s + 1], cache)
+              for s in range(steps)]
+        outs.append(torch.cat(ys, dim=2))
+        sels.append(cache["selected"].clone())
+        if live:
+            want = kernels.key_norms(cache["k"][:, :, :t0 + steps])
+            torch.testing.assert_close(cache["key_norms"][:, :, :t0 + steps], want, atol=1e-3, rtol=1e-3)
+    torch.cuda.synchronize()
+    assert _lib.device_status() == 0
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(sels[0], sels[1])
+
+
 def test_unsupported_engines_ignore_the_request():
     g = torch.Generator("cpu").manual_seed(1)
     q, k, v = (torch.randn(1, 2, 200, 32, generator=g).cuda() for _ in range(3))
