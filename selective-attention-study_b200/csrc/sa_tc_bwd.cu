@@ -34,6 +34,11 @@
 // dK += (dz + g)^T Q and dQ = (dz + g) K, with (dz + g)^T in this thread's X columns.  40 MMAs per query tile instead
 // of 64, no Q0 / K0 tiles, no Z, one read-out per tile (deferred into the next tile's first half).
 //
+// Code shape.  The diagonal tile, the only one that needs the causal mask inside the tile, is the LAST tile of a CTA's
+// walk: the loop holds the unmasked form of the per-half arithmetic only and the masked form runs once after it, and
+// the two halves of a tile are inlined (constant barrier parities and tile addresses).  That removes no work and 8 % of
+// the time.  LIVE: with a table of live tiles (sa_tc_skip.cu) the walk starts at the key tile's last live query tile.
+//
 // Reference for the arithmetic: src/selective_attention/kernels.py:196-268 (one head), :271-364 (the shared
 // selection-gradient products).
 #include <type_traits>
