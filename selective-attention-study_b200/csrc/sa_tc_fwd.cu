@@ -470,11 +470,12 @@ __global__ void __launch_bounds__(kWideThreads, 1)
       mbar_wait(&bar_l0, it & 1, status, 313);
       tc_fence_after_sync();
       const bool masked = (j0 + kTile > i0) || (j0 < exempt);
+      uint32_t r32[32];
+      tmem_ld32(lane_base + kColL + cw, r32);                 // one load and one wait for the step's 32 columns
+      tmem_ld_wait();
 #pragma unroll
       for (int hc = 0; hc < 2; ++hc) {
-        uint32_t r[16];
-        tmem_ld16(lane_base + kColL + cw + hc * 16, r);
-        tmem_ld_wait();
+        const uint32_t* r = r32 + hc * 16;
         float s[16];
         if (masked) {
 #pragma unroll
