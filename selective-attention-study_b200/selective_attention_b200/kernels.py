@@ -648,11 +648,15 @@ def decode_step(cache: dict, q1: torch.Tensor, k1: torch.Tensor, v1: torch.Tenso
     if d not in HEAD_DIMS:
         raise ValueError(f"head_dim must be one of {HEAD_DIMS}; got {d}")
     groups = selected.shape[1]
-    q1, k1, v1 = (t.reshape(b, h, d).to(kc.dtype).contiguous() for t in (q1, k1, v1))
+    q1, k1, v1 = (t.reshape(b, h, d) for t in (q1, k1, v1))
+    q1, k1, v1 = (t if (t.dtype == kc.dtype and t.is_contiguous()) else t.to(kc.dtype).contiguous() for t in (q1, k1, v1))
     dev = kc.device
     y = torch.empty(b, h, 1, d, device=dev, dtype=torch.float32)
     need = lib.sa_decode_workspace_bytes(b, h, groups, length, d)
-    ws = torch.empty(max(need, 1), device=dev, dtype=torch.uint8)
+    ws = cache.get("_workspace")                  # scratch of the step, kept with the cache and grown when needed
+    if ws is None or ws.numel() < need or ws.device != dev:
+        ws = torch.empty(max(2 * need, 1 << 16), device=dev, dtype=torch.uint8)
+        cache["_workspace"] = ws
     norms = cache.get("key_norms")
     if norms is not None and not (norms.is_cuda and norms.dtype == torch.float32 and norms.is_contiguous()
                                   and tuple(norms.shape) == (b, h, cap)):
