@@ -37,8 +37,9 @@ def test_two_ranks_report_the_slowest_time_and_the_whole_job_rate():
 
 
 def test_shard_plans_cover_the_batch_exactly_once():
-    c2, c3, c4 = (bench.WORKLOADS[n] for n in ("c2", "c3", "c4"))
-    for w in (c2, c3, c4):
+    c2, c3, c4, wide = (bench.WORKLOADS[n] for n in ("c2", "c3", "c4", "c2d128"))
+    assert bench.algorithmic_flops(wide)["attention_only"] == bench.algorithmic_flops(c2)["attention_only"]
+    for w in (c2, c3, c4, wide):
         for world in (1, 2, 4, 8):
             if w is c4 and world == 1:
                 continue
